@@ -1,0 +1,164 @@
+// CSR topology from an unsorted int64 key vector (receiver or sender of every edge).
+//
+// rowptr = exclusive prefix sum of the key histogram; order = edge ids grouped by key, ascending
+// inside a row (what a stable sort by key would give), so every reduction that walks a row has a
+// fixed summation order.  Integer atomics are used for the histogram and for handing out slots; the
+// slot order is then made canonical by ranking the edge ids inside each row.  When the keys are
+// already non-decreasing the order is the identity and the ranking pass exits immediately.
+// Replaces ictc_o3/backends/k100/generated_csr_forward.py:17-31 (bincount + cumsum + stable argsort)
+// and the device counting sort ictc_o3/ops/message_topology.py:15-36.
+#include "ictc_common.cuh"
+
+namespace ictc {
+
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 8;
+constexpr int kScanTile = kScanThreads * kScanItems;  // 2048 values per block
+
+__global__ void csr_init_kernel(int64_t* rowptr, int64_t n1, int32_t* flag) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n1) rowptr[i] = 0;
+  if (i == 0) *flag = 1;
+}
+
+__global__ void csr_count_kernel(const int64_t* __restrict__ keys, int64_t E, int64_t N, int64_t* rowptr,
+                                 int32_t* flag) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  const int64_t k = keys[e];
+  if (k < 0 || k >= N) {
+    atomicMin(flag, -1);
+    return;
+  }
+  if (e > 0 && keys[e - 1] > k) atomicMin(flag, 0);
+  atomicAdd(reinterpret_cast<unsigned long long*>(rowptr + k + 1), 1ULL);
+}
+
+// In-place inclusive scan of one 2048-value tile per block; the tile total goes to sums[block].
+__global__ void __launch_bounds__(kScanThreads) scan_tile_kernel(int64_t* data, int64_t n, int64_t* sums) {
+  __shared__ int64_t warp_tot[kScanThreads / 32];
+  const int64_t base = int64_t(blockIdx.x) * kScanTile + int64_t(threadIdx.x) * kScanItems;
+  int64_t v[kScanItems];
+  int64_t run = 0;
+#pragma unroll
+  for (int i = 0; i < kScanItems; ++i) {
+    v[i] = (base + i < n) ? data[base + i] : 0;
+    run += v[i];
+    v[i] = run;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int64_t inc = run;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int64_t up = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += up;
+  }
+  if (lane == 31) warp_tot[warp] = inc;
+  __syncthreads();
+  int64_t offset = inc - run;
+  for (int w = 0; w < warp; ++w) offset += warp_tot[w];
+#pragma unroll
+  for (int i = 0; i < kScanItems; ++i)
+    if (base + i < n) data[base + i] = v[i] + offset;
+  if (sums && threadIdx.x == kScanThreads - 1) sums[blockIdx.x] = offset + run;
+}
+
+__global__ void scan_add_kernel(int64_t* data, int64_t n, const int64_t* sums) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t tile = i / kScanTile;
+  if (i < n && tile > 0) data[i] += sums[tile - 1];
+}
+
+__global__ void csr_cursor_kernel(const int64_t* rowptr, int64_t N, int64_t* cursor) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < N) cursor[i] = rowptr[i];
+}
+
+__global__ void csr_fill_kernel(const int64_t* __restrict__ keys, int64_t E, int64_t N, int64_t* cursor,
+                                int64_t* slots, int64_t* order, const int32_t* flag) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  if (*flag == 1) {
+    order[e] = e;
+    return;
+  }
+  const int64_t k = keys[e];
+  if (k < 0 || k >= N) return;
+  const unsigned long long pos = atomicAdd(reinterpret_cast<unsigned long long*>(cursor + k), 1ULL);
+  slots[pos] = e;
+}
+
+// One warp per row: order[row_begin + rank(edge id)] = edge id.
+__global__ void csr_rank_kernel(const int64_t* __restrict__ rowptr, int64_t N, const int64_t* __restrict__ slots,
+                                int64_t* order, const int32_t* flag) {
+  if (*flag == 1) return;
+  const int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) / 32;
+  if (row >= N) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t begin = rowptr[row], end = rowptr[row + 1];
+  for (int64_t a = begin + lane; a < end; a += 32) {
+    const int64_t mine = slots[a];
+    int64_t rank = 0;
+    for (int64_t b = begin; b < end; ++b) rank += slots[b] < mine;
+    order[begin + rank] = mine;
+  }
+}
+
+static int64_t scan_sums_elems(int64_t n) {
+  int64_t total = 0;
+  while (n > kScanTile) {
+    n = (n + kScanTile - 1) / kScanTile;
+    total += n;
+  }
+  return total + 1;
+}
+
+// Inclusive scan of data[0..n) using `sums` as scratch for the tile totals of every level.
+static void inclusive_scan(int64_t* data, int64_t n, int64_t* sums, cudaStream_t st) {
+  if (n <= 0) return;
+  const int64_t tiles = (n + kScanTile - 1) / kScanTile;
+  scan_tile_kernel<<<(unsigned)tiles, kScanThreads, 0, st>>>(data, n, tiles > 1 ? sums : nullptr);
+  if (tiles > 1) {
+    inclusive_scan(sums, tiles, sums + tiles, st);
+    scan_add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(data, n, sums);
+  }
+}
+
+}  // namespace ictc
+
+using namespace ictc;
+
+extern "C" {
+
+int64_t ictc_csr_scratch_bytes(int64_t N, int64_t E) {
+  if (N < 0 || E < 0) return 0;
+  return 8 * (N + E + scan_sums_elems(N + 1) + 2);
+}
+
+int ictc_csr_build(const int64_t* keys, int64_t N, int64_t E, int64_t* rowptr, int64_t* order, int32_t* sorted_flag,
+                   void* scratch, void* stream) {
+  if (N < 0 || E < 0) { set_error("csr_build: negative size"); return ICTC_ERR_BAD_ARG; }
+  if (!rowptr || !sorted_flag || !scratch || (E > 0 && (!keys || !order))) {
+    set_error("csr_build: NULL buffer");
+    return ICTC_ERR_BAD_ARG;
+  }
+  if ((N + 256) / 256 > 2147483647LL || (E + 255) / 256 > 2147483647LL || (N + 7) / 8 > 2147483647LL) {
+    set_error("csr_build: too many rows");
+    return ICTC_ERR_TOO_LARGE;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  int64_t* cursor = reinterpret_cast<int64_t*>(scratch);
+  int64_t* slots = cursor + N;
+  int64_t* sums = slots + E;
+  csr_init_kernel<<<(unsigned)((N + 1 + 255) / 256), 256, 0, st>>>(rowptr, N + 1, sorted_flag);
+  if (E > 0) csr_count_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(keys, E, N, rowptr, sorted_flag);
+  inclusive_scan(rowptr, N + 1, sums, st);
+  if (E > 0) {
+    if (N > 0) csr_cursor_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(rowptr, N, cursor);
+    csr_fill_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(keys, E, N, cursor, slots, order, sorted_flag);
+    if (N > 0) csr_rank_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(rowptr, N, slots, order, sorted_flag);
+  }
+  return finish_launch("csr_build");
+}
+
+}  // extern "C"

@@ -1,0 +1,132 @@
+// C-ABI entry points of the tensor product / graph message kernels and library-wide helpers.
+#include <stdarg.h>
+#include <string.h>
+#include "tp_kernels.cuh"
+
+namespace ictc {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+#define ICTC_DECL_OPS(S, a, b, c) TpOps tp_ops_##S();
+ICTC_TP_SPEC_LIST(ICTC_DECL_OPS)
+
+struct SpecEntry { int lin, ledge, lout; TpOps ops; };
+
+static const SpecEntry* spec_table(int* count) {
+#define ICTC_ENTRY(S, a, b, c) SpecEntry{a, b, c, tp_ops_##S()},
+  static const SpecEntry table[] = {ICTC_TP_SPEC_LIST(ICTC_ENTRY)};
+  *count = int(sizeof(table) / sizeof(table[0]));
+  return table;
+}
+
+static const TpOps* find_ops(int spec) {
+  int count;
+  const SpecEntry* t = spec_table(&count);
+  if (spec < 0 || spec >= count) {
+    set_error("tensor-product spec %d is not compiled into this library", spec);
+    return nullptr;
+  }
+  return &t[spec].ops;
+}
+
+static bool check(bool ok, const char* what) {
+  if (!ok) set_error("invalid argument: %s", what);
+  return ok;
+}
+
+}  // namespace ictc
+
+using namespace ictc;
+
+extern "C" {
+
+const char* ictc_last_error(void) { return g_error; }
+const char* ictc_version(void) { return "ictc_b200 sm_100a"; }
+
+int ictc_tp_spec(int input_lmax, int edge_lmax, int output_lmax) {
+  int count;
+  const SpecEntry* t = spec_table(&count);
+  for (int i = 0; i < count; ++i)
+    if (t[i].lin == input_lmax && t[i].ledge == edge_lmax && t[i].lout == output_lmax) return i;
+  set_error("no compiled tensor-product kernels for (input_lmax=%d, edge_lmax=%d, output_lmax=%d)", input_lmax,
+            edge_lmax, output_lmax);
+  return ICTC_ERR_BAD_SPEC;
+}
+
+int ictc_tp_spec_info(int spec, int* nx, int* nh, int* np, int* no, int* nnz) {
+  const TpOps* o = find_ops(spec);
+  if (!o) return ICTC_ERR_BAD_SPEC;
+  if (nx) *nx = o->nx;
+  if (nh) *nh = o->nh;
+  if (np) *np = o->np;
+  if (no) *no = o->no;
+  if (nnz) *nnz = o->nnz;
+  return ICTC_OK;
+}
+
+int ictc_tp_edge_forward(int spec, int channels, int64_t num_edges, const float* x, const float* sh, const float* w,
+                         const float* g, const float* mask, float* out, void* stream) {
+  const TpOps* o = find_ops(spec);
+  if (!o) return ICTC_ERR_BAD_SPEC;
+  if (!check(channels > 0 && num_edges >= 0, "channels > 0, num_edges >= 0")) return ICTC_ERR_BAD_ARG;
+  if (num_edges == 0) return ICTC_OK;
+  if (!check(x && sh && g && out, "x, sh, g, out must not be NULL")) return ICTC_ERR_BAD_ARG;
+  TpArgs a{};
+  a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.out = out; a.E = num_edges; a.N = num_edges; a.C = channels;
+  return o->edge_forward(a, (cudaStream_t)stream);
+}
+
+int ictc_tp_edge_adjoint(int spec, int channels, int64_t num_edges, const float* x, const float* sh, const float* w,
+                         const float* g, const float* mask, const float* v, float* dx, float* dsh, float* dg,
+                         void* stream) {
+  const TpOps* o = find_ops(spec);
+  if (!o) return ICTC_ERR_BAD_SPEC;
+  if (!check(channels > 0 && num_edges >= 0, "channels > 0, num_edges >= 0")) return ICTC_ERR_BAD_ARG;
+  if (num_edges == 0 || (!dx && !dsh && !dg)) return ICTC_OK;
+  if (!check(x && sh && g && v, "x, sh, g, v must not be NULL")) return ICTC_ERR_BAD_ARG;
+  TpArgs a{};
+  a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.v = v; a.dx = dx; a.dsh = dsh; a.dg = dg;
+  a.E = num_edges; a.N = num_edges; a.C = channels;
+  return o->adjoint(a, false, (cudaStream_t)stream);
+}
+
+int ictc_tp_graph_forward(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                          const float* sh, const float* w, const float* g, const int64_t* src,
+                          const int64_t* dst_rowptr, const int64_t* dst_order, const float* mask, float* out,
+                          void* stream) {
+  const TpOps* o = find_ops(spec);
+  if (!o) return ICTC_ERR_BAD_SPEC;
+  if (!check(channels > 0 && num_edges >= 0 && num_nodes >= 0, "sizes")) return ICTC_ERR_BAD_ARG;
+  if (num_nodes == 0) return ICTC_OK;
+  if (!check(out && dst_rowptr, "out, dst_rowptr must not be NULL")) return ICTC_ERR_BAD_ARG;
+  if (num_edges > 0 && !check(x && sh && g && src, "x, sh, g, src must not be NULL")) return ICTC_ERR_BAD_ARG;
+  TpArgs a{};
+  a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.out = out; a.nbr = src; a.rowptr = dst_rowptr;
+  a.order = dst_order; a.E = num_edges; a.N = num_nodes; a.C = channels;
+  return o->graph_forward(a, (cudaStream_t)stream);
+}
+
+int ictc_tp_graph_adjoint(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                          const float* sh, const float* w, const float* g, const int64_t* dst,
+                          const int64_t* src_rowptr, const int64_t* src_order, const float* mask, const float* v,
+                          float* dx, float* dsh, float* dg, void* stream) {
+  const TpOps* o = find_ops(spec);
+  if (!o) return ICTC_ERR_BAD_SPEC;
+  if (!check(channels > 0 && num_edges >= 0 && num_nodes >= 0, "sizes")) return ICTC_ERR_BAD_ARG;
+  if (num_nodes == 0 || (!dx && !dsh && !dg)) return ICTC_OK;
+  if (!check(src_rowptr && x, "x, src_rowptr must not be NULL")) return ICTC_ERR_BAD_ARG;
+  if (num_edges > 0 && !check(sh && g && dst && v, "sh, g, dst, v must not be NULL")) return ICTC_ERR_BAD_ARG;
+  TpArgs a{};
+  a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.v = v; a.dx = dx; a.dsh = dsh; a.dg = dg; a.nbr = dst;
+  a.rowptr = src_rowptr; a.order = src_order; a.E = num_edges; a.N = num_nodes; a.C = channels;
+  return o->adjoint(a, true, (cudaStream_t)stream);
+}
+
+}  // extern "C"

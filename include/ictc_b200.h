@@ -1,0 +1,121 @@
+/*
+ * ictc_b200.h — C ABI of the B200 (sm_100a) kernels for the ICTC equivariant hot path.
+ *
+ * Conventions (all entry points):
+ *   - every pointer is a DEVICE pointer unless its name says "host"; buffers are contiguous,
+ *     row-major, IEEE fp32; indices are int64; nothing is allocated, freed or synchronised;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - the return value is 0 on success or a negative ICTC_ERR_* code; kernels never trap or abort;
+ *   - a NULL output pointer means "this result is not needed" where the comment says so;
+ *   - thread-safe for concurrent calls on different streams (no global mutable state except the
+ *     entry point that is documented otherwise).
+ *
+ * Feature rows use the "ir_mul" layout of the reference (ictc_o3/operators.py:283-308):
+ * degrees ascending, each degree stored [2l+1, C] with the channel index contiguous.  Output rows:
+ * degrees ascending, inside a degree one slot per path (slot order = reference `path_offset`,
+ * ictc_o3/basis/ictd_irreps.py:2694-2706), each slot [2l+1, C].  Gates are [E, P, C].
+ *
+ * Each function names the reference interface it replaces (path inside the reference project).
+ */
+#ifndef ICTC_B200_H
+#define ICTC_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ICTC_OK 0
+#define ICTC_ERR_BAD_SPEC (-1)     /* path set / degree not compiled into this library */
+#define ICTC_ERR_BAD_ARG (-2)      /* NULL where a buffer is required, negative size, ... */
+#define ICTC_ERR_LAUNCH (-3)       /* CUDA reported a launch error; see ictc_last_error() */
+#define ICTC_ERR_TOO_LARGE (-4)    /* size beyond a documented limit */
+
+/* Human-readable description of the last error raised on the calling thread. */
+const char* ictc_last_error(void);
+/* Library build tag, e.g. "ictc_b200 sm_100a". */
+const char* ictc_version(void);
+
+/* ------------------------------------------------------------------ tensor-product specs
+ * A spec is the natural-parity path set of EdgeTensorProduct.create(input_lmax, edge_lmax,
+ * output_lmax) (reference: ictc_o3/operators.py:190-215).  Returns the spec id (>= 0) or
+ * ICTC_ERR_BAD_SPEC when that path set has no compiled kernels. */
+int ictc_tp_spec(int input_lmax, int edge_lmax, int output_lmax);
+/* Sizes of a spec in units of one channel vector: nx feature components, nh harmonics,
+ * np paths (= gate blocks), no output components, nnz non-zero couplings. */
+int ictc_tp_spec_info(int spec, int* nx, int* nh, int* np, int* no, int* nnz);
+
+/* ------------------------------------------------------------------ edge-wise tensor product
+ * Replaces generated_forward with edge-owned rows (src = dst = edge id):
+ *   ictc_o3/backends/k100/generated_cartesian_message.py:260-270 (forward branch :179-187),
+ *   called from ictc_o3/operators.py:106-127.
+ * x [E, nx*C], sh [E, nh], g [E, np*C], w [np*C] or NULL (unit base coefficients),
+ * mask [E] or NULL, out [E, no*C] (fully overwritten). */
+int ictc_tp_edge_forward(int spec, int channels, int64_t num_edges, const float* x, const float* sh,
+                         const float* w, const float* g, const float* mask, float* out, void* stream);
+
+/* First adjoint of the edge-wise product; replaces generated_adjoint for edge-owned rows:
+ *   ictc_o3/backends/k100/generated_cartesian_message.py:271-287 (adjoint branch :188-224),
+ *   called from ictc_o3/operators.py:129-158.
+ * v [E, no*C] is the cotangent of out.  dx [E, nx*C], dsh [E, nh], dg [E, np*C]: each may be NULL
+ * when not needed; every non-NULL output is fully overwritten. */
+int ictc_tp_edge_adjoint(int spec, int channels, int64_t num_edges, const float* x, const float* sh,
+                         const float* w, const float* g, const float* mask, const float* v,
+                         float* dx, float* dsh, float* dg, void* stream);
+
+/* ------------------------------------------------------------------ graph message (TP + scatter-sum)
+ * out[n] = sum over edges e with dst(e) = n of TP(x[src(e)], sh[e], g[e]) * mask[e].
+ * Replaces csr_forward / generated_forward with node-owned rows:
+ *   ictc_o3/backends/k100/generated_csr_forward.py:136-157, generated_cartesian_message.py:260-270,
+ *   driven by ictc_o3/ops/rematerialized_message.py:166-205.
+ * The receiver CSR (dst_rowptr [N+1], dst_order [E] or NULL when the edge list is already sorted by
+ * receiver) comes from ictc_csr_build.  Each receiver row is reduced by one warp in CSR order: no
+ * atomics, bitwise reproducible.  x [N, nx*C], out [N, no*C] (fully overwritten, zero rows for
+ * receivers without edges). */
+int ictc_tp_graph_forward(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                          const float* sh, const float* w, const float* g, const int64_t* src,
+                          const int64_t* dst_rowptr, const int64_t* dst_order, const float* mask,
+                          float* out, void* stream);
+
+/* First adjoint of the graph message; replaces generated_adjoint + source_adjoint:
+ *   ictc_o3/backends/k100/generated_cartesian_message.py:271-287, generated_csr_adjoint.py:63-79,
+ *   generated_csr_fused_adjoint.py:13-120, driven by ictc_o3/ops/rematerialized_message.py:25-83.
+ * One traversal owned by the SENDER: dx[s] is reduced over the out-edges of s in sender-CSR order
+ * (src_rowptr [N+1], src_order [E] or NULL when edges are sorted by sender), dg and dsh are written
+ * per edge.  v [N, no*C] is the cotangent of out, gathered at dst[e].  dx [N, nx*C], dsh [E, nh],
+ * dg [E, np*C]; each may be NULL; non-NULL outputs are fully overwritten. */
+int ictc_tp_graph_adjoint(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                          const float* sh, const float* w, const float* g, const int64_t* dst,
+                          const int64_t* src_rowptr, const int64_t* src_order, const float* mask,
+                          const float* v, float* dx, float* dsh, float* dg, void* stream);
+
+/* ------------------------------------------------------------------ CSR topology
+ * Counting sort of edges by an int64 key in [0, num_nodes): rowptr [N+1], order [E] (edge ids,
+ * ascending inside a row, i.e. a stable sort), *sorted_flag (device int32) = 1 when the keys were
+ * already non-decreasing (then order is the identity).  Replaces
+ *   ictc_o3/backends/k100/generated_csr_forward.py:17-31 and the device counting sort
+ *   ictc_o3/ops/message_topology.py:15-36.
+ * scratch: device buffer of ictc_csr_scratch_bytes(N, E) bytes owned by the caller.
+ * Keys outside [0, N) are ignored by the count and set *sorted_flag to -1. */
+int64_t ictc_csr_scratch_bytes(int64_t num_nodes, int64_t num_edges);
+int ictc_csr_build(const int64_t* keys, int64_t num_nodes, int64_t num_edges, int64_t* rowptr,
+                   int64_t* order, int32_t* sorted_flag, void* scratch, void* stream);
+
+/* ------------------------------------------------------------------ direction harmonics
+ * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).
+ * Replaces the harmonics<MODE> kernel run(n,g,h,y,dn,dg,mode,needn,needg):
+ *   ictc_o3/backends/k100/hip_direction_harmonics.py:11-56 (math: ictc_o3/basis/ictd_irreps.py:1153-1208).
+ * forward: n [E,3] -> y [E,(lmax+1)^2].
+ * vjp:     dn[e,a] = sum_h gy[e,h] dY_h/dn_a                        (MODE 1)
+ * second:  given tangent hn [E,3] on the vjp output: dgy[e,h] = sum_a hn_a dY_h/dn_a,
+ *          dn2[e,a] = sum_h gy_h sum_b hn_b d2Y_h/dn_a dn_b          (MODE 2); either may be NULL. */
+int ictc_harmonics_forward(int lmax, int64_t num_edges, const float* n, float* y, void* stream);
+int ictc_harmonics_vjp(int lmax, int64_t num_edges, const float* n, const float* gy, float* dn, void* stream);
+int ictc_harmonics_second(int lmax, int64_t num_edges, const float* n, const float* gy, const float* hn,
+                          float* dn2, float* dgy, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ICTC_B200_H */
