@@ -1,0 +1,329 @@
+#!/usr/bin/env python
+"""Benchmark of the ICTC hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload fused_message]
+
+Workload ``fused_message`` (BASELINE configuration 2): fused edge tensor product + receiver
+scatter-sum, forward and first adjoint (dx, dsh, dg), fp32, C=64, lmax 2, 65,536 atoms at uniform
+random positions in a periodic cube of density 0.1 / A^3, cutoff 4.5 A (about 38 neighbours per
+atom, ~2.5 M directed edges sorted by receiver), node features ~ N(0,1), gates from a random-init
+radial MLP 8 -> 64 -> 64 -> 64 -> 704 over an 8-function Bessel basis.  A "step" is one forward plus
+one adjoint over the whole edge list; the metric is directed edges processed per second.
+
+One JSON line is printed by rank 0.  With N > 1 (torchrun) every rank processes its own independent
+system of the same size (no data-path collective; weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "ictc-o3-hp-k100_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+CHANNELS, LMAX, NUM_ATOMS, DENSITY, CUTOFF = 64, 2, 65536, 0.1, 4.5
+NX, NH, NP, NO = 9, 9, 11, 35
+
+
+def algorithmic_bytes(n, e, c=CHANNELS):
+    """Bytes that one launch must move when every operand crosses HBM exactly once."""
+    fwd = 4 * (n * NX * c + e * NH + e * NP * c + n * NO * c) + 16 * e
+    bwd = 4 * (n * NX * c + e * NH + e * NP * c + n * NO * c) + 16 * e + 4 * (n * NX * c + e * NH + e * NP * c)
+    return fwd, bwd
+
+
+def make_system(seed, num_atoms=NUM_ATOMS):
+    from mace_ictc import synthetic as S
+    pos, box = S.uniform_box(num_atoms, DENSITY, seed)
+    src, dst, shifts = S.neighbor_list_host(pos, box, CUTOFF)
+    return pos, box, src, dst, shifts
+
+
+def make_inputs(seed, device, num_atoms=NUM_ATOMS, dtype=torch.float32):
+    """Inputs of the fused message on ``device`` (torch ops only; untimed set-up)."""
+    from mace_ictc import synthetic as S
+    pos, box, src, dst, shifts = make_system(seed, num_atoms)
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(num_atoms, NX * CHANNELS, generator=gen).to(device=device, dtype=dtype)
+    p = torch.as_tensor(pos, dtype=torch.float64)
+    vec = p[dst] - p[src] + torch.as_tensor(shifts * box, dtype=torch.float64)
+    r = vec.norm(dim=-1)
+    unit = (vec / r.unsqueeze(-1)).to(device=device, dtype=dtype)
+    r = r.to(device=device, dtype=dtype)
+    weights = S.random_radial_mlp([8, 64, 64, 64, NP * CHANNELS], seed + 1, device)
+    weights = [w.to(dtype) for w in weights]
+    gates = torch.cat([S.radial_gates(S.bessel_basis(rr, CUTOFF), weights) for rr in r.split(262144)], 0)
+    v = torch.randn(num_atoms, NO * CHANNELS, generator=gen).to(device=device, dtype=dtype)
+    return {"x": x, "unit": unit, "gates": gates.contiguous(), "v": v,
+            "src": torch.as_tensor(src, device=device), "dst": torch.as_tensor(dst, device=device)}
+
+
+# ------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            if len(row) < 9:
+                continue
+            try:
+                sm.append(float(row[1]))
+                smax = float(row[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, row[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------ CPU arm
+def cpu_reference_step_factory(seed, sample_atoms):
+    """The oracle's restatement of the reference torch path (fp32, all host threads) on a bounded
+    sample: the first ``sample_atoms`` receivers of the workload and all their in-edges."""
+    from oracle import ictc_oracle as O
+    inp = make_inputs(seed, "cpu")
+    rowend = int(torch.searchsorted(inp["dst"], torch.tensor(sample_atoms)))
+    src, dst = inp["src"][:rowend], inp["dst"][:rowend]
+    paths = O.natural_paths(LMAX, LMAX, LMAX)
+    tp = O.TensorProduct(CHANNELS, LMAX, paths, dtype=torch.float32)
+    w = torch.ones(NP, CHANNELS)
+    x = inp["x"].clone().requires_grad_(True)
+    unit = inp["unit"][:rowend].clone().requires_grad_(True)
+    g = inp["gates"][:rowend].reshape(rowend, NP, CHANNELS).clone().requires_grad_(True)
+    v = inp["v"]
+
+    def step():
+        sh = torch.cat(O.direction_harmonics(unit, LMAX), -1)
+        out = O.graph_message(tp, x, sh, g, w, src, dst, None, LMAX, LMAX)
+        torch.autograd.grad(out, [x, unit, g], v)
+        return rowend
+
+    return step, rowend
+
+
+def run_cpu(seed, steps, warmup, sample_atoms):
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    step, edges = cpu_reference_step_factory(seed, sample_atoms)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": edges / dt, "unit": "edges/s", "cores": threads, "kind": "port",
+            "sample": f"first {sample_atoms} receivers of the workload with all their in-edges ({edges} edges), "
+                      f"fp32 torch CPU, forward + adjoint, {steps} timed steps",
+            "ms_per_step": dt * 1e3}
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="fused_message")
+    ap.add_argument("--atoms", type=int, default=NUM_ATOMS)
+    ap.add_argument("--cpu-sample-atoms", type=int, default=2048)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    workload = {"workload": f"fused_message: TP+scatter forward+adjoint, fp32, C{CHANNELS}, lmax {LMAX}, "
+                            f"{args.atoms} atoms/GPU uniform density {DENSITY}, cutoff {CUTOFF}",
+                "l2": "inputs larger than L2 (gates alone are 7 GB)", "atoms_per_gpu": args.atoms}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
+        res = run_cpu(0, steps, warmup, args.cpu_sample_atoms)
+        line = {"impl": "reference", "metric": "TP edges/s", "value": res["value"], "unit": "edges/s",
+                "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": res["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": workload,
+                "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": res["value"], "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    from ictc_o3 import PackedGraphMessage, direction_harmonics
+    from ictc_o3.ops import tensor_product as tpmod
+
+    inp = make_inputs(1000 + rank, dev, args.atoms)
+    n, e = args.atoms, int(inp["src"].numel())
+    op = PackedGraphMessage.create(channels=CHANNELS, input_lmax=LMAX, edge_lmax=LMAX, output_lmax=LMAX, device=dev)
+    sh = torch.cat(direction_harmonics(inp["unit"], LMAX), -1).contiguous()
+    x = inp["x"].requires_grad_(True)
+    shg = sh.requires_grad_(True)
+    g = inp["gates"].requires_grad_(True)
+    src, dst, v = inp["src"], inp["dst"], inp["v"]
+
+    def step():
+        out = op(x, shg, g, src, dst)
+        return torch.autograd.grad(out, [x, shg, g], v)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(local)
+    tpmod.PROFILE = []
+    barrier()
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = start.elapsed_time(stop) / args.steps
+    profile, tpmod.PROFILE = tpmod.PROFILE, None
+    launches = len(profile)
+    kern = {}
+    for name, a, b in profile:
+        kern.setdefault(name, []).append(a.elapsed_time(b))
+    kern_ms = {k: float(np.mean(vv)) for k, vv in kern.items()}
+
+    # end to end: host (pinned) buffers in, host buffers out, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        import psutil
+        host = {k: t.detach() for k, t in (("x", x), ("sh", sh), ("g", g), ("v", v), ("src", src), ("dst", dst))}
+        need = sum(t.numel() * t.element_size() for t in host.values()) * 2.2
+        if psutil.virtual_memory().available > need * 1.5 * max(1, world):
+            pin = {k: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for k, t in host.items()}
+            outs = None
+
+            def e2e_step():
+                nonlocal outs
+                d = {k: t.to(dev, non_blocking=True) for k, t in pin.items()}
+                xs, ss, gs = (d[k].requires_grad_(True) for k in ("x", "sh", "g"))
+                out = op(xs, ss, gs, d["src"], d["dst"])
+                grads = torch.autograd.grad(out, [xs, ss, gs], d["v"])
+                res = (out.detach(),) + grads
+                if outs is None:
+                    outs = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in res]
+                for o, t in zip(outs, res):
+                    o.copy_(t, non_blocking=True)
+
+            e2e_steps = max(1, min(args.steps, 5))
+            for _ in range(2):
+                e2e_step()
+            barrier()
+            s2, t2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s2.record()
+            for _ in range(e2e_steps):
+                e2e_step()
+            t2.record()
+            barrier()
+            e2e_ms = s2.elapsed_time(t2) / e2e_steps
+            h2d = sum(t.numel() * t.element_size() for t in pin.values())
+            d2h = sum(t.numel() * t.element_size() for t in outs)
+            e2e = [e2e_ms, h2d, d2h, e2e_steps]
+            del pin, outs
+
+    if world > 1:
+        t = torch.tensor([ms, e2e[0] if e2e else 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        if e2e:
+            e2e[0] = float(t[1])
+        tot = torch.tensor([e], device=dev, dtype=torch.float64)
+        dist.all_reduce(tot)
+        total_edges = float(tot[0])
+    else:
+        total_edges = float(e)
+
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        else:
+            peak, peak_src = 6650.0, "fallback"
+        fwd_b, bwd_b = algorithmic_bytes(n, e)
+        dom = max(kern_ms, key=kern_ms.get) if kern_ms else None
+        dom_bytes = {"graph_forward": fwd_b, "graph_adjoint": bwd_b}.get(dom, 0)
+        achieved = dom_bytes / (kern_ms[dom] * 1e-3) / 1e9 if dom else None
+        line = {"metric": "TP edges/s", "value": total_edges / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": dict(workload, edges_per_gpu=e, step="forward + adjoint(dx,dsh,dg)"),
+                "gpu_launches": launches, "clocks": clocks,
+                "kernels_ms": kern_ms,
+                "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                             "frac": achieved / peak if achieved else None, "peak_source": peak_src,
+                             "algorithmic_bytes_per_launch": dom_bytes, "traffic": None},
+                "e2e": ({"value": total_edges / (e2e[0] * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": e2e[1],
+                         "d2h_bytes_per_step": e2e[2], "ms_per_step": e2e[0], "steps": e2e[3]} if e2e else None)}
+        if world == 1 and not args.no_cpu_baseline:
+            res = run_cpu(1000, 2, 1, args.cpu_sample_atoms)
+            line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

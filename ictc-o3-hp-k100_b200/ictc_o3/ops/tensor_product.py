@@ -17,6 +17,27 @@ from ..autograd.adjoint_requirements import required_gradients
 from .topology import Topology
 
 
+# When set to a list, every launch appends (kernel name, start event, end event) recorded on the
+# launching stream; used by bench.py to time kernels live and to count launches.
+PROFILE = None
+
+
+class _Timed:
+    def __init__(self, name, device):
+        self.name, self.device = name, device
+
+    def __enter__(self):
+        if PROFILE is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.device))
+
+    def __exit__(self, *exc):
+        if PROFILE is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record(torch.cuda.current_stream(self.device))
+            PROFILE.append((self.name, self.start, end))
+
+
 class TpCall:
     """Bound, non-differentiable arguments of one tensor-product call."""
 
@@ -31,7 +52,9 @@ class TpCall:
     def forward(self, x, sh, g):
         lib, dev, c = _lib.load(), x.device, self.channels
         topo = self.topology
-        with _lib.on_device(dev):
+        if topo is not None:
+            rowptr, order = topo.by_dst()
+        with _lib.on_device(dev), _Timed("edge_forward" if topo is None else "graph_forward", dev):
             if topo is None:
                 e = x.shape[0]
                 out = torch.empty(e, self.no * c, dtype=torch.float32, device=dev)
@@ -39,7 +62,6 @@ class TpCall:
                                                     _lib.ptr(g), _lib.ptr(self.mask), _lib.ptr(out),
                                                     _lib.stream(dev)), "ictc_tp_edge_forward")
             else:
-                rowptr, order = topo.by_dst()
                 out = torch.empty(topo.num_nodes, self.no * c, dtype=torch.float32, device=dev)
                 _lib.check(lib.ictc_tp_graph_forward(self.spec, c, topo.num_nodes, topo.num_edges, _lib.ptr(x),
                                                      _lib.ptr(sh), _lib.ptr(self.weight), _lib.ptr(g),
@@ -57,7 +79,9 @@ class TpCall:
         dg = torch.empty_like(g) if needed[2] else None
         if not any(needed):
             return dx, dsh, dg
-        with _lib.on_device(dev):
+        if topo is not None:
+            topo.by_src()
+        with _lib.on_device(dev), _Timed("edge_adjoint" if topo is None else "graph_adjoint", dev):
             if topo is None:
                 _lib.check(lib.ictc_tp_edge_adjoint(self.spec, c, e, _lib.ptr(x), _lib.ptr(sh), _lib.ptr(self.weight),
                                                     _lib.ptr(g), _lib.ptr(self.mask), _lib.ptr(v), _lib.ptr(dx),
