@@ -77,6 +77,56 @@ def emit_tp(lines):
         lines.append(f"#define ICTC_TP_{n}_QBYP(F,A) " + " ".join(ent))
         op = plan.out_path()
         lines.append(f"#define ICTC_TP_{n}_OUTP(X) " + " ".join(f"X({k},{p})" for k, p in enumerate(op)))
+        # ---- per-edge geometry b[i,k] = sum_j C[i,j,k] sh[j] (at most two terms per entry) shared by all
+        # channels of an edge.  FB: entries ordered for the forward (by output k), AB: for the adjoint
+        # (by (i,p) group).  *_TAB(X): X(j1, c1, j2, c2) rows used to build b from the harmonics.
+        ik = {}
+        for i, j, k, p_, c in plan.nnz:
+            ik.setdefault((i, k, p_), []).append((j, c))
+        assert max(len(v) for v in ik.values()) <= 2
+        lines.append(f"#define ICTC_TP_{n}_NB {len(ik)}")
+
+        def btab(name, order):
+            rows = []
+            for key in order:
+                terms = ik[key] + [(0, 0.0)]
+                rows.append(f"X({terms[0][0]},{flit(terms[0][1])},{terms[1][0]},{flit(terms[1][1])})")
+            lines.append(f"#define ICTC_TP_{n}_{name}_TAB(X) \\\n  " + " \\\n  ".join(
+                " ".join(rows[a:a + 4]) for a in range(0, len(rows), 4)))
+
+        fb = sorted(ik, key=lambda t: (t[1], t[0]))
+        btab("FB", fb)
+        seen, ent = set(), []
+        for e, (i, k, p_) in enumerate(fb):
+            ent.append(f"{'A' if k in seen else 'F'}({e},{i})")
+            seen.add(k)
+            if e + 1 == len(fb) or fb[e + 1][1] != k:
+                ent.append(f"K({k},{p_})")
+        lines.append(f"#define ICTC_TP_{n}_FB(F,A,K) \\\n  " + " \\\n  ".join(
+            " ".join(ent[a:a + 6]) for a in range(0, len(ent), 6)))
+        ab = sorted(ik, key=lambda t: (qidx[(t[0], t[2])], t[1]))
+        btab("AB", ab)
+        ent = []
+        for e, (i, k, p_) in enumerate(ab):
+            first = e == 0 or qidx[(ab[e - 1][0], ab[e - 1][2])] != qidx[(i, p_)]
+            last = e + 1 == len(ab) or qidx[(ab[e + 1][0], ab[e + 1][2])] != qidx[(i, p_)]
+            ent.append(f"{'F' if first else 'A'}({e},{k})")
+            if last:
+                ent.append(f"Q({i},{p_})")
+        lines.append(f"#define ICTC_TP_{n}_AB(F,A,Q) \\\n  " + " \\\n  ".join(
+            " ".join(ent[a:a + 6]) for a in range(0, len(ent), 6)))
+        # couplings ordered by harmonic j with their position t in the constant array
+        byj = sorted(plan.nnz, key=lambda e_: (e_[1], e_[2], e_[0]))
+        lines.append(f"#define ICTC_TP_{n}_CLIST(X) " + " ".join(f"X({flit(e_[4])})" for e_ in byj))
+        import struct
+        bits = [struct.unpack("<I", struct.pack("<f", e_[4]))[0] for e_ in byj]
+        lines.append(f"#define ICTC_TP_{n}_CLIST64(X) " + " ".join(f"X(0x{b:08x}{b:08x}ULL)" for b in bits))
+        seen, ent = set(), []
+        for t, (i, j, k, p_, c) in enumerate(byj):
+            ent.append(f"{'A' if j in seen else 'F'}({t},{i},{j},{k},{p_})")
+            seen.add(j)
+        lines.append(f"#define ICTC_TP_{n}_BYJT(F,A) \\\n  " + " \\\n  ".join(
+            " ".join(ent[a:a + 5]) for a in range(0, len(ent), 5)))
         used_i = sorted({e[0] for e in plan.nnz})
         used_j = sorted({e[1] for e in plan.nnz})
         lines.append(f"#define ICTC_TP_{n}_XUSED(X) " + " ".join(f"X({i})" for i in used_i))
