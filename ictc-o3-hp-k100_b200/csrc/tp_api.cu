@@ -1,9 +1,11 @@
 // C-ABI entry points of the tensor product / graph message kernels and library-wide helpers.
 #include <stdarg.h>
 #include <string.h>
-#include "tp_kernels.cuh"
+#include "tp_tma_kernels.cuh"
 
 namespace ictc {
+
+__device__ int g_kernel_error = 0;
 
 static thread_local char g_error[512] = "";
 
@@ -36,6 +38,18 @@ static const TpOps* find_ops(int spec) {
   return &t[spec].ops;
 }
 
+// Device address of the status word of the current device (looked up once per device).
+static int* status_word() {
+  static int* cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cache[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_kernel_error) == cudaSuccess) cache[dev] = static_cast<int*>(p);
+  }
+  return cache[dev];
+}
+
 static bool check(bool ok, const char* what) {
   if (!ok) set_error("invalid argument: %s", what);
   return ok;
@@ -49,6 +63,21 @@ extern "C" {
 
 const char* ictc_last_error(void) { return g_error; }
 const char* ictc_version(void) { return "ictc_b200 sm_100a"; }
+
+int ictc_kernel_status(int* host_status, int reset) {
+  if (!host_status) { set_error("host_status must not be NULL"); return ICTC_ERR_BAD_ARG; }
+  cudaError_t err = cudaDeviceSynchronize();
+  if (err == cudaSuccess) err = cudaMemcpyFromSymbol(host_status, g_kernel_error, sizeof(int));
+  if (err == cudaSuccess && reset) {
+    const int zero = 0;
+    err = cudaMemcpyToSymbol(g_kernel_error, &zero, sizeof(int));
+  }
+  if (err != cudaSuccess) {
+    set_error("kernel_status: %s", cudaGetErrorString(err));
+    return ICTC_ERR_LAUNCH;
+  }
+  return ICTC_OK;
+}
 
 int ictc_tp_spec(int input_lmax, int edge_lmax, int output_lmax) {
   int count;
@@ -93,7 +122,7 @@ int ictc_tp_edge_adjoint(int spec, int channels, int64_t num_edges, const float*
   if (!check(x && sh && g && v, "x, sh, g, v must not be NULL")) return ICTC_ERR_BAD_ARG;
   TpArgs a{};
   a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.v = v; a.dx = dx; a.dsh = dsh; a.dg = dg;
-  a.E = num_edges; a.N = num_edges; a.C = channels;
+  a.E = num_edges; a.N = num_edges; a.C = channels; a.status = status_word();
   return o->adjoint(a, false, (cudaStream_t)stream);
 }
 
@@ -109,7 +138,7 @@ int ictc_tp_graph_forward(int spec, int channels, int64_t num_nodes, int64_t num
   if (num_edges > 0 && !check(x && sh && g && src, "x, sh, g, src must not be NULL")) return ICTC_ERR_BAD_ARG;
   TpArgs a{};
   a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.out = out; a.nbr = src; a.rowptr = dst_rowptr;
-  a.order = dst_order; a.E = num_edges; a.N = num_nodes; a.C = channels;
+  a.order = dst_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = status_word();
   return o->graph_forward(a, (cudaStream_t)stream);
 }
 
@@ -125,7 +154,7 @@ int ictc_tp_graph_adjoint(int spec, int channels, int64_t num_nodes, int64_t num
   if (num_edges > 0 && !check(sh && g && dst && v, "sh, g, dst, v must not be NULL")) return ICTC_ERR_BAD_ARG;
   TpArgs a{};
   a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.v = v; a.dx = dx; a.dsh = dsh; a.dg = dg; a.nbr = dst;
-  a.rowptr = src_rowptr; a.order = src_order; a.E = num_edges; a.N = num_nodes; a.C = channels;
+  a.rowptr = src_rowptr; a.order = src_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = status_word();
   return o->adjoint(a, true, (cudaStream_t)stream);
 }
 

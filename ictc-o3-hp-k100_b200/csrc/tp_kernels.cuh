@@ -83,6 +83,7 @@ struct TpArgs {
   const int64_t* order;   // CSR edge order or null (identity)
   int64_t N, E;
   int C;
+  int* status;          // device status word for kernels with bounded waits (may be null)
 };
 
 // ---------------------------------------------------------------------------------------------

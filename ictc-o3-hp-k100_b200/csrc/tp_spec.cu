@@ -1,5 +1,5 @@
 // One translation unit per tensor-product spec: compile with -DICTC_SPEC=L222 (etc.).
-#include "tp_fast_kernels.cuh"
+#include "tp_tma_kernels.cuh"
 
 #ifndef ICTC_SPEC
 #error "compile with -DICTC_SPEC=<spec name from generated/tp_spec_tables.cuh>"
@@ -15,5 +15,5 @@
 namespace ictc {
 ICTC_DEFINE_(ICTC_SPEC)
 ICTC_FAST_DEFINE_(ICTC_SPEC)
-TpOps ICTC_CAT(tp_ops_, ICTC_SPEC)() { return make_ops_fast<TpSpec<ICTC_ID(ICTC_SPEC)>, ICTC_ID(ICTC_SPEC)>(); }
+TpOps ICTC_CAT(tp_ops_, ICTC_SPEC)() { return make_ops_tma<TpSpec<ICTC_ID(ICTC_SPEC)>, ICTC_ID(ICTC_SPEC)>(); }
 }  // namespace ictc

@@ -1,0 +1,393 @@
+// Graph-message kernels with TMA-staged rows (C = 32 or 64, 16-byte aligned buffers).
+//
+// Same arithmetic as tp_fast_kernels.cuh.  The wide operands of an edge — its gate row and the
+// gathered feature row (forward) or cotangent row (adjoint) — are contiguous in memory, so one lane
+// fetches each of them with a single bulk asynchronous copy (cp.async.bulk, global -> shared, no
+// multicast) into a warp-private ring of STAGES slots and the warp picks them up from shared memory
+// when an mbarrier reports the bytes have landed.  The ring keeps several edges' worth of HBM
+// requests in flight per warp without holding them in registers, which is what the latency-bound
+// register version lacked.  Index chains (order -> edge -> neighbour row) and the harmonics of the
+// next edge are fetched ahead of use.
+//
+// Every mbarrier wait is bounded: when a wait runs out the warp records the fact in a device error
+// word, waits (bounded again) for its outstanding copies and leaves.  The host reads the word with
+// ictc_kernel_status().
+#pragma once
+#include "tp_fast_kernels.cuh"
+
+namespace ictc {
+
+constexpr long long kWaitCycles = 2000000000LL;   // about one second at the SM clock
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait for the phase with the given parity; false when the time limit ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+  if (mbar_try(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try(bar, parity))
+    if (clock64() - start > kWaitCycles) return false;
+  return true;
+}
+
+template <int CPL> __device__ __forceinline__ Vec<CPL> lds_vec(const unsigned char* p);
+template <> __device__ __forceinline__ Vec<1> lds_vec<1>(const unsigned char* p) {
+  return Vec<1>{*reinterpret_cast<const float*>(p)};
+}
+template <> __device__ __forceinline__ Vec<2> lds_vec<2>(const unsigned char* p) {
+  return Vec<2>{*reinterpret_cast<const unsigned long long*>(p)};
+}
+
+template <class S, class F, int CPL, int STAGES, bool ADJ> struct TmaLayout {
+  static constexpr int C = 32 * CPL;
+  static constexpr int R = (F::NB + 31) / 32, NBP = R * 32;
+  static constexpr unsigned GATE_BYTES = S::NP * C * 4;
+  static constexpr unsigned ROW_BYTES = (ADJ ? S::NO : S::NX) * C * 4;
+  static constexpr unsigned SLOT_BYTES = GATE_BYTES + ROW_BYTES;
+  static constexpr unsigned GEO_BYTES = 2 * NBP * sizeof(Vec<CPL>);
+  static constexpr unsigned BAR_OFF = STAGES * SLOT_BYTES;
+  static constexpr unsigned GEO_OFF = BAR_OFF + ((STAGES * 8 + 15) / 16) * 16;
+  static constexpr unsigned WARP_BYTES = ((GEO_OFF + GEO_BYTES + 127) / 128) * 128;
+  static constexpr unsigned BLOCK_BYTES = WARP_BYTES * kFastWarps;
+};
+
+// ------------------------------------------------------------------------------------------------
+template <class S, class F, int CPL, int STAGES>
+__global__ void __launch_bounds__(kFastWarps * 32) tp_graph_forward_tma_kernel(TpArgs a) {
+  using V = Vec<CPL>;
+  using L = TmaLayout<S, F, CPL, STAGES, false>;
+  constexpr int C = L::C;
+  extern __shared__ __align__(128) unsigned char tma_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t n = int64_t(blockIdx.x) * kFastWarps + warp;
+  if (n >= a.N) return;
+  unsigned char* mine = tma_smem + warp * L::WARP_BYTES;
+  const unsigned bars = smem_addr(mine + L::BAR_OFF);
+  V* geo = reinterpret_cast<V*>(mine + L::GEO_OFF);
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bars + s * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  BTerm bt[L::R];
+#pragma unroll
+  for (int r = 0; r < L::R; ++r) bt[r] = (r * 32 + lane < F::NB) ? F::fb(r * 32 + lane) : BTerm{0, 0.f, 0, 0.f};
+  V acc[S::NO];
+#pragma unroll
+  for (int k = 0; k < S::NO; ++k) acc[k] = V::dup(0.f);
+  const int64_t begin = ldg(a.rowptr + n), end = ldg(a.rowptr + n + 1);
+  auto edge_at = [&](int64_t it) -> int64_t { return a.order ? ldg(a.order + it) : it; };
+  auto issue = [&](int slot, int64_t e, int64_t s) {
+    if (lane == 0) {
+      const unsigned bar = bars + slot * 8;
+      unsigned char* dst = mine + slot * L::SLOT_BYTES;
+      mbar_expect_tx(bar, L::SLOT_BYTES);
+      bulk_g2s(smem_addr(dst), a.g + e * (S::NP * C), L::GATE_BYTES, bar);
+      bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.x + s * (S::NX * C), L::ROW_BYTES, bar);
+    }
+  };
+  // prologue: fill the ring
+#pragma unroll
+  for (int k = 0; k < STAGES; ++k)
+    if (begin + k < end) {
+      const int64_t e = edge_at(begin + k);
+      issue(k, e, ldg(a.nbr + e));
+    }
+  // (edge id, sender) of the edge that will be issued at the END of this iteration, started early
+  int64_t e_pf = 0, s_pf = 0;
+  if (begin + STAGES < end) {
+    e_pf = edge_at(begin + STAGES);
+    s_pf = ldg(a.nbr + e_pf);
+  }
+  int64_t e_cur = begin < end ? edge_at(begin) : 0;
+  float shv = (begin < end && lane < S::NH) ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
+  int slot = 0, buf = 0;
+  unsigned parity = 0;
+  for (int64_t it = begin; it < end; ++it, buf ^= 1) {
+    const int64_t e = e_cur;
+    const float sh_now = shv;
+    // start the index/harmonic loads of later edges before blocking on this edge's data
+    int64_t e_pf2 = 0, s_pf2 = 0;
+    if (it + 1 < end) {
+      e_cur = edge_at(it + 1);
+      shv = lane < S::NH ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
+    }
+    if (it + STAGES + 1 < end) {
+      e_pf2 = edge_at(it + STAGES + 1);
+      s_pf2 = ldg(a.nbr + e_pf2);
+    }
+    V* sb = geo + buf * L::NBP;
+    build_geometry<F::NB, CPL, L::R>(bt, sh_now, lane, sb);
+    if (!mbar_wait(bars + slot * 8, parity)) {
+      if (lane == 0 && a.status) atomicExch(a.status, 1);
+      // outstanding copies of the other slots: bounded second wait, then leave
+      for (int s = 0; s < STAGES; ++s) mbar_wait(bars + s * 8, parity);
+      return;
+    }
+    const unsigned char* base = mine + slot * L::SLOT_BYTES + lane * (CPL * 4);
+    V ge[S::NP], x[S::NX];
+#pragma unroll
+    for (int p = 0; p < S::NP; ++p) ge[p] = lds_vec<CPL>(base + p * (C * 4));
+#pragma unroll
+    for (int i = 0; i < S::NX; ++i) x[i] = lds_vec<CPL>(base + L::GATE_BYTES + i * (C * 4));
+    if (a.mask || a.w) {
+      const V mu = V::dup(a.mask ? ldg(a.mask + e) : 1.f);
+#pragma unroll
+      for (int p = 0; p < S::NP; ++p) {
+        ge[p] = vmul(ge[p], mu);
+        if (a.w) ge[p] = vmul(ge[p], V::load(a.w + p * C + lane * CPL));
+      }
+    }
+    __syncwarp();   // geometry visible; every lane has read its slot data into registers
+    F::forward(x, ge, sb, acc);
+    // the slot's values were consumed by the arithmetic above: refill it for edge it + STAGES
+    if (it + STAGES < end) issue(slot, e_pf, s_pf);
+    e_pf = e_pf2;
+    s_pf = s_pf2;
+    if (++slot == STAGES) {
+      slot = 0;
+      parity ^= 1;
+    }
+  }
+  float* op = a.out + n * (S::NO * C) + lane * CPL;
+#pragma unroll
+  for (int k = 0; k < S::NO; ++k) acc[k].store(op + k * C);
+}
+
+// ------------------------------------------------------------------------------------------------
+template <class S, class F, int CPL, int STAGES, bool GRAPH, bool NEEDX, bool NEEDH, bool NEEDG>
+__global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs a) {
+  using V = Vec<CPL>;
+  using L = TmaLayout<S, F, CPL, STAGES, true>;
+  constexpr int C = L::C;
+  extern __shared__ __align__(128) unsigned char tma_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t owner = int64_t(blockIdx.x) * kFastWarps + warp;
+  if (owner >= (GRAPH ? a.N : a.E)) return;
+  unsigned char* mine = tma_smem + warp * L::WARP_BYTES;
+  const unsigned bars = smem_addr(mine + L::BAR_OFF);
+  V* geo = reinterpret_cast<V*>(mine + L::GEO_OFF);
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bars + s * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  BTerm bt[L::R];
+#pragma unroll
+  for (int r = 0; r < L::R; ++r) bt[r] = (r * 32 + lane < F::NB) ? F::ab(r * 32 + lane) : BTerm{0, 0.f, 0, 0.f};
+  V x[S::NX], dx[S::NX];
+  {
+    const float* xp = a.x + owner * (S::NX * C) + lane * CPL;
+#pragma unroll
+    for (int i = 0; i < S::NX; ++i) {
+      x[i] = V::load(xp + i * C);
+      dx[i] = V::dup(0.f);
+    }
+  }
+  int64_t begin = owner, end = owner + 1;
+  if (GRAPH) {
+    begin = ldg(a.rowptr + owner);
+    end = ldg(a.rowptr + owner + 1);
+  }
+  auto edge_at = [&](int64_t it) -> int64_t { return (GRAPH && a.order) ? ldg(a.order + it) : it; };
+  auto row_of = [&](int64_t e) -> int64_t { return GRAPH ? ldg(a.nbr + e) : e; };
+  auto issue = [&](int slot, int64_t e, int64_t d) {
+    if (lane == 0) {
+      const unsigned bar = bars + slot * 8;
+      unsigned char* dst = mine + slot * L::SLOT_BYTES;
+      mbar_expect_tx(bar, L::SLOT_BYTES);
+      bulk_g2s(smem_addr(dst), a.g + e * (S::NP * C), L::GATE_BYTES, bar);
+      bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.v + d * (S::NO * C), L::ROW_BYTES, bar);
+    }
+  };
+#pragma unroll
+  for (int k = 0; k < STAGES; ++k)
+    if (begin + k < end) {
+      const int64_t e = edge_at(begin + k);
+      issue(k, e, row_of(e));
+    }
+  int64_t e_pf = 0, d_pf = 0;
+  if (begin + STAGES < end) {
+    e_pf = edge_at(begin + STAGES);
+    d_pf = row_of(e_pf);
+  }
+  int64_t e_cur = begin < end ? edge_at(begin) : 0;
+  float shv = (begin < end && lane < S::NH) ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
+  int slot = 0, buf = 0;
+  unsigned parity = 0;
+  for (int64_t it = begin; it < end; ++it, buf ^= 1) {
+    const int64_t e = e_cur;
+    const float sh_now = shv;
+    int64_t e_pf2 = 0, d_pf2 = 0;
+    if (it + 1 < end) {
+      e_cur = edge_at(it + 1);
+      shv = lane < S::NH ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
+    }
+    if (it + STAGES + 1 < end) {
+      e_pf2 = edge_at(it + STAGES + 1);
+      d_pf2 = row_of(e_pf2);
+    }
+    V* sb = geo + buf * L::NBP;
+    if (NEEDX || NEEDG) build_geometry<F::NB, CPL, L::R>(bt, sh_now, lane, sb);
+    if (!mbar_wait(bars + slot * 8, parity)) {
+      if (lane == 0 && a.status) atomicExch(a.status, 2);
+      for (int s = 0; s < STAGES; ++s) mbar_wait(bars + s * 8, parity);
+      return;
+    }
+    const unsigned char* base = mine + slot * L::SLOT_BYTES + lane * (CPL * 4);
+    V ge[S::NP], v[S::NO], scale[S::NP];
+#pragma unroll
+    for (int p = 0; p < S::NP; ++p) ge[p] = lds_vec<CPL>(base + p * (C * 4));
+#pragma unroll
+    for (int k = 0; k < S::NO; ++k) v[k] = lds_vec<CPL>(base + L::GATE_BYTES + k * (C * 4));
+    const bool scaled = a.mask || a.w;
+    if (scaled) {
+      const V mu = V::dup(a.mask ? ldg(a.mask + e) : 1.f);
+#pragma unroll
+      for (int p = 0; p < S::NP; ++p) {
+        scale[p] = a.w ? vmul(mu, V::load(a.w + p * C + lane * CPL)) : mu;
+        ge[p] = vmul(ge[p], scale[p]);
+      }
+    }
+    __syncwarp();
+    if (NEEDX || NEEDG) {
+      V dg[S::NP];
+#pragma unroll
+      for (int p = 0; p < S::NP; ++p) dg[p] = V::dup(0.f);
+      F::template adjoint_xg<NEEDX, NEEDG>(x, v, ge, sb, dx, dg);
+      if (NEEDG) {
+        float* dgp = a.dg + e * (S::NP * C) + lane * CPL;
+#pragma unroll
+        for (int p = 0; p < S::NP; ++p) (scaled ? vmul(dg[p], scale[p]) : dg[p]).store(dgp + p * C);
+      }
+    }
+    if (NEEDH) {
+      V dshv[S::NH];
+      F::dharm(x, v, ge, dshv);
+      float mine_sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < S::NH; ++j) {
+        const float tot = warp_sum(dshv[j].hsum());
+        if (lane == j) mine_sum = tot;
+      }
+      if (lane < S::NH) a.dsh[e * S::NH + lane] = mine_sum;
+    }
+    if (it + STAGES < end) issue(slot, e_pf, d_pf);
+    e_pf = e_pf2;
+    d_pf = d_pf2;
+    if (++slot == STAGES) {
+      slot = 0;
+      parity ^= 1;
+    }
+  }
+  if (NEEDX) {
+    float* dxp = a.dx + owner * (S::NX * C) + lane * CPL;
+#pragma unroll
+    for (int i = 0; i < S::NX; ++i) dx[i].store(dxp + i * C);
+  }
+}
+
+// ---------------------------------------------------------------------------------------- launchers
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <class K> int set_smem(K kernel, unsigned bytes) {
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (err != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%u bytes): %s", bytes, cudaGetErrorString(err));
+    return ICTC_ERR_LAUNCH;
+  }
+  return ICTC_OK;
+}
+
+constexpr int kFwdStages = 3, kAdjStages = 2;
+
+template <class S, class F, int CPL> int launch_graph_forward_tma(const TpArgs& a, cudaStream_t st) {
+  using L = TmaLayout<S, F, CPL, kFwdStages, false>;
+  auto kernel = tp_graph_forward_tma_kernel<S, F, CPL, kFwdStages>;
+  static const int attr = set_smem(kernel, L::BLOCK_BYTES);
+  if (attr != ICTC_OK) return attr;
+  const int64_t blocks = (a.N + kFastWarps - 1) / kFastWarps;
+  kernel<<<(unsigned)blocks, kFastWarps * 32, L::BLOCK_BYTES, st>>>(a);
+  return finish_launch("tp_graph_forward_tma");
+}
+
+template <class S, class F, int CPL, bool GRAPH, bool NX_, bool NH_, bool NG_>
+int launch_adjoint_tma_one(const TpArgs& a, cudaStream_t st) {
+  using L = TmaLayout<S, F, CPL, kAdjStages, true>;
+  auto kernel = tp_adjoint_tma_kernel<S, F, CPL, kAdjStages, GRAPH, NX_, NH_, NG_>;
+  static const int attr = set_smem(kernel, L::BLOCK_BYTES);
+  if (attr != ICTC_OK) return attr;
+  const int64_t owners = GRAPH ? a.N : a.E;
+  const int64_t blocks = (owners + kFastWarps - 1) / kFastWarps;
+  kernel<<<(unsigned)blocks, kFastWarps * 32, L::BLOCK_BYTES, st>>>(a);
+  return finish_launch("tp_adjoint_tma");
+}
+
+template <class S, class F, int CPL, bool GRAPH> int launch_adjoint_tma_g(const TpArgs& a, cudaStream_t st) {
+  const int key = (a.dx ? 4 : 0) | (a.dsh ? 2 : 0) | (a.dg ? 1 : 0);
+  switch (key) {
+    case 1: return launch_adjoint_tma_one<S, F, CPL, GRAPH, false, false, true>(a, st);
+    case 2: return launch_adjoint_tma_one<S, F, CPL, GRAPH, false, true, false>(a, st);
+    case 3: return launch_adjoint_tma_one<S, F, CPL, GRAPH, false, true, true>(a, st);
+    case 4: return launch_adjoint_tma_one<S, F, CPL, GRAPH, true, false, false>(a, st);
+    case 5: return launch_adjoint_tma_one<S, F, CPL, GRAPH, true, false, true>(a, st);
+    case 6: return launch_adjoint_tma_one<S, F, CPL, GRAPH, true, true, false>(a, st);
+    case 7: return launch_adjoint_tma_one<S, F, CPL, GRAPH, true, true, true>(a, st);
+    default: return ICTC_OK;
+  }
+}
+
+template <class S, int ID> int graph_forward_dispatch_tma(const TpArgs& a, cudaStream_t st) {
+  if (a.N > 0 && a.E > 0 && (a.C == 32 || a.C == 64) && (a.N + kFastWarps - 1) / kFastWarps <= 2147483647LL &&
+      aligned16(a.x) && aligned16(a.g) && aligned8(a.out) && (!a.w || aligned8(a.w))) {
+    if (a.C == 64) return launch_graph_forward_tma<S, TpFast<ID, 2>, 2>(a, st);
+    return launch_graph_forward_tma<S, TpFast<ID, 1>, 1>(a, st);
+  }
+  return graph_forward_dispatch<S, ID>(a, st);
+}
+
+template <class S, int ID> int adjoint_dispatch_tma(const TpArgs& a, bool graph, cudaStream_t st) {
+  const int64_t owners = graph ? a.N : a.E;
+  if (owners > 0 && a.E > 0 && (a.C == 32 || a.C == 64) && (owners + kFastWarps - 1) / kFastWarps <= 2147483647LL &&
+      aligned16(a.g) && aligned16(a.v) && aligned8(a.x) && (!a.w || aligned8(a.w)) && (!a.dx || aligned8(a.dx)) &&
+      (!a.dg || aligned8(a.dg))) {
+    if (a.C == 64)
+      return graph ? launch_adjoint_tma_g<S, TpFast<ID, 2>, 2, true>(a, st)
+                   : launch_adjoint_tma_g<S, TpFast<ID, 2>, 2, false>(a, st);
+    return graph ? launch_adjoint_tma_g<S, TpFast<ID, 1>, 1, true>(a, st)
+                 : launch_adjoint_tma_g<S, TpFast<ID, 1>, 1, false>(a, st);
+  }
+  return adjoint_dispatch<S, ID>(a, graph, st);
+}
+
+template <class S, int ID> TpOps make_ops_tma() {
+  return TpOps{S::NX, S::NH, S::NP, S::NO, S::NNZ, &launch_edge_forward<S>, &graph_forward_dispatch_tma<S, ID>,
+               &adjoint_dispatch_tma<S, ID>};
+}
+
+}  // namespace ictc

@@ -20,6 +20,7 @@ _P, _I, _L = C.c_void_p, C.c_int, C.c_int64
 SIGNATURES = {
     "ictc_last_error": (C.c_char_p, []),
     "ictc_version": (C.c_char_p, []),
+    "ictc_kernel_status": (_I, [C.POINTER(C.c_int), _I]),
     "ictc_tp_spec": (_I, [_I, _I, _I]),
     "ictc_tp_spec_info": (_I, [_I] + [C.POINTER(C.c_int)] * 5),
     "ictc_tp_edge_forward": (_I, [_I, _I, _L, _P, _P, _P, _P, _P, _P, _P]),
@@ -59,6 +60,13 @@ def last_error() -> str:
 def check(rc: int, what: str):
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}: {last_error()}")
+
+
+def kernel_status(reset: bool = True) -> int:
+    """Synchronise the current device and return its kernel status word (0 = ok)."""
+    value = C.c_int(0)
+    check(load().ictc_kernel_status(C.byref(value), int(reset)), "ictc_kernel_status")
+    return value.value
 
 
 def ptr(t):

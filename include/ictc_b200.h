@@ -34,6 +34,11 @@ extern "C" {
 
 /* Human-readable description of the last error raised on the calling thread. */
 const char* ictc_last_error(void);
+/* Device-side status word of the current device: kernels with bounded waits (the TMA-staged graph
+ * kernels wait on mbarriers with an iteration limit) record a non-zero code instead of hanging when
+ * a wait runs out.  Synchronises the device, copies the word to *host_status (host pointer) and
+ * clears it when reset != 0.  0 = every kernel so far completed normally. */
+int ictc_kernel_status(int* host_status, int reset);
 /* Library build tag, e.g. "ictc_b200 sm_100a". */
 const char* ictc_version(void);
 

@@ -15,6 +15,14 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-5
 
 
+@pytest.fixture(autouse=True)
+def _kernel_status_is_clean():
+    """No kernel may have given up on a bounded wait."""
+    yield
+    from ictc_o3 import _lib
+    assert _lib.kernel_status() == 0
+
+
 def _rel(a, b, floor=None):
     """max|a-b| / max|b|; ``floor`` (a tensor of the same problem) bounds the denominator from below
     for references that vanish by symmetry."""
