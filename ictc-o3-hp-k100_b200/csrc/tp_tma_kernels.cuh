@@ -61,11 +61,15 @@ template <> __device__ __forceinline__ Vec<2> lds_vec<2>(const unsigned char* p)
   return Vec<2>{*reinterpret_cast<const unsigned long long*>(p)};
 }
 
+// Only the gate rows (a pure HBM stream) go through the ring; the gathered feature / cotangent rows
+// are mostly L2 hits and are loaded straight into registers, which keeps shared-memory traffic low.
+constexpr bool kStageRows = false;
+
 template <class S, class F, int CPL, int STAGES, bool ADJ> struct TmaLayout {
   static constexpr int C = 32 * CPL;
   static constexpr int R = (F::NB + 31) / 32, NBP = R * 32;
   static constexpr unsigned GATE_BYTES = S::NP * C * 4;
-  static constexpr unsigned ROW_BYTES = (ADJ ? S::NO : S::NX) * C * 4;
+  static constexpr unsigned ROW_BYTES = kStageRows ? (ADJ ? S::NO : S::NX) * C * 4 : 0;
   static constexpr unsigned SLOT_BYTES = GATE_BYTES + ROW_BYTES;
   static constexpr unsigned GEO_BYTES = 2 * NBP * sizeof(Vec<CPL>);
   static constexpr unsigned BAR_OFF = STAGES * SLOT_BYTES;
@@ -107,7 +111,7 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_graph_forward_tma_kernel(T
       unsigned char* dst = mine + slot * L::SLOT_BYTES;
       mbar_expect_tx(bar, L::SLOT_BYTES);
       bulk_g2s(smem_addr(dst), a.g + e * (S::NP * C), L::GATE_BYTES, bar);
-      bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.x + s * (S::NX * C), L::ROW_BYTES, bar);
+      if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.x + s * (S::NX * C), L::ROW_BYTES, bar);
     }
   };
   // prologue: fill the ring
@@ -124,16 +128,24 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_graph_forward_tma_kernel(T
     s_pf = ldg(a.nbr + e_pf);
   }
   int64_t e_cur = begin < end ? edge_at(begin) : 0;
+  int64_t r_cur = begin < end ? ldg(a.nbr + e_cur) : 0;
   float shv = (begin < end && lane < S::NH) ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
   int slot = 0, buf = 0;
   unsigned parity = 0;
   for (int64_t it = begin; it < end; ++it, buf ^= 1) {
     const int64_t e = e_cur;
     const float sh_now = shv;
+    V ge[S::NP], x[S::NX];
+    if (!kStageRows) {
+      const float* xp = a.x + r_cur * (S::NX * C) + lane * CPL;
+#pragma unroll
+      for (int i = 0; i < S::NX; ++i) x[i] = V::load(xp + i * C);
+    }
     // start the index/harmonic loads of later edges before blocking on this edge's data
     int64_t e_pf2 = 0, s_pf2 = 0;
     if (it + 1 < end) {
       e_cur = edge_at(it + 1);
+      r_cur = ldg(a.nbr + e_cur);
       shv = lane < S::NH ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
     }
     if (it + STAGES + 1 < end) {
@@ -149,11 +161,12 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_graph_forward_tma_kernel(T
       return;
     }
     const unsigned char* base = mine + slot * L::SLOT_BYTES + lane * (CPL * 4);
-    V ge[S::NP], x[S::NX];
 #pragma unroll
     for (int p = 0; p < S::NP; ++p) ge[p] = lds_vec<CPL>(base + p * (C * 4));
+    if (kStageRows) {
 #pragma unroll
-    for (int i = 0; i < S::NX; ++i) x[i] = lds_vec<CPL>(base + L::GATE_BYTES + i * (C * 4));
+      for (int i = 0; i < S::NX; ++i) x[i] = lds_vec<CPL>(base + L::GATE_BYTES + i * (C * 4));
+    }
     if (a.mask || a.w) {
       const V mu = V::dup(a.mask ? ldg(a.mask + e) : 1.f);
 #pragma unroll
@@ -222,7 +235,7 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs 
       unsigned char* dst = mine + slot * L::SLOT_BYTES;
       mbar_expect_tx(bar, L::SLOT_BYTES);
       bulk_g2s(smem_addr(dst), a.g + e * (S::NP * C), L::GATE_BYTES, bar);
-      bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.v + d * (S::NO * C), L::ROW_BYTES, bar);
+      if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.v + d * (S::NO * C), L::ROW_BYTES, bar);
     }
   };
 #pragma unroll
@@ -237,15 +250,23 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs 
     d_pf = row_of(e_pf);
   }
   int64_t e_cur = begin < end ? edge_at(begin) : 0;
+  int64_t r_cur = begin < end ? row_of(e_cur) : 0;
   float shv = (begin < end && lane < S::NH) ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
   int slot = 0, buf = 0;
   unsigned parity = 0;
   for (int64_t it = begin; it < end; ++it, buf ^= 1) {
     const int64_t e = e_cur;
     const float sh_now = shv;
+    V ge[S::NP], v[S::NO], scale[S::NP];
+    if (!kStageRows) {
+      const float* vp = a.v + r_cur * (S::NO * C) + lane * CPL;
+#pragma unroll
+      for (int k = 0; k < S::NO; ++k) v[k] = V::load(vp + k * C);
+    }
     int64_t e_pf2 = 0, d_pf2 = 0;
     if (it + 1 < end) {
       e_cur = edge_at(it + 1);
+      r_cur = row_of(e_cur);
       shv = lane < S::NH ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
     }
     if (it + STAGES + 1 < end) {
@@ -260,11 +281,12 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs 
       return;
     }
     const unsigned char* base = mine + slot * L::SLOT_BYTES + lane * (CPL * 4);
-    V ge[S::NP], v[S::NO], scale[S::NP];
 #pragma unroll
     for (int p = 0; p < S::NP; ++p) ge[p] = lds_vec<CPL>(base + p * (C * 4));
+    if (kStageRows) {
 #pragma unroll
-    for (int k = 0; k < S::NO; ++k) v[k] = lds_vec<CPL>(base + L::GATE_BYTES + k * (C * 4));
+      for (int k = 0; k < S::NO; ++k) v[k] = lds_vec<CPL>(base + L::GATE_BYTES + k * (C * 4));
+    }
     const bool scaled = a.mask || a.w;
     if (scaled) {
       const V mu = V::dup(a.mask ? ldg(a.mask + e) : 1.f);
@@ -324,7 +346,7 @@ template <class K> int set_smem(K kernel, unsigned bytes) {
   return ICTC_OK;
 }
 
-constexpr int kFwdStages = 3, kAdjStages = 2;
+constexpr int kFwdStages = 4, kAdjStages = 4;
 
 template <class S, class F, int CPL> int launch_graph_forward_tma(const TpArgs& a, cudaStream_t st) {
   using L = TmaLayout<S, F, CPL, kFwdStages, false>;
