@@ -163,5 +163,176 @@ def main():
     write("harmonics_tables.cuh", emit_harmonics)
 
 
+# ------------------------------------------------------------------------------------------------
+# Symmetric contraction (correlation 3, lmax 2): straight-line polynomial code.
+#
+# y[l,m] = sum_nu sum_p W[l,nu,p] * sum_{monomials} A[l,nu][m, monomial, p] * monomial(x), where A is the
+# U tensor of the reference symmetrised over the feature indices (x (x) x (x) x is symmetric, so only
+# the symmetric part of U contributes).  Code is emitted for a generic number type T so the same text
+# serves plain floats and first-order dual numbers (for mixed second derivatives).
+def sc_coefficients():
+    import itertools
+    import numpy as np
+    out = {}
+    for l in range(T.TABLE_LMAX + 1):
+        for nu in (1, 2, 3):
+            u = T.sc_u_tensor(l, nu)
+            if l == 0:
+                u = u[None]
+            sym = {}
+            for idx in itertools.product(range(u.shape[1]), repeat=nu):
+                key = tuple(sorted(idx))
+                sym[key] = sym.get(key, 0) + u[(slice(None),) + idx]
+            terms = {}   # (p, m) -> [(monomial, coeff)]
+            for key, blk in sorted(sym.items()):
+                for m in range(blk.shape[0]):
+                    for p in range(blk.shape[1]):
+                        if abs(blk[m, p]) > T.COEFF_THRESHOLD:
+                            terms.setdefault((p, m), []).append((key, float(blk[m, p])))
+            out[(l, nu)] = (u.shape[-1], terms)
+    return out
+
+
+def sc_weight_offsets(target_lmax):
+    """Offset of the (l_out, nu) weight block inside the packed per-species bank; order (l, nu, p)."""
+    coefs = sc_coefficients()
+    off, res = 0, {}
+    for l in range(target_lmax + 1):
+        for nu in (1, 2, 3):
+            res[(l, nu)] = off
+            off += coefs[(l, nu)][0]
+    return res, off
+
+
+def _mono_expr(key):
+    if len(key) == 1:
+        return f"x[{key[0]}]"
+    if len(key) == 2:
+        return f"q{key[0]}{key[1]}"
+    return f"mul(q{key[0]}{key[1]}, x[{key[2]}])"
+
+
+def emit_sc(lines):
+    coefs = sc_coefficients()
+    lines.append("// Symmetric contraction, lmax 2, correlation 3.  LT = target lmax (0 or 2).")
+    lines.append("// Number type T needs: mul(T,T), add(T,T), madd(float,T,T) = c*a+b, fmadd(T,T,T) = a*b+c, scale(float,T), zero<T>().")
+    for lt in (0, T.TABLE_LMAX):
+        woff, nw = sc_weight_offsets(lt)
+        lines.append(f"#define ICTC_SC_NW_LT{lt} {nw}")
+    quad = [(a, b) for a in range(9) for b in range(a, 9)]
+
+    def used_quads(ls):
+        used = set()
+        for l in ls:
+            for nu in (2, 3):
+                for tl in coefs[(l, nu)][1].values():
+                    for key, _c in tl:
+                        used.add((key[0], key[1]))
+        return sorted(used)
+
+    for lt in (0, T.TABLE_LMAX):
+        ls = list(range(lt + 1))
+        woff, nw = sc_weight_offsets(lt)
+        qs = used_quads(ls)
+        # ---------------- forward
+        lines.append(f"template <class T, class WF> __device__ __forceinline__ void sc_forward_lt{lt}(const T (&x)[9], WF w, T (&y)[{(lt + 1) ** 2}]) {{")
+        for a, b in qs:
+            lines.append(f"  const T q{a}{b} = mul(x[{a}], x[{b}]);")
+        for l in ls:
+            for m in range(2 * l + 1):
+                lines.append(f"  y[{l * l + m}] = zero<T>();")
+            for nu in (1, 2, 3):
+                npath, terms = coefs[(l, nu)]
+                for p in range(npath):
+                    ms = [m for m in range(2 * l + 1) if (p, m) in terms]
+                    if not ms:
+                        continue
+                    lines.append(f"  {{ const T wp = w({woff[(l, nu)] + p});")
+                    for m in ms:
+                        tl = terms[(p, m)]
+                        lines.append(f"    {{ T t = scale({flit(tl[0][1])}, {_mono_expr(tl[0][0])});")
+                        for key, c in tl[1:]:
+                            lines.append(f"      t = madd({flit(c)}, {_mono_expr(key)}, t);")
+                        lines.append(f"      y[{l * l + m}] = fmadd(wp, t, y[{l * l + m}]); }}")
+                    lines.append("  }")
+        lines.append("}")
+        # ---------------- weight gradient: gw[idx] = sum_m gy[l,m] * t[l,nu,p,m]
+        lines.append(f"template <class T, class GF> __device__ __forceinline__ void sc_wgrad_lt{lt}(const T (&x)[9], const T (&gy)[{(lt + 1) ** 2}], GF gw) {{")
+        for a, b in qs:
+            lines.append(f"  const T q{a}{b} = mul(x[{a}], x[{b}]);")
+        for l in ls:
+            for nu in (1, 2, 3):
+                npath, terms = coefs[(l, nu)]
+                for p in range(npath):
+                    ms = [m for m in range(2 * l + 1) if (p, m) in terms]
+                    if not ms:
+                        lines.append(f"  gw({woff[(l, nu)] + p}, zero<T>());")
+                        continue
+                    lines.append("  { T acc = zero<T>();")
+                    for m in ms:
+                        tl = terms[(p, m)]
+                        lines.append(f"    {{ T t = scale({flit(tl[0][1])}, {_mono_expr(tl[0][0])});")
+                        for key, c in tl[1:]:
+                            lines.append(f"      t = madd({flit(c)}, {_mono_expr(key)}, t);")
+                        lines.append(f"      acc = fmadd(gy[{l * l + m}], t, acc); }}")
+                    lines.append(f"    gw({woff[(l, nu)] + p}, acc); }}")
+        lines.append("}")
+        # ---------------- feature gradient: gx = d<gy, y>/dx, one output degree at a time
+        lines.append(f"template <class T, class WF> __device__ __forceinline__ void sc_xgrad_lt{lt}(const T (&x)[9], WF w, const T (&gy)[{(lt + 1) ** 2}], T (&gx)[9]) {{")
+        for a, b in qs:
+            lines.append(f"  const T q{a}{b} = mul(x[{a}], x[{b}]);")
+        for i in range(9):
+            lines.append(f"  gx[{i}] = zero<T>();")
+        for l in ls:
+            lines.append("  {")
+            bymono = {}
+            for nu in (1, 2, 3):
+                npath, terms = coefs[(l, nu)]
+                for (p, m), tl in sorted(terms.items()):
+                    for key, c in tl:
+                        bymono.setdefault(key, []).append((nu, p, m, c))
+            used_a = sorted({(nu, p, m) for v in bymono.values() for nu, p, m, _c in v})
+            for nu, p, m in used_a:
+                lines.append(f"    const T a{nu}_{p}_{m} = mul(w({woff[(l, nu)] + p}), gy[{l * l + m}]);")
+            for key, tl in sorted(bymono.items(), key=lambda kv: (len(kv[0]), kv[0])):
+                nu, p, m, c = tl[0]
+                lines.append(f"    {{ T g = scale({flit(c)}, a{nu}_{p}_{m});")
+                for nu, p, m, c in tl[1:]:
+                    lines.append(f"      g = madd({flit(c)}, a{nu}_{p}_{m}, g);")
+                if len(key) == 1:
+                    lines.append(f"      gx[{key[0]}] = add(gx[{key[0]}], g); }}")
+                elif len(key) == 2:
+                    a, b = key
+                    if a == b:
+                        lines.append(f"      gx[{a}] = fmadd(g, add(x[{a}], x[{a}]), gx[{a}]); }}")
+                    else:
+                        lines.append(f"      gx[{a}] = fmadd(g, x[{b}], gx[{a}]); gx[{b}] = fmadd(g, x[{a}], gx[{b}]); }}")
+                else:
+                    a, b, c3 = key
+                    # d(x_a x_b x_c): group equal indices
+                    from collections import Counter
+                    cnt = Counter(key)
+                    stmts = []
+                    for v, mult in sorted(cnt.items()):
+                        rest = list(key)
+                        rest.remove(v)
+                        r0, r1 = sorted(rest)
+                        qn = f"q{r0}{r1}" if (r0, r1) in set(qs) else f"mul(x[{r0}], x[{r1}])"
+                        gterm = "g" if mult == 1 else f"scale({float(mult)}f, g)"
+                        stmts.append(f"gx[{v}] = fmadd({gterm}, {qn}, gx[{v}]);")
+                    lines.append("      " + " ".join(stmts) + " }")
+            lines.append("  }")
+        lines.append("}")
+        lines.append("")
+
+
+_main_tp = main
+
+
+def main():  # noqa: F811
+    _main_tp()
+    write("sc_code.cuh", emit_sc)
+
+
 if __name__ == "__main__":
     main()

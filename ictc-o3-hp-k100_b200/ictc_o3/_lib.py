@@ -32,6 +32,11 @@ SIGNATURES = {
     "ictc_harmonics_forward": (_I, [_I, _L, _P, _P, _P]),
     "ictc_harmonics_vjp": (_I, [_I, _L, _P, _P, _P, _P]),
     "ictc_harmonics_second": (_I, [_I, _L, _P, _P, _P, _P, _P, _P]),
+    "ictc_sc_num_weights": (_I, [_I, _I]),
+    "ictc_sc_scratch_bytes": (_L, [_I, _I, _I, _L, _I]),
+    "ictc_sc_forward": (_I, [_I, _I, _I, _L, _I, _I, _P, _P, _P, _P, _P]),
+    "ictc_sc_adjoint": (_I, [_I, _I, _I, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "ictc_sc_second": (_I, [_I, _I, _I, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
 }
 
 _lib = None

@@ -120,6 +120,34 @@ int ictc_harmonics_vjp(int lmax, int64_t num_edges, const float* n, const float*
 int ictc_harmonics_second(int lmax, int64_t num_edges, const float* n, const float* gy, const float* hn,
                           float* dn2, float* dgy, void* stream);
 
+/* ------------------------------------------------------------------ symmetric contraction
+ * Per-species symmetric contraction of correlation 3 over lmax-2 node features:
+ *   y[n,c,l,m] = sum_nu sum_p W_nu^l[species(n),p,c] sum U_nu^l[m,i1..i_nu,p] prod_k x[n,c,i_k]
+ * Replaces the SC circuit kernels run(x, bank, g, idx, out, backward), the training-mode run(...) and
+ * reduce(...):  ictc_o3/backends/k100/hip_circuit.py:115-125, 223-255 (math:
+ * ictc_o3/ops/_mace_symmetric_contraction.py:298-354 with U from ictc_o3/basis/ictd_irreps.py:1535-1557).
+ * Only lmax = 2 and target_lmax in {0, 2} are compiled.
+ *   x  [N, 9*C]   node features; ir_mul = 0: degree blocks [C, 2l+1] (the reference's mul_ir rows),
+ *                 ir_mul = 1: degree blocks [2l+1, C]
+ *   w  [S, NW, C] packed weight bank, NW = ictc_sc_num_weights(); block order (l_out, nu = 1,2,3, p)
+ *   y  [N, (target_lmax+1)^2 * C] in the same block convention as x
+ * adjoint: gy is the cotangent of y; gx [N, 9*C] and gw [S, NW, C] may each be NULL.
+ * second : mixed second derivatives.  With Phi = <gy, y>, gx = dPhi/dx, gw = dPhi/dw and cotangents
+ *          hx (of gx, may be NULL) and hw (of gw, may be NULL):  Psi = <hx, gx> + <hw, gw>;
+ *          dgy = dPsi/dgy, dx = dPsi/dx, dw = dPsi/dw (each may be NULL).
+ * scratch: device buffer of ictc_sc_scratch_bytes() bytes, needed when gw / dw is requested (chunk
+ *          partial sums of the weight gradient, reduced in fixed order: no float atomics). */
+int ictc_sc_num_weights(int lmax, int target_lmax);
+int64_t ictc_sc_scratch_bytes(int lmax, int target_lmax, int channels, int64_t num_nodes, int num_species);
+int ictc_sc_forward(int lmax, int target_lmax, int channels, int64_t num_nodes, int num_species, int ir_mul,
+                    const float* x, const int64_t* species, const float* w, float* y, void* stream);
+int ictc_sc_adjoint(int lmax, int target_lmax, int channels, int64_t num_nodes, int num_species, int ir_mul,
+                    const float* x, const int64_t* species, const float* w, const float* gy, float* gx,
+                    float* gw, void* scratch, void* stream);
+int ictc_sc_second(int lmax, int target_lmax, int channels, int64_t num_nodes, int num_species, int ir_mul,
+                   const float* x, const int64_t* species, const float* w, const float* gy, const float* hx,
+                   const float* hw, float* dgy, float* dx, float* dw, void* scratch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
