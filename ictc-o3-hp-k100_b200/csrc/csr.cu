@@ -7,6 +7,7 @@
 // already non-decreasing the order is the identity and the ranking pass exits immediately.
 // Replaces ictc_o3/backends/k100/generated_csr_forward.py:17-31 (bincount + cumsum + stable argsort)
 // and the device counting sort ictc_o3/ops/message_topology.py:15-36.
+#include <mutex>
 #include "ictc_common.cuh"
 
 namespace ictc {
@@ -124,6 +125,12 @@ static void inclusive_scan(int64_t* data, int64_t n, int64_t* sums, cudaStream_t
   }
 }
 
+// ---- built-in scratch for callers that cannot allocate (see ictc_csr_build_static) ----------------
+constexpr int64_t kStaticMaxNodes = 1 << 16;   // 65,536 rows
+constexpr int64_t kStaticMaxEdges = 1 << 20;   // 1,048,576 edges
+constexpr int64_t kStaticElems = kStaticMaxNodes + kStaticMaxEdges + 64;   // + scan totals and padding
+static __device__ __align__(256) int64_t g_csr_static_scratch[kStaticElems];   // ~8.9 MB per device
+
 }  // namespace ictc
 
 using namespace ictc;
@@ -133,6 +140,58 @@ extern "C" {
 int64_t ictc_csr_scratch_bytes(int64_t N, int64_t E) {
   if (N < 0 || E < 0) return 0;
   return 8 * (N + E + scan_sums_elems(N + 1) + 2);
+}
+
+// Device address of the built-in scratch on the current device, looked up on first use per device.
+static int static_scratch(void** out) {
+  static std::mutex lock;
+  static void* cache[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("csr_build_static: cannot identify the current device");
+    return ICTC_ERR_LAUNCH;
+  }
+  std::lock_guard<std::mutex> guard(lock);
+  if (!cache[dev]) {
+    void* p = nullptr;
+    // In host code the array name is only a handle; the kernels need its address on THIS device.
+    err = cudaGetSymbolAddress(&p, g_csr_static_scratch);
+    if (err != cudaSuccess || !p) {
+      set_error("csr_build_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+      return ICTC_ERR_LAUNCH;
+    }
+    cache[dev] = p;
+  }
+  *out = cache[dev];
+  return ICTC_OK;
+}
+
+int ictc_csr_build(const int64_t* keys, int64_t N, int64_t E, int64_t* rowptr, int64_t* order, int32_t* sorted_flag,
+                   void* scratch, void* stream);
+
+int ictc_csr_build_static(const int64_t* keys, int64_t N, int64_t E, int64_t* rowptr, int64_t* order,
+                          int32_t* sorted_flag, void* stream) {
+  if (N < 0 || E < 0) { set_error("csr_build_static: negative size"); return ICTC_ERR_BAD_ARG; }
+  if (N > kStaticMaxNodes || E > kStaticMaxEdges) {
+    set_error("csr_build_static: %lld rows / %lld edges exceed the built-in scratch (at most %lld rows and %lld "
+              "edges); use ictc_csr_build with caller-owned scratch", (long long)N, (long long)E,
+              (long long)kStaticMaxNodes, (long long)kStaticMaxEdges);
+    return ICTC_ERR_TOO_LARGE;
+  }
+  if (ictc_csr_scratch_bytes(N, E) > kStaticElems * 8) {
+    set_error("csr_build_static: internal size bound violated");
+    return ICTC_ERR_TOO_LARGE;
+  }
+  void* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  return ictc_csr_build(keys, N, E, rowptr, order, sorted_flag, scratch, stream);
+}
+
+int ictc_csr_static_limits(int64_t* max_nodes, int64_t* max_edges) {
+  if (max_nodes) *max_nodes = kStaticMaxNodes;
+  if (max_edges) *max_edges = kStaticMaxEdges;
+  return ICTC_OK;
 }
 
 int ictc_csr_build(const int64_t* keys, int64_t N, int64_t E, int64_t* rowptr, int64_t* order, int32_t* sorted_flag,

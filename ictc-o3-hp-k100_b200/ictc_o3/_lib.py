@@ -29,6 +29,8 @@ SIGNATURES = {
     "ictc_tp_graph_adjoint": (_I, [_I, _I, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_csr_scratch_bytes": (_L, [_L, _L]),
     "ictc_csr_build": (_I, [_P, _L, _L, _P, _P, _P, _P, _P]),
+    "ictc_csr_build_static": (_I, [_P, _L, _L, _P, _P, _P, _P]),
+    "ictc_csr_static_limits": (_I, [C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "ictc_harmonics_forward": (_I, [_I, _L, _P, _P, _P]),
     "ictc_harmonics_vjp": (_I, [_I, _L, _P, _P, _P, _P]),
     "ictc_harmonics_second": (_I, [_I, _L, _P, _P, _P, _P, _P, _P]),

@@ -107,6 +107,25 @@ int64_t ictc_csr_scratch_bytes(int64_t num_nodes, int64_t num_edges);
 int ictc_csr_build(const int64_t* keys, int64_t num_nodes, int64_t num_edges, int64_t* rowptr,
                    int64_t* order, int32_t* sorted_flag, void* scratch, void* stream);
 
+/* ictc_csr_build without any allocation by anyone: same result as ictc_csr_build, but the scratch is
+ * a fixed array built into the library (about 8.9 MB of device memory on every GPU that loads the
+ * library, held until the process exits), so the caller passes inputs and outputs only.
+ * No counterpart in the reference; added for hosts that cannot call cudaMalloc where the topology is
+ * rebuilt, e.g. an MD driver that re-sorts its edges every few steps inside a loop where an
+ * allocation would stall the whole device, or a plugin host that hands out all device memory at
+ * start-up and offers no allocator afterwards.
+ * Limits: num_nodes <= 65,536 and num_edges <= 1,048,576 (ictc_csr_static_limits reports them);
+ * larger sizes return ICTC_ERR_TOO_LARGE and change nothing.
+ * The first call on each device looks up the device address of the built-in array (one
+ * cudaGetSymbolAddress with that device current); make that first call before any stream capture
+ * begins.  The entry point itself calls no cudaMalloc / cudaFree or any allocating routine.
+ * All calls on a device share the one array and it keeps whatever the previous call left there;
+ * nothing in it needs to start at zero (every part is written before it is read within a call),
+ * but two calls whose kernels overlap on the GPU (different streams) race on it: serialise them. */
+int ictc_csr_build_static(const int64_t* keys, int64_t num_nodes, int64_t num_edges, int64_t* rowptr,
+                          int64_t* order, int32_t* sorted_flag, void* stream);
+int ictc_csr_static_limits(int64_t* host_max_nodes, int64_t* host_max_edges);
+
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).
  * Replaces the harmonics<MODE> kernel run(n,g,h,y,dn,dg,mode,needn,needg):
