@@ -188,6 +188,15 @@ int ictc_csr_build_static(const int64_t* keys, int64_t N, int64_t E, int64_t* ro
   return ictc_csr_build(keys, N, E, rowptr, order, sorted_flag, scratch, stream);
 }
 
+// Inclusive scan of an int64 device vector in place (used by the neighbour build for its row offsets).
+int64_t ictc_scan_scratch_bytes(int64_t n) { return n < 0 ? 0 : 8 * (scan_sums_elems(n) + 2); }
+int ictc_inclusive_scan_i64(int64_t* data, int64_t n, void* scratch, void* stream) {
+  if (n < 0 || (n > 0 && (!data || !scratch))) { set_error("scan: invalid arguments"); return ICTC_ERR_BAD_ARG; }
+  if ((n + kScanTile - 1) / kScanTile > 2147483647LL) { set_error("scan: too long"); return ICTC_ERR_TOO_LARGE; }
+  inclusive_scan(data, n, reinterpret_cast<int64_t*>(scratch), (cudaStream_t)stream);
+  return finish_launch("inclusive_scan");
+}
+
 int ictc_csr_static_limits(int64_t* max_nodes, int64_t* max_edges) {
   if (max_nodes) *max_nodes = kStaticMaxNodes;
   if (max_edges) *max_edges = kStaticMaxEdges;
