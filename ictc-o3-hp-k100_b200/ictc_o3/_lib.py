@@ -31,6 +31,14 @@ SIGNATURES = {
     "ictc_csr_build": (_I, [_P, _L, _L, _P, _P, _P, _P, _P]),
     "ictc_csr_build_static": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "ictc_csr_static_limits": (_I, [C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "ictc_scan_scratch_bytes": (_L, [_L]),
+    "ictc_inclusive_scan_i64": (_I, [_P, _L, _P, _P]),
+    "ictc_neighbor_scratch_bytes": (_L, [_L, C.POINTER(C.c_double), C.POINTER(C.c_double), C.c_double]),
+    "ictc_neighbor_count": (_I, [_P, _L, _L, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
+                                 C.POINTER(C.c_int), C.c_double, _P, _P, _P]),
+    "ictc_neighbor_fill": (_I, [_P, _L, _L, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
+                                C.POINTER(C.c_int), C.c_double, _P, _L, _P, _P, _P, _P, _P, _P]),
+    "ictc_md_kick": (_I, [_L, C.c_float, _P, _P, _P, _P, _P, _I, _P]),
     "ictc_harmonics_forward": (_I, [_I, _L, _P, _P, _P]),
     "ictc_harmonics_vjp": (_I, [_I, _L, _P, _P, _P, _P]),
     "ictc_harmonics_second": (_I, [_I, _L, _P, _P, _P, _P, _P, _P]),

@@ -1,0 +1,198 @@
+"""Molecular-dynamics step on the B200 kernels: neighbour build, energy and forces, velocity Verlet,
+optional spatial domain decomposition over the GPUs of one node.
+
+The reference runs MD through LAMMPS (``examples/in.hco``: metal units, NVE, neighbour rebuild with
+0.5 A skin) with its pair style building the edge list from LAMMPS' full neighbour list
+(lammps_user_mfftorch/src/USER-MFFTORCH/pair_mff_torch_kokkos.cpp:661-871) and calling the model for
+``E_local = sum over owned atoms`` and ``F = -dE/dpos`` (mff_torch_engine.cpp:1739-1859).  LAMMPS is not
+part of this build; this module is the stand-alone driver with the same step semantics.
+Units: A, fs, eV, amu (1 eV/(A amu) = 9.64853321e-3 A/fs^2).
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from ictc_o3 import _lib
+from ictc_o3.ops.topology import Topology
+from . import domain as D
+
+KB_EV = 8.617333262e-5
+ACCEL = 9.64853321e-3
+MASSES = {1: 1.008, 6: 12.011, 8: 15.999}
+
+
+def neighbor_list(pos, num_centres, lo, hi, box, periodic, cutoff):
+    """Edges (src=j, dst=i) of the first ``num_centres`` rows, sorted by (dst, src, shift).
+
+    pos [N,3] fp32 CUDA; lo/hi: bounds of the cell grid; box: periodic lengths; periodic: 3 flags.
+    Returns src, dst (int64 [E]), shifts (float32 [E,3], lattice units), rowptr (int64 [centres+1]).
+    """
+    import ctypes as C
+    lib, dev = _lib.load(), pos.device
+    n = pos.shape[0]
+    arr = lambda v, t: (t * 3)(*[v[i] for i in range(3)])
+    lo_c, hi_c, box_c = arr([float(x) for x in lo], C.c_double), arr([float(x) for x in hi], C.c_double), \
+        arr([float(x) for x in box], C.c_double)
+    per_c = arr([int(x) for x in periodic], C.c_int)
+    nbytes = int(lib.ictc_neighbor_scratch_bytes(n, lo_c, hi_c, float(cutoff)))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    rowptr = torch.empty(num_centres + 1, dtype=torch.int64, device=dev)
+    scan = torch.empty(int(lib.ictc_scan_scratch_bytes(num_centres + 1)), dtype=torch.uint8, device=dev)
+    pos = pos.contiguous()
+    with _lib.on_device(dev):
+        st = _lib.stream(dev)
+        _lib.check(lib.ictc_neighbor_count(pos.data_ptr(), n, num_centres, lo_c, hi_c, box_c, per_c, float(cutoff),
+                                           rowptr.data_ptr(), scratch.data_ptr(), st), "ictc_neighbor_count")
+        _lib.check(lib.ictc_inclusive_scan_i64(rowptr.data_ptr(), num_centres + 1, scan.data_ptr(), st),
+                   "ictc_inclusive_scan_i64")
+        e = int(rowptr[-1].item())
+        src = torch.empty(e, dtype=torch.int64, device=dev)
+        dst = torch.empty(e, dtype=torch.int64, device=dev)
+        shifts = torch.empty(e, 3, dtype=torch.float32, device=dev)
+        keys = torch.empty(e, dtype=torch.int64, device=dev)
+        _lib.check(lib.ictc_neighbor_fill(pos.data_ptr(), n, num_centres, lo_c, hi_c, box_c, per_c, float(cutoff),
+                                          rowptr.data_ptr(), e, _lib.ptr(src), _lib.ptr(dst), _lib.ptr(shifts),
+                                          _lib.ptr(keys), scratch.data_ptr(), st), "ictc_neighbor_fill")
+    return src, dst, shifts, rowptr
+
+
+def maxwell_boltzmann(masses: np.ndarray, temperature: float, seed: int) -> np.ndarray:
+    """Gaussian velocities (A/fs) at ``temperature`` with zero total momentum, rescaled to the exact
+    target (LAMMPS ``velocity all create T seed mom yes rot no dist gaussian``)."""
+    rng = np.random.default_rng(seed)
+    sigma = np.sqrt(KB_EV * temperature * ACCEL / masses)[:, None]
+    v = rng.normal(size=(masses.shape[0], 3)) * sigma
+    v -= (v * masses[:, None]).sum(0) / masses.sum()
+    ke = 0.5 * (masses[:, None] * v * v).sum() / ACCEL
+    dof = 3 * masses.shape[0] - 3
+    v *= math.sqrt(0.5 * dof * KB_EV * temperature / ke)
+    return v.astype(np.float32)
+
+
+class MolecularDynamics:
+    """NVE velocity-Verlet driver around a model created by ``mace_ictc.hp.create_model``.
+
+    With ``torch.distributed`` initialised (one rank per GPU) atoms are split over a brick grid: each
+    rank evaluates energies of its own atoms, node features of ghost atoms cross ranks inside the model
+    (``domain.exchange``) and the position gradients are summed over ranks.
+    """
+
+    def __init__(self, model, positions, atomic_numbers, box, *, dt=1.0, temperature=300.0, seed=0,
+                 velocities=None, distributed=False):
+        self.model = model
+        dev = next(model.parameters()).device
+        self.device = dev
+        self.box = torch.as_tensor(np.asarray(box, dtype=np.float64))
+        self.box_f = self.box.to(dev, torch.float32)
+        self.pos = torch.as_tensor(np.asarray(positions, dtype=np.float32)).to(dev).contiguous()
+        self.z = torch.as_tensor(np.asarray(atomic_numbers)).long().to(dev)
+        masses = np.array([MASSES[int(a)] for a in np.asarray(atomic_numbers)], dtype=np.float64)
+        self.masses = torch.as_tensor(masses, dtype=torch.float32).to(dev)
+        self.inv_mass = (1.0 / self.masses).contiguous()
+        if velocities is None:
+            velocities = maxwell_boltzmann(masses, temperature, seed)
+        self.vel = torch.as_tensor(np.asarray(velocities, dtype=np.float32)).to(dev).contiguous()
+        self.dt = float(dt)
+        self.cutoff = float(model.max_radius)
+        self.distributed = bool(distributed)
+        if self.distributed:
+            import torch.distributed as dist
+            self.rank, self.world = dist.get_rank(), dist.get_world_size()
+            self.grid = D.brick_grid(self.world, self.box.tolist())
+        else:
+            self.rank, self.world, self.grid = 0, 1, (1, 1, 1)
+        model.preserve_edge_order = True
+        model.skip_input_validation = True
+        self.forces = None
+        self.energy = None
+        self.num_edges = 0
+        self.launches = 0
+
+    # ------------------------------------------------------------------ forces
+    def compute_forces(self):
+        if self.world == 1:
+            return self._forces_single()
+        return self._forces_decomposed()
+
+    def _forces_single(self):
+        n = self.pos.shape[0]
+        box = self.box.tolist()
+        src, dst, shifts, rowptr = neighbor_list(self.pos, n, [0, 0, 0], box, box, (1, 1, 1), self.cutoff)
+        self.num_edges = int(src.numel())
+        topo = Topology(src, dst, n, dst_sorted=True)
+        topo._by_dst = (rowptr, None)
+        pos = self.pos.detach().requires_grad_(True)
+        batch = torch.zeros(n, dtype=torch.long, device=self.device)
+        cell = torch.diag(self.box_f).unsqueeze(0)
+        with torch.enable_grad():
+            atomic = self.model(pos, self.z, batch, src, dst, shifts, cell, topology=topo)
+            energy = atomic.sum()
+            (grad,) = torch.autograd.grad(energy, pos)
+        self.energy = energy.detach()
+        self.forces = (-grad).contiguous()
+        return self.forces
+
+    def _forces_decomposed(self):
+        import torch.distributed as dist
+        dom = D.decompose(self.pos, self.box.to(self.device), self.grid, self.rank, self.cutoff)
+        plan = D.ExchangePlan(dom, self.rank, self.world)
+        n_owned = dom.num_owned
+        if n_owned == 0:
+            raise RuntimeError("a rank owns no atoms; use fewer ranks for this box")
+        local = dom.local_positions(self.pos, self.box.to(self.device)).contiguous()
+        ids = dom.local_ids()
+        lo = (dom.lo - self.cutoff).tolist()
+        hi = (dom.hi + self.cutoff).tolist()
+        src, dst, shifts, rowptr = neighbor_list(local, n_owned, lo, hi, self.box.tolist(), (0, 0, 0), self.cutoff)
+        self.num_edges = int(src.numel())
+        n_local = local.shape[0]
+        topo = Topology(src, dst, n_local, dst_sorted=True)
+        pad = rowptr.new_full((n_local - n_owned,), int(rowptr[-1].item()))
+        topo._by_dst = (torch.cat((rowptr, pad)), None)
+        pos = local.detach().requires_grad_(True)
+        batch = torch.zeros(n_local, dtype=torch.long, device=self.device)
+        cell = torch.diag(self.box_f).unsqueeze(0)
+
+        def callback(layer, h_owned):
+            if layer == len(self.model.interactions) - 1:
+                return h_owned
+            return torch.cat((h_owned, D.exchange(h_owned, plan)), 0)
+
+        with torch.enable_grad():
+            atomic = self.model(pos, self.z.index_select(0, ids), batch, src, dst, shifts, cell,
+                                local_atom_count=n_owned, layer_state_callback=callback, topology=topo)
+            energy = atomic[:n_owned].sum()
+            (grad,) = torch.autograd.grad(energy, pos)
+        total = torch.zeros_like(self.pos)
+        total.index_add_(0, ids, grad)
+        e = energy.detach().reshape(1).clone()
+        dist.all_reduce(total)
+        dist.all_reduce(e)
+        self.energy = e[0]
+        self.forces = (-total).contiguous()
+        return self.forces
+
+    # ------------------------------------------------------------------ integration
+    def _kick(self, drift):
+        lib = _lib.load()
+        with _lib.on_device(self.device):
+            _lib.check(lib.ictc_md_kick(self.pos.shape[0], self.dt, self.forces.data_ptr(), self.inv_mass.data_ptr(),
+                                        self.vel.data_ptr(), self.pos.data_ptr(), self.box_f.data_ptr(), int(drift),
+                                        _lib.stream(self.device)), "ictc_md_kick")
+
+    def step(self):
+        """One velocity-Verlet step; neighbours are rebuilt every step."""
+        if self.forces is None:
+            self.compute_forces()
+        self._kick(True)
+        self.compute_forces()
+        self._kick(False)
+
+    def kinetic_energy(self):
+        return 0.5 * float((self.masses.double().unsqueeze(1) * self.vel.double() ** 2).sum()) / ACCEL
+
+    def temperature(self):
+        return 2.0 * self.kinetic_energy() / ((3 * self.pos.shape[0] - 3) * KB_EV)

@@ -279,7 +279,8 @@ class MaceIctcModel(nn.Module):
         total = None
         for layer, (interaction, product) in enumerate(zip(self.interactions, self.products)):
             message, sc = interaction(h, sh, edge_feats, edge_src, edge_dst, mask, species, topology)
-            h = product(message, sc, species)
+            # only owned rows feed the product (ghost rows have no in-edges here)
+            h = product(message[:owned], sc[:owned], species[:owned])
             if layer_state_callback is not None:
                 h = layer_state_callback(layer, h)
             if layer < self.num_interaction - 1:

@@ -126,6 +126,39 @@ int ictc_csr_build_static(const int64_t* keys, int64_t num_nodes, int64_t num_ed
                           int64_t* order, int32_t* sorted_flag, void* stream);
 int ictc_csr_static_limits(int64_t* host_max_nodes, int64_t* host_max_edges);
 
+/* In-place inclusive prefix sum of an int64 device vector (row offsets of variable-length rows).
+ * scratch: ictc_scan_scratch_bytes(n) bytes. */
+int64_t ictc_scan_scratch_bytes(int64_t n);
+int ictc_inclusive_scan_i64(int64_t* data, int64_t n, void* scratch, void* stream);
+
+/* ------------------------------------------------------------------ neighbour list and MD integrator
+ * Full neighbour list of the first num_centres atoms among num_atoms rows of pos [N,3] (fp32):
+ * edge (src = j, dst = i) for every ordered pair with |r_i - r_j + S*box|^2 <= cutoff^2, evaluated in
+ * double precision on the fp32 coordinates (each operation rounded separately), ordered by
+ * (dst, src, S_x, S_y, S_z).  Semantics of the reference's graph fill and canonical edge order:
+ *   lammps_user_mfftorch/src/USER-MFFTORCH/pair_mff_torch_kokkos.cpp:661-871, 897-911.
+ * host_lo/host_hi: bounds of the cell grid (HOST double[3]; all atoms lie inside), host_box: periodic
+ * lengths, host_periodic: int[3] flags; an axis that is not periodic gets no image shifts.
+ * Step 1 ictc_neighbor_count writes per-centre counts to rowptr[1..centres] (rowptr[0] = 0); the caller
+ * turns them into offsets with ictc_inclusive_scan_i64 and sizes the edge buffers from
+ * rowptr[centres].  Step 2 ictc_neighbor_fill (same positions, same scratch, untouched in between)
+ * writes src, dst [E], shifts [E,3] (fp32, lattice units, edge_vec = pos[dst] - pos[src] + shifts*box)
+ * and uses edge_keys [E] as work space.  Rows that would exceed `capacity` edges are skipped.
+ * scratch: ictc_neighbor_scratch_bytes() bytes. */
+int64_t ictc_neighbor_scratch_bytes(int64_t num_atoms, const double* host_lo, const double* host_hi, double cutoff);
+int ictc_neighbor_count(const float* pos, int64_t num_atoms, int64_t num_centres, const double* host_lo,
+                        const double* host_hi, const double* host_box, const int* host_periodic, double cutoff,
+                        int64_t* rowptr, void* scratch, void* stream);
+int ictc_neighbor_fill(const float* pos, int64_t num_atoms, int64_t num_centres, const double* host_lo,
+                       const double* host_hi, const double* host_box, const int* host_periodic, double cutoff,
+                       const int64_t* rowptr, int64_t capacity, int64_t* src, int64_t* dst, float* shifts,
+                       int64_t* edge_keys, void* scratch, void* stream);
+/* Half step of velocity Verlet: vel += dt/2 * F/m (A, fs, eV, amu); with drift != 0 also
+ * pos += dt * vel, wrapped into [0, box) on axes with box > 0.  The reference leaves integration to
+ * LAMMPS `fix nve` (examples/in.hco); this is the stand-alone equivalent. */
+int ictc_md_kick(int64_t num_atoms, float dt, const float* force, const float* inv_mass, float* vel, float* pos,
+                 const float* box, int drift, void* stream);
+
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).
  * Replaces the harmonics<MODE> kernel run(n,g,h,y,dn,dg,mode,needn,needg):

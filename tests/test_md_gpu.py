@@ -1,0 +1,78 @@
+"""Neighbour list (bit-exact), MD integrator and the MD force path on one GPU."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ictc_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    yield
+    from ictc_o3 import _lib
+    assert _lib.kernel_status() == 0
+
+
+@pytest.mark.parametrize("n,box,periodic,centres,seed", [
+    (300, (14.0, 15.0, 16.0), (1, 1, 1), 300, 0),      # 3 cells per axis
+    (120, (9.5, 10.0, 4.6), (1, 1, 1), 120, 1),        # 2 and 1 cells per axis: same cell, several images
+    (200, (12.0, 13.0, 11.0), (0, 0, 0), 150, 2),      # open boundaries, centres = first 150 rows
+    (180, (10.0, 20.0, 10.0), (1, 0, 1), 180, 3),      # mixed
+    (1, (10.0, 10.0, 10.0), (1, 1, 1), 1, 4), (5, (10.0, 10.0, 10.0), (1, 1, 1), 0, 5)])
+def test_neighbor_list_bit_exact(n, box, periodic, centres, seed):
+    from mace_ictc.md import neighbor_list
+    rng = np.random.default_rng(seed)
+    pos = (rng.random((n, 3)) * np.array(box)).astype(np.float32)
+    cutoff = 4.5
+    rs, rd, rsh = O.neighbor_list_bruteforce(pos, centres, box, periodic, cutoff)
+    src, dst, shifts, rowptr = neighbor_list(torch.as_tensor(pos).cuda(), centres, [0, 0, 0], box, box, periodic, cutoff)
+    assert src.numel() == rs.shape[0]
+    assert torch.equal(src.cpu(), torch.as_tensor(rs))
+    assert torch.equal(dst.cpu(), torch.as_tensor(rd))
+    assert torch.equal(shifts.cpu().long(), torch.as_tensor(rsh))
+    assert torch.equal(rowptr.cpu(), torch.as_tensor(np.concatenate([[0], np.cumsum(np.bincount(rd, minlength=centres))])))
+
+
+def test_neighbor_list_matches_host_builder_on_config_sized_system():
+    """32,768-atom jittered lattice (BASELINE configuration 4): same edges as the host k-d tree builder."""
+    from mace_ictc import synthetic as S
+    from mace_ictc.md import neighbor_list
+    pos, box, _species = S.jittered_lattice(32, 32, 32, 2.15, 0.1, 0)
+    hs, hd, hsh = S.neighbor_list_host(pos, box, 4.5)
+    src, dst, shifts, _ = neighbor_list(torch.as_tensor(pos).cuda(), pos.shape[0], [0, 0, 0], box, box, (1, 1, 1), 4.5)
+    assert torch.equal(src.cpu(), torch.as_tensor(hs)) and torch.equal(dst.cpu(), torch.as_tensor(hd))
+    assert torch.equal(shifts.cpu().long(), torch.as_tensor(hsh))
+    assert 30.0 < src.numel() / pos.shape[0] < 36.0
+
+
+def test_md_forces_match_public_api_and_energy_is_conserved():
+    from mace_ictc import synthetic as S
+    from mace_ictc.hp import create_model, energy_and_forces
+    from mace_ictc.md import MolecularDynamics
+    torch.manual_seed(1)
+    pos, box, species = S.jittered_lattice(8, 8, 8, 2.15, 0.1, 3)
+    z = np.array([1, 6, 8])[species]
+    model = create_model(channels=32, lmax=2, cutoff=4.5, avg_num_neighbors=32.0)
+    md = MolecularDynamics(model, pos, z, box, dt=0.5, temperature=300.0, seed=7)
+    f = md.compute_forces().clone()
+    hs, hd, hsh = S.neighbor_list_host(pos, box, 4.5)
+    n = pos.shape[0]
+    dev = "cuda"
+    model.preserve_edge_order = False
+    ref = energy_and_forces(model, torch.as_tensor(pos).to(dev), torch.as_tensor(z).to(dev),
+                            torch.zeros(n, dtype=torch.long, device=dev), torch.as_tensor(hs).to(dev),
+                            torch.as_tensor(hd).to(dev), torch.as_tensor(hsh).to(dev),
+                            torch.as_tensor(np.diag(box)).float().unsqueeze(0).to(dev))
+    model.preserve_edge_order = True
+    assert float((f - ref["forces"]).abs().max()) < 1e-5 * float(ref["forces"].abs().max())
+    assert abs(float(md.energy) - float(ref["energy"])) < 1e-5 * abs(float(ref["energy"]))
+    assert abs(md.temperature() - 300.0) < 1e-3
+    e0 = float(md.energy) + md.kinetic_energy()
+    for _ in range(20):
+        md.step()
+    e1 = float(md.energy) + md.kinetic_energy()
+    ke = md.kinetic_energy()
+    assert abs(e1 - e0) < 2e-3 * ke, (e0, e1, ke)      # NVE: total energy drift far below the kinetic energy
+    assert float(md.pos.min()) >= 0.0 and bool((md.pos < md.box_f).all())
