@@ -3,6 +3,13 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload fused_message]
 
+Workload ``md`` (default; BASELINE configuration 5, weak-scaling series): NVE molecular dynamics of the
+C64 / lmax 2 / 2-interaction / correlation-3 random-init model on a jittered simple-cubic H/C/O lattice
+(spacing 2.15 A, sigma 0.1 A, 1:2:1), 131,072 atoms per GPU (64x64x32 sites per brick; 8 GPUs = the
+1,048,576-atom box), cutoff 4.5 A, 1 fs velocity-Verlet steps from a 300 K Maxwell-Boltzmann start.  A
+"step" is one full MD step: neighbour rebuild, energy, forces (autograd through the kernels), halo
+exchange when N > 1, integration.  Metric: atom-steps per second over all GPUs.
+
 Workload ``fused_message`` (BASELINE configuration 2): fused edge tensor product + receiver
 scatter-sum, forward and first adjoint (dx, dsh, dg), fp32, C=64, lmax 2, 65,536 atoms at uniform
 random positions in a periodic cube of density 0.1 / A^3, cutoff 4.5 A (about 38 neighbours per
@@ -10,8 +17,9 @@ atom, ~2.5 M directed edges sorted by receiver), node features ~ N(0,1), gates f
 radial MLP 8 -> 64 -> 64 -> 64 -> 704 over an 8-function Bessel basis.  A "step" is one forward plus
 one adjoint over the whole edge list; the metric is directed edges processed per second.
 
-One JSON line is printed by rank 0.  With N > 1 (torchrun) every rank processes its own independent
-system of the same size (no data-path collective; weak scaling).
+One JSON line is printed by rank 0.  With N > 1 (torchrun) the MD box is split into N bricks (spatial
+domain decomposition, NCCL halo exchange); the fused_message workload gives every rank its own
+independent system (no data-path collective).  Both are weak scaling.
 """
 from __future__ import annotations
 
@@ -160,6 +168,207 @@ def run_cpu(seed, steps, warmup, sample_atoms):
             "ms_per_step": dt * 1e3}
 
 
+
+# ------------------------------------------------------------------------------------ MD workload
+MD_BRICK = (64, 64, 32)          # lattice sites per GPU
+MD_SPACING, MD_SIGMA, MD_CUTOFF, MD_DT, MD_T = 2.15, 0.1, 4.5, 1.0, 300.0
+
+
+def md_lattice_dims(world):
+    from mace_ictc.domain import brick_grid
+    dims = list(MD_BRICK)
+    n = world
+    while n > 1:                      # double the currently shortest box edge, so bricks stay 64x64x32
+        axis = min(range(3), key=lambda a: dims[a])
+        dims[axis] *= 2
+        n //= 2
+    return tuple(dims)
+
+
+def md_cpu_step_factory(side):
+    """The oracle model (fp32, all host threads): energy and forces of a side^3-atom periodic sample of
+    the same lattice, neighbour list included."""
+    from mace_ictc import synthetic as S
+    from mace_ictc.model import MaceIctcModel
+    from oracle.model_oracle import ModelOracle
+    torch.manual_seed(0)
+    pos, box, species = S.jittered_lattice(side, side, side, MD_SPACING, MD_SIGMA, 0)
+    z = torch.as_tensor(np.array([1, 6, 8])[species])
+    weights = MaceIctcModel(channels=CHANNELS, cutoff=MD_CUTOFF, avg_num_neighbors=32.0).state_dict()
+    oracle = ModelOracle(weights, channels=CHANNELS, lmax=2, num_interactions=2, correlation=3,
+                         atomic_numbers=(1, 6, 8), cutoff=MD_CUTOFF, avg_num_neighbors=32.0, dtype=torch.float32)
+    p = torch.as_tensor(pos)
+    batch = torch.zeros(p.shape[0], dtype=torch.long)
+    cell = torch.as_tensor(np.diag(box)).float().unsqueeze(0)
+
+    def step():
+        src, dst, shifts = S.neighbor_list_host(pos, box, MD_CUTOFF)
+        oracle.energy_and_forces(p, z, batch, torch.as_tensor(src), torch.as_tensor(dst), torch.as_tensor(shifts), cell)
+        return p.shape[0]
+
+    return step, p.shape[0]
+
+
+def run_cpu_md(steps, warmup, side):
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    step, atoms = md_cpu_step_factory(side)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": atoms / dt, "unit": "atom-steps/s", "cores": threads, "kind": "port",
+            "sample": f"{atoms}-atom periodic sample ({side}^3 sites) of the same lattice and model, fp32 torch CPU, "
+                      f"neighbour list + energy + forces per step, {steps} timed steps",
+            "ms_per_step": dt * 1e3}
+
+
+def main_md(args, rank, world, local):
+    dims = md_lattice_dims(world)
+    atoms_total = dims[0] * dims[1] * dims[2]
+    workload = {"workload": f"md: NVE velocity-Verlet, C{CHANNELS}/lmax2/2 interactions/corr3 random-init, jittered "
+                            f"H/C/O lattice {dims[0]}x{dims[1]}x{dims[2]} = {atoms_total} atoms "
+                            f"({MD_BRICK[0] * MD_BRICK[1] * MD_BRICK[2]} per GPU), cutoff {MD_CUTOFF} A, dt {MD_DT} fs, "
+                            f"{MD_T} K, neighbours rebuilt every step",
+                "l2": "edge tensors (gates 12 GB per layer) are larger than L2", "atoms_per_gpu": atoms_total // world}
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps, warmup = max(1, min(args.steps, 3)), 1
+        res = run_cpu_md(steps, warmup, args.cpu_md_side)
+        line = {"impl": "reference", "metric": "MD atom-steps/s", "value": res["value"], "unit": "atom-steps/s",
+                "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": res["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": workload, "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": res["value"], "unit": "atom-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    from ictc_o3 import _lib
+    from ictc_o3.ops import tensor_product as tpmod
+    from mace_ictc import synthetic as S
+    from mace_ictc.hp import create_model
+    from mace_ictc.md import MolecularDynamics
+    torch.manual_seed(0)
+    pos, box, species = S.jittered_lattice(*dims, MD_SPACING, MD_SIGMA, 0)
+    z = np.array([1, 6, 8])[species]
+    model = create_model(channels=CHANNELS, lmax=2, num_interactions=2, correlation=3, cutoff=MD_CUTOFF,
+                         atomic_numbers=(1, 6, 8), avg_num_neighbors=32.0, device=dev)
+    if world > 1:
+        for p in model.parameters():
+            dist.broadcast(p.data, 0)
+    md = MolecularDynamics(model, pos, z, box, dt=MD_DT, temperature=MD_T, seed=1, distributed=world > 1)
+    warm = max(3, args.warmup)
+    for _ in range(warm):
+        md.step()
+    sampler = ClockSampler(local)
+    tpmod.PROFILE = []
+    calls0 = _lib.CALLS
+    barrier()
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        md.step()
+    stop.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = start.elapsed_time(stop) / args.steps
+    calls = _lib.CALLS - calls0
+    profile, tpmod.PROFILE = tpmod.PROFILE, None
+    kern = {}
+    for name, a, b in profile:
+        kern.setdefault(name, []).append(a.elapsed_time(b))
+    # per step there are two graph forwards / adjoints (layer 0 and layer 1): report the slower (layer 1)
+    kern_ms = {k: float(np.max(np.array(v).reshape(args.steps, -1).mean(0))) for k, v in kern.items()}
+    edges = md.num_edges
+
+    # end to end: positions arrive from the host every step, forces and energy go back to the host
+    e2e = None
+    if not args.no_e2e:
+        n = md.pos.shape[0]
+        host_pos = torch.empty(n, 3, pin_memory=True).copy_(md.pos)
+        host_f = torch.empty(n, 3, pin_memory=True)
+        host_e = torch.empty(1, pin_memory=True)
+
+        def e2e_step():
+            md.pos.copy_(host_pos, non_blocking=True)
+            md.compute_forces()
+            host_f.copy_(md.forces, non_blocking=True)
+            host_e.copy_(md.energy.reshape(1), non_blocking=True)
+            md._kick(True)
+            md._kick(False)
+            host_pos.copy_(md.pos, non_blocking=True)
+
+        e2e_steps = max(1, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        s2, t2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        t2.record()
+        barrier()
+        e2e = [s2.elapsed_time(t2) / e2e_steps, n * 12, n * 12 + 4 + n * 12, e2e_steps]
+    status = _lib.kernel_status()
+    if world > 1:
+        t = torch.tensor([ms, e2e[0] if e2e else 0.0, float(edges)], device=dev, dtype=torch.float64)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t)
+        ms = float(tmax[0])
+        if e2e:
+            e2e[0] = float(tmax[1])
+        total_edges = float(t[2])
+    else:
+        total_edges = float(edges)
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        else:
+            peak, peak_src = 6650.0, "fallback"
+        n_local = atoms_total // world
+        _fwd_b, bwd_b = algorithmic_bytes(n_local, edges)
+        adj_ms = kern_ms.get("graph_adjoint")
+        achieved = bwd_b / (adj_ms * 1e-3) / 1e9 if adj_ms else None
+        line = {"metric": "MD atom-steps/s", "value": atoms_total / (ms * 1e-3), "unit": "atom-steps/s",
+                "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": dict(workload, edges_total=total_edges, edges_per_atom=total_edges / atoms_total),
+                "gpu_launches": calls, "kernel_status": status, "clocks": clocks,
+                "kernels_ms": kern_ms,
+                "roofline": {"bound": "hbm", "kernel": "tp_adjoint_tma_kernel (layer-1 graph adjoint: dx, dsh, dg)",
+                             "achieved": achieved, "peak": peak, "unit": "GB/s",
+                             "frac": achieved / peak if achieved else None, "peak_source": peak_src,
+                             "algorithmic_bytes_per_launch": bwd_b, "traffic": None},
+                "e2e": ({"value": atoms_total / (e2e[0] * 1e-3), "unit": "atom-steps/s", "h2d_bytes_per_step": e2e[1],
+                         "d2h_bytes_per_step": e2e[2], "ms_per_step": e2e[0], "steps": e2e[3]} if e2e else None)}
+        if world == 1 and not args.no_cpu_baseline:
+            res = run_cpu_md(2, 1, args.cpu_md_side)
+            line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------------------------ GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -167,7 +376,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="fused_message")
+    ap.add_argument("--workload", default="md", choices=["md", "fused_message"])
+    ap.add_argument("--cpu-md-side", type=int, default=12)
     ap.add_argument("--atoms", type=int, default=NUM_ATOMS)
     ap.add_argument("--cpu-sample-atoms", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -176,6 +386,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload == "md":
+        return main_md(args, rank, world, local)
     workload = {"workload": f"fused_message: TP+scatter forward+adjoint, fp32, C{CHANNELS}, lmax {LMAX}, "
                             f"{args.atoms} atoms/GPU uniform density {DENSITY}, cutoff {CUTOFF}",
                 "l2": "inputs larger than L2 (gates alone are 7 GB)", "atoms_per_gpu": args.atoms}

@@ -72,7 +72,13 @@ def last_error() -> str:
     return load().ictc_last_error().decode()
 
 
+# number of successful C-ABI calls that launch kernels (each call launches one or more kernels)
+CALLS = 0
+
+
 def check(rc: int, what: str):
+    global CALLS
+    CALLS += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}: {last_error()}")
 
