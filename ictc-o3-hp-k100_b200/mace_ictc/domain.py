@@ -82,35 +82,19 @@ def decompose(pos: torch.Tensor, box: torch.Tensor, grid, rank: int, cutoff: flo
     starts = torch.cumsum(counts, 0) - counts
     owner_row = torch.empty_like(owner)
     owner_row[order] = torch.arange(owner.numel(), device=dev) - starts[owner[order]]
-    ids, shifts = [], []
+    # per axis, which of the three images (shift -1, 0, +1) of an atom falls inside the halo-extended brick
     p64 = pos.to(torch.float64)
     lo_d, hi_d, box_d = lo.to(dev), hi.to(dev), box.to(torch.float64).to(dev)
-    for sx in (-1, 0, 1):
-        for sy in (-1, 0, 1):
-            for sz in (-1, 0, 1):
-                s = torch.tensor([sx, sy, sz], dtype=torch.float64, device=dev)
-                # an image can only reach the halo if the shifted box overlaps it
-                reach = True
-                for a, sa in enumerate((sx, sy, sz)):
-                    if sa == -1 and float(lo[a]) - cutoff >= 0.0:
-                        reach = False
-                    if sa == 1 and float(hi[a]) + cutoff <= float(box[a]):
-                        reach = False
-                if not reach:
-                    continue
-                q = p64 + s * box_d
-                inside = ((q >= lo_d - cutoff) & (q < hi_d + cutoff)).all(1)
-                if sx == 0 and sy == 0 and sz == 0:
-                    inside &= owner != rank
-                sel = torch.nonzero(inside).flatten()
-                if sel.numel():
-                    ids.append(sel)
-                    shifts.append(s.to(torch.float32).expand(sel.numel(), 3))
-    if ids:
-        ghost_ids, ghost_shift = torch.cat(ids), torch.cat(shifts)
-    else:
-        ghost_ids = torch.empty(0, dtype=torch.long, device=dev)
-        ghost_shift = torch.empty(0, 3, device=dev)
+    shifts3 = torch.tensor([-1.0, 0.0, 1.0], dtype=torch.float64, device=dev)
+    q = p64.unsqueeze(-1) + shifts3 * box_d.view(1, 3, 1)                       # [N, axis, image]
+    inside = (q >= (lo_d - cutoff).view(1, 3, 1)) & (q < (hi_d + cutoff).view(1, 3, 1))
+    codes = torch.arange(27, device=dev)
+    sx, sy, sz = codes // 9, (codes // 3) % 3, codes % 3                        # image index per axis
+    valid = inside[:, 0, :][:, sx] & inside[:, 1, :][:, sy] & inside[:, 2, :][:, sz]   # [N, 27]
+    valid[:, 13] &= owner != rank                                               # zero shift: ghosts only
+    pairs = torch.nonzero(valid.t())                                            # sorted by (image code, atom id)
+    code, ghost_ids = pairs[:, 0], pairs[:, 1].contiguous()
+    ghost_shift = torch.stack((code // 9 - 1, (code // 3) % 3 - 1, code % 3 - 1), 1).to(torch.float32)
     return LocalDomain(owned, ghost_ids, ghost_shift, lo, hi, owner, owner_row)
 
 

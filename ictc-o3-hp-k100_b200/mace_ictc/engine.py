@@ -1,0 +1,263 @@
+"""Force engine: energy and position gradient of the MACE-ICTC model by an explicit forward and reverse
+sweep over the B200 kernels, without the autograd tape.
+
+Same arithmetic as ``MaceIctcModel.forward`` followed by ``autograd.grad(E, pos)``
+(reference: mace_ictc/hp/runtime.py:82-111 over mace_ictc/models/mace/backbone.py:860-1246), specialised to
+what an MD step needs: frozen weights, gradient with respect to positions only.  Every adjoint below is
+the hand-written reverse of the line that produced the value; tests compare it with the autograd path.
+Node features live in ir_mul rows ([rows, 9C], degree blocks [2l+1, C]) from end to end, so channel
+linears are plain GEMMs over contiguous rows and no mul_ir <-> ir_mul conversion is made.
+Dense layers are fp32 library GEMMs (``torch.mm``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from ictc_o3 import _lib
+from ictc_o3.ops.topology import build_csr
+from ictc_o3.symmetric_contraction import _ScCall
+from . import domain as D
+from .model import SILU_SCALE, MaceIctcModel
+
+
+def _blocks(flat, c):
+    """Views of the three degree blocks of ir_mul rows [rows, 9C] as [rows, m, C]."""
+    rows = flat.shape[0]
+    return [flat[:, 0:c].reshape(rows, 1, c), flat[:, c:4 * c].reshape(rows, 3, c),
+            flat[:, 4 * c:9 * c].reshape(rows, 5, c)]
+
+
+class ForceEngine:
+    def __init__(self, model: MaceIctcModel):
+        if len(model.interactions) != 2:
+            raise ValueError("the force engine covers the two-interaction model")
+        self.model = model
+        self.c = model.channels
+        self.dev = next(model.parameters()).device
+        self.lib = _lib.load()
+        self._versions = None
+        self._spec = {0: _lib.tp_spec(0, 2, 2), 1: _lib.tp_spec(2, 2, 2)}
+        self.refresh()
+
+    # ---------------------------------------------------------------- weights
+    def refresh(self):
+        """(Re)build the GEMM-ready weight views when a parameter changed."""
+        versions = tuple(p._version for p in self.model.parameters())
+        if versions == self._versions:
+            return
+        m, c = self.model, self.c
+        with torch.no_grad():
+            self.emb = m.node_embedding.weight.t().contiguous()                         # [S, C]
+            self.layers = []
+            for k, (inter, prod) in enumerate(zip(m.interactions, m.products)):
+                lin = inter.input_lmax
+                L = {
+                    "up_t": [inter.linear_up.adapters[str(l)].weight.t().contiguous() for l in range(lin + 1)],
+                    "up": [inter.linear_up.adapters[str(l)].weight.contiguous() for l in range(lin + 1)],
+                    "fc": [mod.weight.contiguous() for mod in inter.fc if isinstance(mod, torch.nn.Linear)],
+                    "fc_t": [mod.weight.t().contiguous() for mod in inter.fc if isinstance(mod, torch.nn.Linear)],
+                    "ml": [(inter.message_linear.weights[str(l)] / max(inter.avg_num_neighbors, 1e-8)).contiguous()
+                           for l in range(3)],
+                    "counts": [inter.tp.path_counts_by_l[l] for l in range(3)],
+                    "tpw": None if bool(torch.all(inter.tp.weight == 1)) else inter.tp.weight.contiguous(),
+                }
+                L["ml_t"] = [w.t().contiguous() for w in L["ml"]]
+                wsc = inter.self_connection.weights["0"]                                 # [S, C(out), C(in)]
+                s = wsc.shape[0]
+                L["sc_fwd"] = wsc.permute(2, 0, 1).reshape(c, s * c).contiguous()          # x @ -> [n, S*C(out)]
+                L["sc_bwd"] = wsc.permute(1, 0, 2).reshape(c, s * c).contiguous()          # dout @ -> [n, S*C(in)]
+                L["bank"] = prod.symmetric_contractions.weight_bank()
+                L["target"] = prod.target_lmax
+                L["pl"] = [(prod.linear[str(l)] / math.sqrt(c)).contiguous() for l in range(prod.target_lmax + 1)]
+                L["pl_t"] = [w.t().contiguous() for w in L["pl"]]
+                self.layers.append(L)
+            self.ro0 = m.layer_energy_readouts[0].readout.weight.reshape(-1).contiguous()  # [C]
+            self.ro1_w1 = m.last_layer_energy_readout.linear_1.weight.contiguous()          # [16, C]
+            self.ro1_w2 = m.last_layer_energy_readout.linear_2.weight.reshape(-1).contiguous()  # [16]
+        self._versions = versions
+
+    # ---------------------------------------------------------------- small launch helpers
+    def _st(self):
+        return _lib.stream(self.dev)
+
+    def _silu(self, x):
+        y = torch.empty_like(x)
+        _lib.check(self.lib.ictc_silu_forward(x.numel(), SILU_SCALE, x.data_ptr(), y.data_ptr(), self._st()), "silu")
+        return y
+
+    def _silu_bwd(self, x, dy):
+        dx = torch.empty_like(x)
+        _lib.check(self.lib.ictc_silu_backward(x.numel(), SILU_SCALE, x.data_ptr(), dy.data_ptr(), dx.data_ptr(),
+                                               self._st()), "silu_backward")
+        return dx
+
+    def _mlp(self, rb, L):
+        """Radial MLP: returns gates and the pre-activations needed by the reverse sweep."""
+        pre, h = [], rb
+        for k, wt in enumerate(L["fc_t"]):
+            z = torch.mm(h, wt)
+            if k + 1 < len(L["fc_t"]):
+                pre.append(z)
+                h = self._silu(z)
+            else:
+                return z, pre
+
+    def _mlp_bwd(self, dgates, pre, L):
+        d = torch.mm(dgates, L["fc"][-1])
+        for k in range(len(pre) - 1, -1, -1):
+            d = self._silu_bwd(pre[k], d)
+            d = torch.mm(d, L["fc"][k])
+        return d                                                            # [E, num_basis]
+
+    def _species_linear(self, x, species, w, s):
+        full = torch.mm(x, w).view(x.shape[0], s, self.c)
+        return full.gather(1, species.view(-1, 1, 1).expand(-1, 1, self.c)).squeeze(1)
+
+    def _tp_forward(self, layer, x, sh, g, src, rowptr, rows, e, tpw):
+        c = self.c
+        out = torch.empty(rows, (9 if layer == 0 else 35) * c, dtype=torch.float32, device=self.dev)
+        _lib.check(self.lib.ictc_tp_graph_forward(self._spec[layer], c, rows, e, x.data_ptr(), sh.data_ptr(),
+                                                  _lib.ptr(tpw), g.data_ptr(), src.data_ptr(), rowptr.data_ptr(),
+                                                  None, None, out.data_ptr(), self._st()), "tp_graph_forward")
+        return out
+
+    def _tp_adjoint(self, layer, x, sh, g, dst, src_csr, v, n_rows, e, tpw, need_x):
+        c = self.c
+        dx = torch.empty_like(x) if need_x else None
+        dsh = torch.empty_like(sh)
+        dg = torch.empty_like(g)
+        rowptr, order = src_csr
+        _lib.check(self.lib.ictc_tp_graph_adjoint(self._spec[layer], c, n_rows, e, x.data_ptr(), sh.data_ptr(),
+                                                  _lib.ptr(tpw), g.data_ptr(), dst.data_ptr(), rowptr.data_ptr(),
+                                                  _lib.ptr(order), None, v.data_ptr(), _lib.ptr(dx), dsh.data_ptr(),
+                                                  dg.data_ptr(), self._st()), "tp_graph_adjoint")
+        return dx, dsh, dg
+
+    def _transpose(self, rows, count, m, in_t, in_off, in_stride, out_t, out_off, out_stride, to_gemm):
+        _lib.check(self.lib.ictc_slot_transpose(rows, count, m, self.c, in_stride, out_stride,
+                                                in_t.data_ptr() + 4 * in_off, out_t.data_ptr() + 4 * out_off,
+                                                int(to_gemm), self._st()), "slot_transpose")
+
+    # ---------------------------------------------------------------- the sweep
+    @torch.no_grad()
+    def energy_and_gradient(self, pos, species, src, dst, shifts, box, n_owned, dst_rowptr, plan=None):
+        """pos [N_local,3] (owned rows first), species [N_local] (index), edges sorted by receiver with all
+        receivers < n_owned, dst_rowptr [n_owned+1].  Returns (energy of owned atoms, dE/dpos [N_local,3],
+        per-atom energies [n_owned])."""
+        self.refresh()
+        m, c, lib, dev = self.model, self.c, self.lib, self.dev
+        n_local, e = pos.shape[0], int(src.numel())
+        st = self._st()
+        L0, L1 = self.layers
+        nb, pcut, rmax = m.number_of_basis, m.polynomial_cutoff_p, m.max_radius
+        with _lib.on_device(dev):
+            # ---- edge geometry
+            sh = torch.empty(e, 9, dtype=torch.float32, device=dev)
+            rb = torch.empty(e, nb, dtype=torch.float32, device=dev)
+            unit = torch.empty(e, 3, dtype=torch.float32, device=dev)
+            length = torch.empty(e, dtype=torch.float32, device=dev)
+            box_c = (C.c_float * 3)(*[float(b) for b in box])
+            _lib.check(lib.ictc_edge_geometry_forward(pos.data_ptr(), _lib.ptr(src), _lib.ptr(dst), _lib.ptr(shifts),
+                                                      box_c, rmax, nb, pcut, e, _lib.ptr(sh), _lib.ptr(rb),
+                                                      _lib.ptr(unit), _lib.ptr(length), st), "edge_geometry_forward")
+            src_csr = build_csr(src, n_local, assume_sorted=False)
+            sp_owned = species[:n_owned]
+            s_count = self.emb.shape[0]
+            # ---- layer 0
+            x0 = self.emb.index_select(0, species)                               # [N_local, C]
+            u0 = torch.mm(x0, L0["up_t"][0])
+            g0, pre0 = self._mlp(rb, L0)
+            M0 = self._tp_forward(0, u0, sh, g0, src, dst_rowptr, n_owned, e, L0["tpw"])   # [n, 9C]
+            m0 = torch.empty_like(M0)
+            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                m0[:, off * c:(off + mm) * c] = torch.mm(M0[:, off * c:(off + mm) * c].reshape(-1, c),
+                                                         L0["ml_t"][l]).view(n_owned, mm * c)
+            sc0 = self._species_linear(x0[:n_owned], sp_owned, L0["sc_fwd"], s_count)
+            call0 = _ScCall(c, 2, s_count, sp_owned, True)
+            y0 = call0.forward(m0, L0["bank"])                                    # [n, 9C]
+            h1 = torch.empty_like(y0)
+            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                h1[:, off * c:(off + mm) * c] = torch.mm(y0[:, off * c:(off + mm) * c].reshape(-1, c),
+                                                         L0["pl"][l]).view(n_owned, mm * c)
+            h1[:, :c] += sc0
+            e0 = torch.mv(h1[:, :c], self.ro0)
+            # ---- halo
+            h1_full = h1 if plan is None else torch.cat((h1, plan.forward(h1)), 0)
+            # ---- layer 1
+            u1 = torch.empty(n_local, 9 * c, dtype=torch.float32, device=dev)
+            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                u1[:, off * c:(off + mm) * c] = torch.mm(h1_full[:, off * c:(off + mm) * c].reshape(-1, c),
+                                                         L1["up_t"][l]).view(n_local, mm * c)
+            g1, pre1 = self._mlp(rb, L1)
+            M1 = self._tp_forward(1, u1, sh, g1, src, dst_rowptr, n_owned, e, L1["tpw"])   # [n, 35C]
+            m1 = torch.empty(n_owned, 9 * c, dtype=torch.float32, device=dev)
+            in_off = 0
+            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                cnt = L1["counts"][l]
+                buf = torch.empty(n_owned * mm, cnt * c, dtype=torch.float32, device=dev)
+                self._transpose(n_owned, cnt, mm, M1, in_off, 35 * c, buf, 0, mm * cnt * c, True)
+                m1[:, off * c:(off + mm) * c] = torch.mm(buf, L1["ml_t"][l]).view(n_owned, mm * c)
+                in_off += cnt * mm * c
+            sc1 = self._species_linear(h1[:, :c].contiguous(), sp_owned, L1["sc_fwd"], s_count)
+            call1 = _ScCall(c, 0, s_count, sp_owned, True)
+            y1 = call1.forward(m1, L1["bank"])                                    # [n, C]
+            h2 = torch.mm(y1, L1["pl"][0]) + sc1
+            z = torch.mm(h2, self.ro1_w1.t())
+            a = self._silu(z)
+            e1 = torch.mv(a, self.ro1_w2)
+            atomic = e0 + e1
+            energy = atomic.sum()
+
+            # ================= reverse sweep (dE = 1 for every owned atom) =================
+            da = self.ro1_w2.unsqueeze(0).expand(n_owned, -1).contiguous()
+            dz = self._silu_bwd(z, da)
+            dh2 = torch.mm(dz, self.ro1_w1)                                        # [n, C]
+            dy1 = torch.mm(dh2, L1["pl_t"][0])
+            dm1, _ = call1.adjoint(m1, L1["bank"], dy1, (True, False))             # [n, 9C]
+            v1 = torch.empty(n_owned, 35 * c, dtype=torch.float32, device=dev)
+            out_off = 0
+            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                cnt = L1["counts"][l]
+                buf = torch.mm(dm1[:, off * c:(off + mm) * c].reshape(-1, c), L1["ml"][l])   # [n*mm, cnt*C]
+                self._transpose(n_owned, cnt, mm, buf, 0, mm * cnt * c, v1, out_off, 35 * c, False)
+                out_off += cnt * mm * c
+            du1, dsh1, dg1 = self._tp_adjoint(1, u1, sh, g1, dst, src_csr, v1, n_local, e, L1["tpw"], True)
+            drb = self._mlp_bwd(dg1, pre1, L1)
+            del dg1, g1, pre1
+            dh1_full = torch.empty(n_local, 9 * c, dtype=torch.float32, device=dev)
+            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                dh1_full[:, off * c:(off + mm) * c] = torch.mm(du1[:, off * c:(off + mm) * c].reshape(-1, c),
+                                                               L1["up"][l]).view(n_local, mm * c)
+            dh1 = dh1_full[:n_owned]
+            if plan is not None:
+                dh1 = dh1 + plan.adjoint(dh1_full[n_owned:].contiguous())
+            else:
+                dh1 = dh1.clone()
+            dsc1 = dh2
+            full = torch.mm(dsc1, L1["sc_bwd"]).view(n_owned, s_count, c)
+            dh1[:, :c] += full.gather(1, sp_owned.view(-1, 1, 1).expand(-1, 1, c)).squeeze(1)
+            dh1[:, :c] += self.ro0
+            dy0 = torch.empty_like(dh1)
+            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                dy0[:, off * c:(off + mm) * c] = torch.mm(dh1[:, off * c:(off + mm) * c].reshape(-1, c),
+                                                          L0["pl_t"][l]).view(n_owned, mm * c)
+            dm0, _ = call0.adjoint(m0, L0["bank"], dy0, (True, False))
+            v0 = torch.empty_like(dm0)
+            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                v0[:, off * c:(off + mm) * c] = torch.mm(dm0[:, off * c:(off + mm) * c].reshape(-1, c),
+                                                         L0["ml"][l]).view(n_owned, mm * c)
+            _, dsh0, dg0 = self._tp_adjoint(0, u0, sh, g0, dst, src_csr, v0, n_local, e, L0["tpw"], False)
+            drb += self._mlp_bwd(dg0, pre0, L0)
+            dsh1 += dsh0
+            dvec = torch.empty(e, 3, dtype=torch.float32, device=dev)
+            _lib.check(lib.ictc_edge_geometry_backward(_lib.ptr(unit), _lib.ptr(length), rmax, nb, pcut, e,
+                                                       _lib.ptr(dsh1), _lib.ptr(drb), _lib.ptr(dvec), st),
+                       "edge_geometry_backward")
+            grad = torch.empty(n_local, 3, dtype=torch.float32, device=dev)
+            _lib.check(lib.ictc_position_gradient(n_local, n_owned, dst_rowptr.data_ptr(), src_csr[0].data_ptr(),
+                                                  _lib.ptr(src_csr[1]), _lib.ptr(dvec), grad.data_ptr(), st),
+                       "position_gradient")
+        return energy, grad, atomic

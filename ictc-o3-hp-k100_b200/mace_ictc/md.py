@@ -81,7 +81,7 @@ class MolecularDynamics:
     """
 
     def __init__(self, model, positions, atomic_numbers, box, *, dt=1.0, temperature=300.0, seed=0,
-                 velocities=None, distributed=False):
+                 velocities=None, distributed=False, use_engine=True):
         self.model = model
         dev = next(model.parameters()).device
         self.device = dev
@@ -106,6 +106,12 @@ class MolecularDynamics:
             self.rank, self.world, self.grid = 0, 1, (1, 1, 1)
         model.preserve_edge_order = True
         model.skip_input_validation = True
+        self.species = model.species_index(self.z)
+        if use_engine:
+            from .engine import ForceEngine
+            self.engine = ForceEngine(model)
+        else:
+            self.engine = None
         self.forces = None
         self.energy = None
         self.num_edges = 0
@@ -122,6 +128,11 @@ class MolecularDynamics:
         box = self.box.tolist()
         src, dst, shifts, rowptr = neighbor_list(self.pos, n, [0, 0, 0], box, box, (1, 1, 1), self.cutoff)
         self.num_edges = int(src.numel())
+        if self.engine is not None:
+            energy, grad, _ = self.engine.energy_and_gradient(self.pos, self.species, src, dst, shifts, box, n, rowptr)
+            self.energy = energy
+            self.forces = (-grad).contiguous()
+            return self.forces
         topo = Topology(src, dst, n, dst_sorted=True)
         topo._by_dst = (rowptr, None)
         pos = self.pos.detach().requires_grad_(True)
@@ -149,6 +160,17 @@ class MolecularDynamics:
         src, dst, shifts, rowptr = neighbor_list(local, n_owned, lo, hi, self.box.tolist(), (0, 0, 0), self.cutoff)
         self.num_edges = int(src.numel())
         n_local = local.shape[0]
+        if self.engine is not None:
+            energy, grad, _ = self.engine.energy_and_gradient(local, self.species.index_select(0, ids), src, dst, None,
+                                                              self.box.tolist(), n_owned, rowptr, plan)
+            total = torch.zeros_like(self.pos)
+            total.index_add_(0, ids, grad)
+            e = energy.reshape(1).clone()
+            dist.all_reduce(total)
+            dist.all_reduce(e)
+            self.energy = e[0]
+            self.forces = (-total).contiguous()
+            return self.forces
         topo = Topology(src, dst, n_local, dst_sorted=True)
         pad = rowptr.new_full((n_local - n_owned,), int(rowptr[-1].item()))
         topo._by_dst = (torch.cat((rowptr, pad)), None)

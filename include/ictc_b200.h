@@ -159,6 +159,34 @@ int ictc_neighbor_fill(const float* pos, int64_t num_atoms, int64_t num_centres,
 int ictc_md_kick(int64_t num_atoms, float dt, const float* force, const float* inv_mass, float* vel, float* pos,
                  const float* box, int drift, void* stream);
 
+/* ------------------------------------------------------------------ fused element-wise ends of the model
+ * Edge geometry: vec = pos[dst] - pos[src] + shifts*box, length, unit vector, direction harmonics
+ * (lmax 2, [E,9]) and the Bessel radial basis with polynomial envelope of order p ([E,num_basis]) in one
+ * pass; the backward pass turns cotangents of the harmonics and of the radial basis into d/dvec.
+ * Replaces the operator chain of mace_ictc/models/mace/backbone.py:941-973 (radial_basis.py:11-92,
+ * ictc_o3/basis/ictd_irreps.py:1153-1208).  host_box: HOST float[3] (ignored when shifts is NULL). */
+int ictc_edge_geometry_forward(const float* pos, const int64_t* src, const int64_t* dst, const float* shifts,
+                               const float* host_box, float r_max, int num_basis, int p, int64_t num_edges,
+                               float* sh, float* rb, float* unit, float* length, void* stream);
+int ictc_edge_geometry_backward(const float* unit, const float* length, float r_max, int num_basis, int p,
+                                int64_t num_edges, const float* dsh, const float* drb, float* dvec, void* stream);
+/* grad[i] = sum_{dst(e)=i} dvec[e] - sum_{src(e)=i} dvec[e] for the first num_rows atoms; edges are sorted
+ * by receiver (dst_rowptr over the first num_dst_rows rows) and grouped by sender through the sender CSR.
+ * Atomic-free replacement of autograd's index_add scatter (the reference's add_forces,
+ * pair_mff_torch_kokkos.cpp:1130-1160). */
+int ictc_position_gradient(int64_t num_rows, int64_t num_dst_rows, const int64_t* dst_rowptr,
+                           const int64_t* src_rowptr, const int64_t* src_order, const float* dvec, float* grad,
+                           void* stream);
+/* y = silu(x)*scale and its first derivative; replaces run(x,g,h,y,z,scale,mode,...) modes 0/1 of
+ * ictc_o3/backends/k100/hip_activation.py:27-38. */
+int ictc_silu_forward(int64_t n, float scale, const float* x, float* y, void* stream);
+int ictc_silu_backward(int64_t n, float scale, const float* x, const float* dy, float* dx, void* stream);
+/* One degree block between the TP output layout [rows][count][m][C] (to_gemm = 1: input) and the
+ * GEMM-ready layout [rows][m][count*C]; strides are row strides in floats.  Replaces copy_layout of
+ * ictc_o3/backends/k100/hip_message_layout.py:27-34 for the message linear. */
+int ictc_slot_transpose(int64_t rows, int count, int m, int channels, int64_t in_stride, int64_t out_stride,
+                        const float* in, float* out, int to_gemm, void* stream);
+
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).
  * Replaces the harmonics<MODE> kernel run(n,g,h,y,dn,dg,mode,needn,needg):
