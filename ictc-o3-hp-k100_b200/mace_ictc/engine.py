@@ -40,6 +40,7 @@ class ForceEngine:
         self.lib = _lib.load()
         self._versions = None
         self._spec = {0: _lib.tp_spec(0, 2, 2), 1: _lib.tp_spec(2, 2, 2)}
+        self.fused_mlp = True
         self.refresh()
 
     # ---------------------------------------------------------------- weights
@@ -65,6 +66,8 @@ class ForceEngine:
                     "tpw": None if bool(torch.all(inter.tp.weight == 1)) else inter.tp.weight.contiguous(),
                 }
                 L["ml_t"] = [w.t().contiguous() for w in L["ml"]]
+                L["w3_split"] = self._split(L["fc"][-1])
+                L["w3t_split"] = self._split(L["fc_t"][-1])
                 wsc = inter.self_connection.weights["0"]                                 # [S, C(out), C(in)]
                 s = wsc.shape[0]
                 L["sc_fwd"] = wsc.permute(2, 0, 1).reshape(c, s * c).contiguous()          # x @ -> [n, S*C(out)]
@@ -78,6 +81,14 @@ class ForceEngine:
             self.ro1_w1 = m.last_layer_energy_readout.linear_1.weight.contiguous()          # [16, C]
             self.ro1_w2 = m.last_layer_energy_readout.linear_2.weight.reshape(-1).contiguous()  # [16]
         self._versions = versions
+
+    def _split(self, w):
+        """{tf32(x), tf32(x - tf32(x))} pairs of a weight matrix for the tensor-core MLP kernels."""
+        out = torch.empty(*w.shape, 2, dtype=torch.float32, device=w.device)
+        with _lib.on_device(w.device):
+            _lib.check(self.lib.ictc_split_tf32(w.numel(), w.data_ptr(), out.data_ptr(), _lib.stream(w.device)),
+                       "split_tf32")
+        return out
 
     # ---------------------------------------------------------------- small launch helpers
     def _st(self):
@@ -94,8 +105,24 @@ class ForceEngine:
                                                self._st()), "silu_backward")
         return dx
 
+    def _fused_mlp_ok(self, L):
+        fc = L["fc"]
+        return (self.fused_mlp and len(fc) == 4 and fc[0].shape[0] == 64 and fc[0].shape[1] <= 8
+                and tuple(fc[1].shape) == (64, 64) and tuple(fc[2].shape) == (64, 64)
+                and fc[3].shape[1] == 64 and fc[3].shape[0] % 64 == 0)
+
     def _mlp(self, rb, L):
         """Radial MLP: returns gates and the pre-activations needed by the reverse sweep."""
+        if self._fused_mlp_ok(L):
+            e, fc = rb.shape[0], L["fc"]
+            nout = fc[3].shape[0]
+            gates = torch.empty(e, nout, dtype=torch.float32, device=self.dev)
+            pre = [torch.empty(e, 64, dtype=torch.float32, device=self.dev) for _ in range(3)]
+            _lib.check(self.lib.ictc_radial_mlp_forward(e, rb.shape[1], nout, _lib.ptr(rb), fc[0].data_ptr(),
+                                                        fc[1].data_ptr(), fc[2].data_ptr(), L["w3_split"].data_ptr(),
+                                                        _lib.ptr(gates), _lib.ptr(pre[0]), _lib.ptr(pre[1]),
+                                                        _lib.ptr(pre[2]), self._st()), "radial_mlp_forward")
+            return gates, pre
         pre, h = [], rb
         for k, wt in enumerate(L["fc_t"]):
             z = torch.mm(h, wt)
@@ -106,6 +133,15 @@ class ForceEngine:
                 return z, pre
 
     def _mlp_bwd(self, dgates, pre, L):
+        if self._fused_mlp_ok(L):
+            e, ft = dgates.shape[0], L["fc_t"]
+            nb = ft[0].shape[0]
+            drb = torch.empty(e, nb, dtype=torch.float32, device=self.dev)
+            _lib.check(self.lib.ictc_radial_mlp_backward(e, nb, dgates.shape[1], _lib.ptr(dgates), ft[0].data_ptr(),
+                                                         ft[1].data_ptr(), ft[2].data_ptr(), L["w3t_split"].data_ptr(),
+                                                         _lib.ptr(pre[0]), _lib.ptr(pre[1]), _lib.ptr(pre[2]),
+                                                         _lib.ptr(drb), self._st()), "radial_mlp_backward")
+            return drb
         d = torch.mm(dgates, L["fc"][-1])
         for k in range(len(pre) - 1, -1, -1):
             d = self._silu_bwd(pre[k], d)

@@ -187,6 +187,25 @@ int ictc_silu_backward(int64_t n, float scale, const float* x, const float* dy, 
 int ictc_slot_transpose(int64_t rows, int count, int m, int channels, int64_t in_stride, int64_t out_stride,
                         const float* in, float* out, int to_gemm, void* stream);
 
+/* Radial gate MLP num_basis -> 64 -> 64 -> 64 -> num_out (bias-free, SiLU*1.6791767923989418 between
+ * layers) on the tensor cores with error-compensated TF32 splitting (fp32-level accuracy).
+ * Replaces the per-layer F.linear chain of the interaction block's `fc`
+ * (mace_ictc/models/mace/layers.py:825-835; ictc_o3/ops/streamed_gate_message.py:112-116).
+ * forward : rb [E,num_basis], w0 [64,num_basis], w1,w2 [64,64], w3_split [num_out,64] pairs -> gates
+ *           [E,num_out]; z1,z2,z3 [E,64] receive the hidden pre-activations when not NULL.
+ * backward: drb [E,num_basis] = (d gates / d rb)^T dgates, from the stored z1..z3 and the TRANSPOSED
+ *           weights w0t [num_basis,64], w1t, w2t [64,64], w3t_split [64,num_out] pairs.
+ * The wide last-layer matrix is passed pre-split by ictc_split_tf32 (dst_pairs holds 2*n floats:
+ * {tf32(x), tf32(x - tf32(x))} per element), so the kernels stage it with plain asynchronous copies.
+ * Limits: 1 <= num_basis <= 8, num_out a multiple of 64, hidden width 64. */
+int ictc_split_tf32(int64_t n, const float* src, float* dst_pairs, void* stream);
+int ictc_radial_mlp_forward(int64_t num_edges, int num_basis, int num_out, const float* rb, const float* w0,
+                            const float* w1, const float* w2, const float* w3_split, float* gates, float* z1,
+                            float* z2, float* z3, void* stream);
+int ictc_radial_mlp_backward(int64_t num_edges, int num_basis, int num_out, const float* dgates, const float* w0t,
+                             const float* w1t, const float* w2t, const float* w3t_split, const float* z1,
+                             const float* z2, const float* z3, float* drb, void* stream);
+
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).
  * Replaces the harmonics<MODE> kernel run(n,g,h,y,dn,dg,mode,needn,needg):
