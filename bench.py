@@ -78,32 +78,47 @@ def make_inputs(seed, device, num_atoms=NUM_ATOMS, dtype=torch.float32):
 
 
 # ------------------------------------------------------------------------------------ clocks
-class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+_SAMPLER_CODE = r"""
+import sys, time
+import pynvml as N
+N.nvmlInit()
+h = N.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+mx = N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM)
+bits = {"hw_slowdown": N.nvmlClocksThrottleReasonHwSlowdown, "hw_thermal_slowdown": N.nvmlClocksThrottleReasonHwThermalSlowdown,
+        "sw_thermal_slowdown": N.nvmlClocksThrottleReasonSwThermalSlowdown, "sw_power_cap": N.nvmlClocksThrottleReasonSwPowerCap}
+while True:
+    sm = N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM)
+    r = N.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+    print(sm, mx, ",".join(k for k, b in bits.items() if r & b), flush=True)
+    time.sleep(0.5)
+"""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+class ClockSampler:
+    """Samples the SM clock and the throttle reasons every 500 ms from a separate small process (NVML:
+    two queries per sample, which disturbs kernel launches far less than an nvidia-smi loop)."""
 
     def __init__(self, gpu_index):
-        self.rows, self.proc, self.gpu = [], None, gpu_index
+        self.rows, self.proc = [], None
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        self.gpu = int(visible.split(",")[gpu_index]) if visible and visible.replace(",", "").isdigit() else gpu_index
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_CODE, str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            time.sleep(1.0)      # let the sampler import and initialise before the timed region
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append(line.split())
 
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["sampler unavailable"]}
         time.sleep(0.25)
         self.proc.terminate()
         try:
@@ -111,18 +126,14 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, smax, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for row in self.rows:
-            if len(row) < 9:
-                continue
             try:
-                sm.append(float(row[1]))
-                smax = float(row[2])
-            except ValueError:
+                sm.append(float(row[0]))
+                smax = float(row[1])
+            except (ValueError, IndexError):
                 continue
-            for name, val in zip(names, row[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
+            if len(row) > 2:
+                reasons.update(x for x in row[2].split(",") if x)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
                 "samples": len(sm)}
 
@@ -226,6 +237,9 @@ def run_cpu_md(steps, warmup, side):
 
 
 def main_md(args, rank, world, local):
+    global MD_BRICK
+    if args.md_brick:
+        MD_BRICK = tuple(int(v) for v in args.md_brick.lower().split("x"))
     dims = md_lattice_dims(world)
     atoms_total = dims[0] * dims[1] * dims[2]
     workload = {"workload": f"md: NVE velocity-Verlet, C{CHANNELS}/lmax2/2 interactions/corr3 random-init, jittered "
@@ -277,11 +291,11 @@ def main_md(args, rank, world, local):
     for _ in range(warm):
         md.step()
     sampler = ClockSampler(local)
-    tpmod.PROFILE = []
+    md.engine.profile = []
     calls0 = _lib.CALLS
-    barrier()
     if rank == 0:
         sampler.start()
+    barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
@@ -291,12 +305,11 @@ def main_md(args, rank, world, local):
     clocks = sampler.stop() if rank == 0 else None
     ms = start.elapsed_time(stop) / args.steps
     calls = _lib.CALLS - calls0
-    profile, tpmod.PROFILE = tpmod.PROFILE, None
+    profile, md.engine.profile = md.engine.profile, None
     kern = {}
     for name, a, b in profile:
         kern.setdefault(name, []).append(a.elapsed_time(b))
-    # per step there are two graph forwards / adjoints (layer 0 and layer 1): report the slower (layer 1)
-    kern_ms = {k: float(np.max(np.array(v).reshape(args.steps, -1).mean(0))) for k, v in kern.items()}
+    kern_ms = {k: float(np.mean(v)) for k, v in kern.items()}
     edges = md.num_edges
 
     # end to end: positions arrive from the host every step, forces and energy go back to the host
@@ -347,7 +360,7 @@ def main_md(args, rank, world, local):
             peak, peak_src = 6650.0, "fallback"
         n_local = atoms_total // world
         _fwd_b, bwd_b = algorithmic_bytes(n_local, edges)
-        adj_ms = kern_ms.get("graph_adjoint")
+        adj_ms = kern_ms.get("graph_adjoint_l1")
         achieved = bwd_b / (adj_ms * 1e-3) / 1e9 if adj_ms else None
         line = {"metric": "MD atom-steps/s", "value": atoms_total / (ms * 1e-3), "unit": "atom-steps/s",
                 "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
@@ -378,6 +391,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="md", choices=["md", "fused_message"])
     ap.add_argument("--cpu-md-side", type=int, default=12)
+    ap.add_argument("--md-brick", default=None, help="lattice sites per GPU as XxYxZ (profiling of small cases)")
     ap.add_argument("--atoms", type=int, default=NUM_ATOMS)
     ap.add_argument("--cpu-sample-atoms", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")

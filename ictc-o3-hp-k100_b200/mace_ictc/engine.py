@@ -41,6 +41,7 @@ class ForceEngine:
         self._versions = None
         self._spec = {0: _lib.tp_spec(0, 2, 2), 1: _lib.tp_spec(2, 2, 2)}
         self.fused_mlp = True
+        self.profile = None      # list of (kernel name, start event, end event) when enabled by a benchmark
         self.refresh()
 
     # ---------------------------------------------------------------- weights
@@ -118,10 +119,12 @@ class ForceEngine:
             nout = fc[3].shape[0]
             gates = torch.empty(e, nout, dtype=torch.float32, device=self.dev)
             pre = [torch.empty(e, 64, dtype=torch.float32, device=self.dev) for _ in range(3)]
+            t0 = self._mark()
             _lib.check(self.lib.ictc_radial_mlp_forward(e, rb.shape[1], nout, _lib.ptr(rb), fc[0].data_ptr(),
                                                         fc[1].data_ptr(), fc[2].data_ptr(), L["w3_split"].data_ptr(),
                                                         _lib.ptr(gates), _lib.ptr(pre[0]), _lib.ptr(pre[1]),
                                                         _lib.ptr(pre[2]), self._st()), "radial_mlp_forward")
+            self._done(f"radial_mlp_forward_{nout}", t0)
             return gates, pre
         pre, h = [], rb
         for k, wt in enumerate(L["fc_t"]):
@@ -137,10 +140,12 @@ class ForceEngine:
             e, ft = dgates.shape[0], L["fc_t"]
             nb = ft[0].shape[0]
             drb = torch.empty(e, nb, dtype=torch.float32, device=self.dev)
+            t0 = self._mark()
             _lib.check(self.lib.ictc_radial_mlp_backward(e, nb, dgates.shape[1], _lib.ptr(dgates), ft[0].data_ptr(),
                                                          ft[1].data_ptr(), ft[2].data_ptr(), L["w3t_split"].data_ptr(),
                                                          _lib.ptr(pre[0]), _lib.ptr(pre[1]), _lib.ptr(pre[2]),
                                                          _lib.ptr(drb), self._st()), "radial_mlp_backward")
+            self._done(f"radial_mlp_backward_{dgates.shape[1]}", t0)
             return drb
         d = torch.mm(dgates, L["fc"][-1])
         for k in range(len(pre) - 1, -1, -1):
@@ -152,12 +157,25 @@ class ForceEngine:
         full = torch.mm(x, w).view(x.shape[0], s, self.c)
         return full.gather(1, species.view(-1, 1, 1).expand(-1, 1, self.c)).squeeze(1)
 
+    def _mark(self):
+        if self.profile is None:
+            return None
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream(self.dev))
+        return ev
+
+    def _done(self, name, start):
+        if start is not None:
+            self.profile.append((name, start, self._mark()))
+
     def _tp_forward(self, layer, x, sh, g, src, rowptr, rows, e, tpw):
         c = self.c
         out = torch.empty(rows, (9 if layer == 0 else 35) * c, dtype=torch.float32, device=self.dev)
+        t0 = self._mark()
         _lib.check(self.lib.ictc_tp_graph_forward(self._spec[layer], c, rows, e, x.data_ptr(), sh.data_ptr(),
                                                   _lib.ptr(tpw), g.data_ptr(), src.data_ptr(), rowptr.data_ptr(),
                                                   None, None, out.data_ptr(), self._st()), "tp_graph_forward")
+        self._done(f"graph_forward_l{layer}", t0)
         return out
 
     def _tp_adjoint(self, layer, x, sh, g, dst, src_csr, v, n_rows, e, tpw, need_x):
@@ -166,10 +184,12 @@ class ForceEngine:
         dsh = torch.empty_like(sh)
         dg = torch.empty_like(g)
         rowptr, order = src_csr
+        t0 = self._mark()
         _lib.check(self.lib.ictc_tp_graph_adjoint(self._spec[layer], c, n_rows, e, x.data_ptr(), sh.data_ptr(),
                                                   _lib.ptr(tpw), g.data_ptr(), dst.data_ptr(), rowptr.data_ptr(),
                                                   _lib.ptr(order), None, v.data_ptr(), _lib.ptr(dx), dsh.data_ptr(),
                                                   dg.data_ptr(), self._st()), "tp_graph_adjoint")
+        self._done(f"graph_adjoint_l{layer}", t0)
         return dx, dsh, dg
 
     def _transpose(self, rows, count, m, in_t, in_off, in_stride, out_t, out_off, out_stride, to_gemm):
