@@ -290,9 +290,27 @@ def main_md(args, rank, world, local):
     warm = max(3, args.warmup)
     for _ in range(warm):
         md.step()
-    sampler = ClockSampler(local)
+    # per-kernel CUDA-event timings and the launch count come from eager steps (events cannot be read
+    # inside a replayed graph); the timed region below replays the recorded step when N = 1
     md.engine.profile = []
     calls0 = _lib.CALLS
+    probe_steps = 3
+    for _ in range(probe_steps):
+        md.step()
+    torch.cuda.synchronize()
+    calls_per_step = (_lib.CALLS - calls0) // probe_steps
+    profile, md.engine.profile = md.engine.profile, None
+    kern = {}
+    for name, a, b in profile:
+        kern.setdefault(name, []).append(a.elapsed_time(b))
+    kern_ms = {k: float(np.mean(v)) for k, v in kern.items()}
+    edges = md.num_edges
+    graph_cap = None
+    if world == 1 and not args.no_graph:
+        graph_cap = md.enable_graph()
+        for _ in range(2):
+            md.step()
+    sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     barrier()
@@ -304,12 +322,9 @@ def main_md(args, rank, world, local):
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = start.elapsed_time(stop) / args.steps
-    calls = _lib.CALLS - calls0
-    profile, md.engine.profile = md.engine.profile, None
-    kern = {}
-    for name, a, b in profile:
-        kern.setdefault(name, []).append(a.elapsed_time(b))
-    kern_ms = {k: float(np.mean(v)) for k, v in kern.items()}
+    calls = calls_per_step * args.steps
+    if md.check_overflow():
+        raise SystemExit("edge capacity of the recorded step was exceeded; rerun with a larger margin")
     edges = md.num_edges
 
     # end to end: positions arrive from the host every step, forces and energy go back to the host
@@ -321,12 +336,12 @@ def main_md(args, rank, world, local):
         host_e = torch.empty(1, pin_memory=True)
 
         def e2e_step():
+            # the caller owns the coordinates on the host: they go in, the step runs (integration, neighbour
+            # build, energy, forces), and forces, energy and the new coordinates come back
             md.pos.copy_(host_pos, non_blocking=True)
-            md.compute_forces()
+            md.step()
             host_f.copy_(md.forces, non_blocking=True)
             host_e.copy_(md.energy.reshape(1), non_blocking=True)
-            md._kick(True)
-            md._kick(False)
             host_pos.copy_(md.pos, non_blocking=True)
 
         e2e_steps = max(1, min(args.steps, 10))
@@ -365,7 +380,9 @@ def main_md(args, rank, world, local):
         line = {"metric": "MD atom-steps/s", "value": atoms_total / (ms * 1e-3), "unit": "atom-steps/s",
                 "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": dict(workload, edges_total=total_edges, edges_per_atom=total_edges / atoms_total),
+                "config": dict(workload, edges_total=total_edges, edges_per_atom=total_edges / atoms_total,
+                               step_replayed_as_cuda_graph=graph_cap is not None, edge_capacity=graph_cap,
+                               kernels_ms_from="3 eager steps before the timed region"),
                 "gpu_launches": calls, "kernel_status": status, "clocks": clocks,
                 "kernels_ms": kern_ms,
                 "roofline": {"bound": "hbm", "kernel": "tp_adjoint_tma_kernel (layer-1 graph adjoint: dx, dsh, dg)",
@@ -391,6 +408,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="md", choices=["md", "fused_message"])
     ap.add_argument("--cpu-md-side", type=int, default=12)
+    ap.add_argument("--no-graph", action="store_true", help="do not record the single-GPU MD step as a CUDA graph")
     ap.add_argument("--md-brick", default=None, help="lattice sites per GPU as XxYxZ (profiling of small cases)")
     ap.add_argument("--atoms", type=int, default=NUM_ATOMS)
     ap.add_argument("--cpu-sample-atoms", type=int, default=2048)

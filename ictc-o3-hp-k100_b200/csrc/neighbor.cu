@@ -135,6 +135,18 @@ __global__ void nb_fill_kernel(NbGrid g, const float* __restrict__ pos, const in
   }
 }
 
+// Fills the unused tail [count, capacity) of fixed-capacity edge buffers with inert edges so that every
+// consumer can run over `capacity` rows without knowing the edge count on the host.
+__global__ void nb_pad_kernel(const int64_t* __restrict__ count, int64_t capacity, int64_t pad_src, int64_t pad_dst,
+                              int64_t* src, int64_t* dst, float* shifts, int32_t* overflow) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e == 0 && overflow) *overflow = *count > capacity ? 1 : 0;
+  if (e >= capacity || e < *count) return;
+  src[e] = pad_src;
+  dst[e] = pad_dst;
+  shifts[3 * e] = shifts[3 * e + 1] = shifts[3 * e + 2] = 0.f;
+}
+
 // ---- velocity Verlet (positions in A, velocities in A/fs, forces in eV/A, masses in amu) ----------
 constexpr float kAccel = 9.64853321e-3f;   // 1 eV/(A amu) in A/fs^2
 
@@ -266,6 +278,19 @@ int ictc_neighbor_fill(const float* pos, int64_t num_atoms, int64_t num_centres,
   nb_fill_kernel<<<(unsigned)((num_centres + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
       g, pos, s.cell_start, s.cell_atoms, num_centres, rowptr, capacity, src, dst, shifts, edge_keys);
   return finish_launch("neighbor_fill");
+}
+
+int ictc_neighbor_pad(const int64_t* count, int64_t capacity, int64_t pad_src, int64_t pad_dst, int64_t* src,
+                      int64_t* dst, float* shifts, int32_t* overflow, void* stream) {
+  if (capacity < 0 || !count || (capacity > 0 && (!src || !dst || !shifts))) {
+    set_error("neighbor_pad: invalid arguments");
+    return ICTC_ERR_BAD_ARG;
+  }
+  const int64_t blocks = capacity > 0 ? (capacity + 255) / 256 : 1;
+  if (blocks > 2147483647LL) { set_error("neighbor_pad: too many edges"); return ICTC_ERR_TOO_LARGE; }
+  nb_pad_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(count, capacity, pad_src, pad_dst, src, dst,
+                                                                    shifts, overflow);
+  return finish_launch("neighbor_pad");
 }
 
 int ictc_md_kick(int64_t num_atoms, float dt, const float* force, const float* inv_mass, float* vel, float* pos,

@@ -38,6 +38,7 @@ SIGNATURES = {
                                  C.POINTER(C.c_int), C.c_double, _P, _P, _P]),
     "ictc_neighbor_fill": (_I, [_P, _L, _L, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
                                 C.POINTER(C.c_int), C.c_double, _P, _L, _P, _P, _P, _P, _P, _P]),
+    "ictc_neighbor_pad": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P]),
     "ictc_md_kick": (_I, [_L, C.c_float, _P, _P, _P, _P, _P, _I, _P]),
     "ictc_edge_geometry_forward": (_I, [_P, _P, _P, _P, C.POINTER(C.c_float), C.c_float, _I, _I, _L, _P, _P, _P, _P, _P]),
     "ictc_edge_geometry_backward": (_I, [_P, _P, C.c_float, _I, _I, _L, _P, _P, _P, _P]),

@@ -199,13 +199,15 @@ class ForceEngine:
 
     # ---------------------------------------------------------------- the sweep
     @torch.no_grad()
-    def energy_and_gradient(self, pos, species, src, dst, shifts, box, n_owned, dst_rowptr, plan=None):
+    def energy_and_gradient(self, pos, species, src, dst, shifts, box, n_owned, dst_rowptr, plan=None, n_rows=None):
         """pos [N_local,3] (owned rows first), species [N_local] (index), edges sorted by receiver with all
         receivers < n_owned, dst_rowptr [n_owned+1].  Returns (energy of owned atoms, dE/dpos [N_local,3],
-        per-atom energies [n_owned])."""
+        per-atom energies [n_owned]).  ``n_rows`` < N_local marks trailing rows of ``pos`` as padding: they may
+        be named by inert edges (whose sender index is then outside the sender CSR) but carry no features."""
         self.refresh()
         m, c, lib, dev = self.model, self.c, self.lib, self.dev
-        n_local, e = pos.shape[0], int(src.numel())
+        n_local, e = (pos.shape[0] if n_rows is None else int(n_rows)), int(src.numel())
+        species = species[:n_local]
         st = self._st()
         L0, L1 = self.layers
         nb, pcut, rmax = m.number_of_basis, m.polynomial_cutoff_p, m.max_radius

@@ -59,6 +59,47 @@ def neighbor_list(pos, num_centres, lo, hi, box, periodic, cutoff):
     return src, dst, shifts, rowptr
 
 
+class StaticNeighborList:
+    """Neighbour list into fixed-capacity buffers, with no host read-back: the tail of the edge arrays
+    is padded with inert edges (sender = the extra row ``num_atoms`` of the position buffer, which the
+    sender CSR ignores; receiver 0) and an overflow flag stays on the device.  All buffers are allocated
+    once, so the sequence can be recorded in a CUDA graph."""
+
+    def __init__(self, num_atoms, box, cutoff, capacity, device):
+        import ctypes as C
+        self.n, self.cap, self.cutoff, self.dev = int(num_atoms), int(capacity), float(cutoff), device
+        lib = _lib.load()
+        arr = lambda v, t: (t * 3)(*[v[i] for i in range(3)])
+        self.lo, self.hi = arr([0.0, 0.0, 0.0], C.c_double), arr([float(b) for b in box], C.c_double)
+        self.box, self.per = arr([float(b) for b in box], C.c_double), arr([1, 1, 1], C.c_int)
+        n1 = self.n + 1                                   # the position buffer carries one extra (dummy) row
+        self.scratch = torch.empty(int(lib.ictc_neighbor_scratch_bytes(n1, self.lo, self.hi, self.cutoff)),
+                                   dtype=torch.uint8, device=device)
+        self.scan = torch.empty(int(lib.ictc_scan_scratch_bytes(self.n + 1)), dtype=torch.uint8, device=device)
+        self.rowptr = torch.zeros(self.n + 1, dtype=torch.int64, device=device)
+        self.src = torch.zeros(self.cap, dtype=torch.int64, device=device)
+        self.dst = torch.zeros(self.cap, dtype=torch.int64, device=device)
+        self.shifts = torch.zeros(self.cap, 3, dtype=torch.float32, device=device)
+        self.keys = torch.zeros(self.cap, dtype=torch.int64, device=device)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def build(self, pos_ext):
+        """pos_ext [n+1, 3]: the real atoms followed by the dummy row (far away from every atom)."""
+        lib, st = _lib.load(), _lib.stream(self.dev)
+        n, n1 = self.n, self.n + 1
+        _lib.check(lib.ictc_neighbor_count(pos_ext.data_ptr(), n1, n, self.lo, self.hi, self.box, self.per,
+                                           self.cutoff, self.rowptr.data_ptr(), self.scratch.data_ptr(), st),
+                   "ictc_neighbor_count")
+        _lib.check(lib.ictc_inclusive_scan_i64(self.rowptr.data_ptr(), n + 1, self.scan.data_ptr(), st), "scan")
+        _lib.check(lib.ictc_neighbor_fill(pos_ext.data_ptr(), n1, n, self.lo, self.hi, self.box, self.per, self.cutoff,
+                                          self.rowptr.data_ptr(), self.cap, self.src.data_ptr(), self.dst.data_ptr(),
+                                          self.shifts.data_ptr(), self.keys.data_ptr(), self.scratch.data_ptr(), st),
+                   "ictc_neighbor_fill")
+        _lib.check(lib.ictc_neighbor_pad(self.rowptr.data_ptr() + 8 * n, self.cap, n, 0, self.src.data_ptr(),
+                                         self.dst.data_ptr(), self.shifts.data_ptr(), self.overflow.data_ptr(), st),
+                   "ictc_neighbor_pad")
+
+
 def maxwell_boltzmann(masses: np.ndarray, temperature: float, seed: int) -> np.ndarray:
     """Gaussian velocities (A/fs) at ``temperature`` with zero total momentum, rescaled to the exact
     target (LAMMPS ``velocity all create T seed mom yes rot no dist gaussian``)."""
@@ -116,6 +157,8 @@ class MolecularDynamics:
         self.energy = None
         self.num_edges = 0
         self.launches = 0
+        self.graph = None
+        self._static = None
 
     # ------------------------------------------------------------------ forces
     def compute_forces(self):
@@ -130,8 +173,12 @@ class MolecularDynamics:
         self.num_edges = int(src.numel())
         if self.engine is not None:
             energy, grad, _ = self.engine.energy_and_gradient(self.pos, self.species, src, dst, shifts, box, n, rowptr)
-            self.energy = energy
-            self.forces = (-grad).contiguous()
+            if self._static is not None:            # keep the buffers the recorded graph reads and writes
+                self._static["energy"].copy_(energy.reshape(1))
+                self.forces.copy_(grad).neg_()
+            else:
+                self.energy = energy
+                self.forces = (-grad).contiguous()
             return self.forces
         topo = Topology(src, dst, n, dst_sorted=True)
         topo._by_dst = (rowptr, None)
@@ -197,6 +244,57 @@ class MolecularDynamics:
         self.forces = (-total).contiguous()
         return self.forces
 
+    # ------------------------------------------------------------------ CUDA-graph replay (single GPU)
+    def _step_static(self):
+        """One full step on fixed buffers only (no host read-back, no data-dependent host control flow)."""
+        st = self._static
+        n = self.pos.shape[0]
+        self._kick(True)
+        st["pos_ext"][:n].copy_(self.pos)
+        st["nl"].build(st["pos_ext"])
+        nl = st["nl"]
+        energy, grad, _ = self.engine.energy_and_gradient(st["pos_ext"], st["species_ext"], nl.src, nl.dst, nl.shifts,
+                                                          self.box.tolist(), n, nl.rowptr, n_rows=n)
+        st["energy"].copy_(energy.reshape(1))
+        self.forces.copy_(grad).neg_()
+        self._kick(False)
+
+    def enable_graph(self, margin=1.04, warmup=2):
+        """Record the whole MD step (integration, neighbour build, forces) as one CUDA graph.
+
+        Edge buffers get a fixed capacity of ``margin`` times the current edge count; the device-side
+        overflow flag is checked by ``check_overflow``.  Single-GPU, engine path only."""
+        if self.world != 1 or self.engine is None:
+            raise RuntimeError("graph replay covers the single-GPU engine path")
+        if self.forces is None:
+            self.compute_forces()
+        n, dev = self.pos.shape[0], self.device
+        cap = int(self.num_edges * margin) + 1024
+        pos_ext = torch.zeros(n + 1, 3, dtype=torch.float32, device=dev)
+        pos_ext[n] = -1.0e6          # the dummy row sits far outside every cutoff sphere
+        species_ext = torch.cat((self.species, self.species.new_zeros(1)))
+        self._static = {"nl": StaticNeighborList(n, self.box.tolist(), self.cutoff, cap, dev), "pos_ext": pos_ext,
+                        "species_ext": species_ext, "energy": torch.zeros(1, device=dev), "cap": cap}
+        self.forces = self.forces.clone()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self._step_static()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._step_static()
+        self.energy = self._static["energy"][0]
+        return cap
+
+    def check_overflow(self):
+        """True when a replayed step needed more edges than the recorded capacity (results invalid)."""
+        if self._static is None:
+            return False
+        return bool(int(self._static["nl"].overflow.item()))
+
     # ------------------------------------------------------------------ integration
     def _kick(self, drift):
         lib = _lib.load()
@@ -207,6 +305,9 @@ class MolecularDynamics:
 
     def step(self):
         """One velocity-Verlet step; neighbours are rebuilt every step."""
+        if self.graph is not None:
+            self.graph.replay()
+            return
         if self.forces is None:
             self.compute_forces()
         self._kick(True)

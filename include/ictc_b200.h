@@ -153,6 +153,12 @@ int ictc_neighbor_fill(const float* pos, int64_t num_atoms, int64_t num_centres,
                        const double* host_hi, const double* host_box, const int* host_periodic, double cutoff,
                        const int64_t* rowptr, int64_t capacity, int64_t* src, int64_t* dst, float* shifts,
                        int64_t* edge_keys, void* scratch, void* stream);
+/* Fixed-capacity edge buffers: after ictc_neighbor_fill, rows [*count, capacity) of src/dst/shifts are set
+ * to the inert edge (pad_src, pad_dst, zero shift) and *overflow (device int32, may be NULL) tells
+ * whether *count exceeded the capacity.  `count` is a DEVICE pointer (normally &rowptr[num_centres]).
+ * This lets a whole MD step run without the host ever learning the edge count (CUDA-graph replay). */
+int ictc_neighbor_pad(const int64_t* count, int64_t capacity, int64_t pad_src, int64_t pad_dst, int64_t* src,
+                      int64_t* dst, float* shifts, int32_t* overflow, void* stream);
 /* Half step of velocity Verlet: vel += dt/2 * F/m (A, fs, eV, amu); with drift != 0 also
  * pos += dt * vel, wrapped into [0, box) on axes with box > 0.  The reference leaves integration to
  * LAMMPS `fix nve` (examples/in.hco); this is the stand-alone equivalent. */
