@@ -147,6 +147,66 @@ __global__ void nb_pad_kernel(const int64_t* __restrict__ count, int64_t capacit
   shifts[3 * e] = shifts[3 * e + 1] = shifts[3 * e + 2] = 0.f;
 }
 
+// ---- radial pairing --------------------------------------------------------------------------------
+// Edge (j -> i, S) and its reverse (i -> j, -S) have bitwise the same length, so everything that depends
+// on the length alone (radial basis, gate MLP) is evaluated once per pair.  `rev` finds the reverse edge by
+// binary search in the sorted row of j; an edge is the pair's representative when it has no reverse in the
+// list (sender is not a centre) or when its index is the smaller of the two.
+__global__ void nb_pair_find_kernel(const int64_t* __restrict__ rowptr, const int64_t* __restrict__ dst,
+                                    const int64_t* __restrict__ keys, int64_t centres, int64_t capacity,
+                                    const int64_t* __restrict__ count, int64_t* rev, int64_t* flag) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= capacity) return;
+  if (e >= *count) {
+    rev[e] = -1;
+    flag[e] = 0;
+    return;
+  }
+  const int64_t key = keys[e];
+  const int64_t j = key / 27, i = dst[e];
+  int64_t r = -1;
+  if (j < centres) {
+    const int64_t want = i * 27 + (26 - key % 27);
+    int64_t lo = rowptr[j], hi = rowptr[j + 1];
+    while (lo < hi) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (keys[mid] < want) lo = mid + 1; else hi = mid;
+    }
+    if (lo < rowptr[j + 1] && keys[lo] == want) r = lo;
+  }
+  rev[e] = r;
+  flag[e] = (r < 0 || e < r) ? 1 : 0;
+}
+
+// scan = inclusive prefix sum of the representative flags
+__global__ void nb_pair_assign_kernel(const int64_t* __restrict__ scan, const int64_t* __restrict__ rev,
+                                      int64_t capacity, int64_t unique_capacity, const int64_t* __restrict__ count,
+                                      int64_t* gate_row, int64_t* rep_edge, int64_t* other_edge, int64_t* num_unique) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t n = *count < capacity ? *count : capacity;
+  const int64_t total = n > 0 ? scan[n - 1] : 0;
+  if (e == 0) *num_unique = total;
+  if (e < capacity) {
+    if (e < n) {
+      const int64_t r = rev[e];
+      const bool rep = r < 0 || e < r;
+      const int64_t u = (rep ? scan[e] : scan[r]) - 1;
+      gate_row[e] = u;
+      if (rep && u < unique_capacity) {
+        rep_edge[u] = e;
+        other_edge[u] = r;
+      }
+    } else {
+      gate_row[e] = 0;
+    }
+  }
+  // rows of the pair table beyond the number of pairs point at the last (inert) edge slot
+  if (e >= total && e < unique_capacity) {
+    rep_edge[e] = capacity - 1;
+    other_edge[e] = -1;
+  }
+}
+
 // ---- velocity Verlet (positions in A, velocities in A/fs, forces in eV/A, masses in amu) ----------
 constexpr float kAccel = 9.64853321e-3f;   // 1 eV/(A amu) in A/fs^2
 
@@ -291,6 +351,34 @@ int ictc_neighbor_pad(const int64_t* count, int64_t capacity, int64_t pad_src, i
   nb_pad_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(count, capacity, pad_src, pad_dst, src, dst,
                                                                     shifts, overflow);
   return finish_launch("neighbor_pad");
+}
+
+extern "C" int ictc_inclusive_scan_i64(int64_t* data, int64_t n, void* scratch, void* stream);
+
+int ictc_neighbor_pairs(const int64_t* rowptr, const int64_t* dst, const int64_t* edge_keys, int64_t num_centres,
+                        int64_t capacity, int64_t unique_capacity, const int64_t* count, int64_t* rev, int64_t* scan,
+                        int64_t* gate_row, int64_t* rep_edge, int64_t* other_edge, int64_t* num_unique,
+                        void* scan_scratch, void* stream) {
+  if (num_centres < 0 || capacity < 0 || unique_capacity < 0 || !count || !num_unique) {
+    set_error("neighbor_pairs: invalid arguments");
+    return ICTC_ERR_BAD_ARG;
+  }
+  const int64_t span = capacity > unique_capacity ? capacity : unique_capacity;
+  if (span == 0) return ICTC_OK;
+  if (!rowptr || !dst || !edge_keys || !rev || !scan || !gate_row || !rep_edge || !other_edge || !scan_scratch) {
+    set_error("neighbor_pairs: NULL buffer");
+    return ICTC_ERR_BAD_ARG;
+  }
+  if ((span + 255) / 256 > 2147483647LL) { set_error("neighbor_pairs: too many edges"); return ICTC_ERR_TOO_LARGE; }
+  cudaStream_t st = (cudaStream_t)stream;
+  if (capacity > 0) {
+    nb_pair_find_kernel<<<(unsigned)((capacity + 255) / 256), 256, 0, st>>>(rowptr, dst, edge_keys, num_centres,
+                                                                           capacity, count, rev, scan);
+    if (int rc = ictc_inclusive_scan_i64(scan, capacity, scan_scratch, stream)) return rc;
+  }
+  nb_pair_assign_kernel<<<(unsigned)((span + 255) / 256), 256, 0, st>>>(scan, rev, capacity, unique_capacity, count,
+                                                                      gate_row, rep_edge, other_edge, num_unique);
+  return finish_launch("neighbor_pairs");
 }
 
 int ictc_md_kick(int64_t num_atoms, float dt, const float* force, const float* inv_mass, float* vel, float* pos,

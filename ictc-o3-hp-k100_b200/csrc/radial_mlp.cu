@@ -130,7 +130,9 @@ struct MlpArgs {
   float* z1;            // [E, 64] pre-activations (optional in forward, required in backward)
   float* z2;
   float* z3;
-  const float* dgates;  // [E, nout]
+  const float* dgates;  // [rows, nout]
+  const int64_t* pair_a;  // optional: row u of the MLP reads dgates[pair_a[u]] + dgates[pair_b[u]] (pair_b < 0: none)
+  const int64_t* pair_b;
   float* drb;           // [E, nb]
   int64_t E;
   int nb, nout;
@@ -264,6 +266,8 @@ __global__ void __launch_bounds__(kMlpWarps * 32, 1) radial_mlp_backward_kernel(
     const int64_t r_lo = row0 + g, r_hi = row0 + g + 8;
     const bool ok_lo = r_lo < a.E, ok_hi = r_hi < a.E;
     const int64_t c_lo = ok_lo ? r_lo : 0, c_hi = ok_hi ? r_hi : 0;   // clamped rows for loads
+    const int64_t da_lo = a.pair_a ? a.pair_a[c_lo] : c_lo, da_hi = a.pair_a ? a.pair_a[c_hi] : c_hi;
+    const int64_t db_lo = a.pair_b ? a.pair_b[c_lo] : -1, db_hi = a.pair_b ? a.pair_b[c_hi] : -1;
     stage_split_async(w3s, a.w3, a.nout);
     wait_async();
     __syncthreads();
@@ -276,8 +280,18 @@ __global__ void __launch_bounds__(kMlpWarps * 32, 1) radial_mlp_backward_kernel(
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const int col = ch * kH + ks * 8 + 2 * t;
-        float2 lo = *reinterpret_cast<const float2*>(a.dgates + c_lo * a.nout + col);
-        float2 hi = *reinterpret_cast<const float2*>(a.dgates + c_hi * a.nout + col);
+        float2 lo = *reinterpret_cast<const float2*>(a.dgates + da_lo * a.nout + col);
+        float2 hi = *reinterpret_cast<const float2*>(a.dgates + da_hi * a.nout + col);
+        if (db_lo >= 0) {
+          const float2 o = *reinterpret_cast<const float2*>(a.dgates + db_lo * a.nout + col);
+          lo.x += o.x;
+          lo.y += o.y;
+        }
+        if (db_hi >= 0) {
+          const float2 o = *reinterpret_cast<const float2*>(a.dgates + db_hi * a.nout + col);
+          hi.x += o.x;
+          hi.y += o.y;
+        }
         if (!ok_lo) lo = make_float2(0.f, 0.f);
         if (!ok_hi) hi = make_float2(0.f, 0.f);
         const float v[4] = {lo.x, hi.x, lo.y, hi.y};
@@ -392,9 +406,22 @@ int ictc_radial_mlp_forward(int64_t num_edges, int num_basis, int num_out, const
   return finish_launch("radial_mlp_forward");
 }
 
+int ictc_radial_mlp_backward_paired(int64_t num_rows, int num_basis, int num_out, const float* dgates,
+                                    const int64_t* pair_a, const int64_t* pair_b, const float* w0t, const float* w1t,
+                                    const float* w2t, const float* w3t_split, const float* z1, const float* z2,
+                                    const float* z3, float* drb, void* stream);
+
 int ictc_radial_mlp_backward(int64_t num_edges, int num_basis, int num_out, const float* dgates, const float* w0t,
                              const float* w1t, const float* w2t, const float* w3t_split, const float* z1,
                              const float* z2, const float* z3, float* drb, void* stream) {
+  return ictc_radial_mlp_backward_paired(num_edges, num_basis, num_out, dgates, nullptr, nullptr, w0t, w1t, w2t,
+                                         w3t_split, z1, z2, z3, drb, stream);
+}
+
+int ictc_radial_mlp_backward_paired(int64_t num_edges, int num_basis, int num_out, const float* dgates,
+                                    const int64_t* pair_a, const int64_t* pair_b, const float* w0t, const float* w1t,
+                                    const float* w2t, const float* w3t_split, const float* z1, const float* z2,
+                                    const float* z3, float* drb, void* stream) {
   if (int rc = mlp_check(num_edges, num_basis, num_out)) return rc;
   if (num_edges == 0) return ICTC_OK;
   if (!dgates || !w0t || !w1t || !w2t || !w3t_split || !z1 || !z2 || !z3 || !drb) {
@@ -403,6 +430,7 @@ int ictc_radial_mlp_backward(int64_t num_edges, int num_basis, int num_out, cons
   }
   MlpArgs a{};
   a.w0 = w0t; a.w1 = w1t; a.w2 = w2t; a.w3 = reinterpret_cast<const float2*>(w3t_split); a.dgates = dgates; a.drb = drb;
+  a.pair_a = pair_a; a.pair_b = pair_b;
   a.z1 = const_cast<float*>(z1); a.z2 = const_cast<float*>(z2); a.z3 = const_cast<float*>(z3);
   a.E = num_edges; a.nb = num_basis; a.nout = num_out;
   const size_t smem = size_t(8 * kWS + 4 * kH * kWS) * sizeof(float2) + size_t(kMlpWarps * 16 * kAS) * sizeof(float);

@@ -126,10 +126,23 @@ int ictc_tp_edge_adjoint(int spec, int channels, int64_t num_edges, const float*
   return o->adjoint(a, false, (cudaStream_t)stream);
 }
 
+int ictc_tp_graph_forward_shared(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                                 const float* sh, const float* w, const float* g, const int64_t* gate_row,
+                                 const int64_t* src, const int64_t* dst_rowptr, const int64_t* dst_order,
+                                 const float* mask, float* out, void* stream);
+
 int ictc_tp_graph_forward(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
                           const float* sh, const float* w, const float* g, const int64_t* src,
                           const int64_t* dst_rowptr, const int64_t* dst_order, const float* mask, float* out,
                           void* stream) {
+  return ictc_tp_graph_forward_shared(spec, channels, num_nodes, num_edges, x, sh, w, g, nullptr, src, dst_rowptr,
+                                      dst_order, mask, out, stream);
+}
+
+int ictc_tp_graph_forward_shared(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                                 const float* sh, const float* w, const float* g, const int64_t* gate_row,
+                                 const int64_t* src, const int64_t* dst_rowptr, const int64_t* dst_order,
+                                 const float* mask, float* out, void* stream) {
   const TpOps* o = find_ops(spec);
   if (!o) return ICTC_ERR_BAD_SPEC;
   if (!check(channels > 0 && num_edges >= 0 && num_nodes >= 0, "sizes")) return ICTC_ERR_BAD_ARG;
@@ -138,14 +151,27 @@ int ictc_tp_graph_forward(int spec, int channels, int64_t num_nodes, int64_t num
   if (num_edges > 0 && !check(x && sh && g && src, "x, sh, g, src must not be NULL")) return ICTC_ERR_BAD_ARG;
   TpArgs a{};
   a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.out = out; a.nbr = src; a.rowptr = dst_rowptr;
-  a.order = dst_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = status_word();
+  a.grow = gate_row; a.order = dst_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = status_word();
   return o->graph_forward(a, (cudaStream_t)stream);
 }
+
+int ictc_tp_graph_adjoint_shared(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                                 const float* sh, const float* w, const float* g, const int64_t* gate_row,
+                                 const int64_t* dst, const int64_t* src_rowptr, const int64_t* src_order,
+                                 const float* mask, const float* v, float* dx, float* dsh, float* dg, void* stream);
 
 int ictc_tp_graph_adjoint(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
                           const float* sh, const float* w, const float* g, const int64_t* dst,
                           const int64_t* src_rowptr, const int64_t* src_order, const float* mask, const float* v,
                           float* dx, float* dsh, float* dg, void* stream) {
+  return ictc_tp_graph_adjoint_shared(spec, channels, num_nodes, num_edges, x, sh, w, g, nullptr, dst, src_rowptr,
+                                      src_order, mask, v, dx, dsh, dg, stream);
+}
+
+int ictc_tp_graph_adjoint_shared(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                                 const float* sh, const float* w, const float* g, const int64_t* gate_row,
+                                 const int64_t* dst, const int64_t* src_rowptr, const int64_t* src_order,
+                                 const float* mask, const float* v, float* dx, float* dsh, float* dg, void* stream) {
   const TpOps* o = find_ops(spec);
   if (!o) return ICTC_ERR_BAD_SPEC;
   if (!check(channels > 0 && num_edges >= 0 && num_nodes >= 0, "sizes")) return ICTC_ERR_BAD_ARG;
@@ -154,7 +180,7 @@ int ictc_tp_graph_adjoint(int spec, int channels, int64_t num_nodes, int64_t num
   if (num_edges > 0 && !check(sh && g && dst && v, "sh, g, dst, v must not be NULL")) return ICTC_ERR_BAD_ARG;
   TpArgs a{};
   a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.v = v; a.dx = dx; a.dsh = dsh; a.dg = dg; a.nbr = dst;
-  a.rowptr = src_rowptr; a.order = src_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = status_word();
+  a.grow = gate_row; a.rowptr = src_rowptr; a.order = src_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = status_word();
   return o->adjoint(a, true, (cudaStream_t)stream);
 }
 

@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_graph_forward_fast_kernel(
       s_next = ldg(a.nbr + e_next);
     }
     const float shv = lane < S::NH ? ldg(a.sh + e * S::NH + lane) : 0.f;
-    const float* gp = a.g + e * (S::NP * C) + lane * CPL;
+    const float* gp = a.g + (a.grow ? ldg(a.grow + e) : e) * (S::NP * C) + lane * CPL;
     const float* xp = a.x + s * (S::NX * C) + lane * CPL;
     V ge[S::NP], x[S::NX];
 #pragma unroll
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_fast_kernel(TpArgs
       d_next = GRAPH ? ldg(a.nbr + e_next) : e_next;
     }
     const float shv = lane < S::NH ? ldg(a.sh + e * S::NH + lane) : 0.f;
-    const float* gp = a.g + e * (S::NP * C) + lane * CPL;
+    const float* gp = a.g + (a.grow ? ldg(a.grow + e) : e) * (S::NP * C) + lane * CPL;
     const float* vp = a.v + d * (S::NO * C) + lane * CPL;
     V ge[S::NP], v[S::NO], scale[S::NP];
 #pragma unroll

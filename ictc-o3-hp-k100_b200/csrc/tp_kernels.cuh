@@ -81,6 +81,7 @@ struct TpArgs {
   const int64_t* nbr;     // forward: src[E]; adjoint: dst[E]   (graph kernels)
   const int64_t* rowptr;  // CSR over the owner of the reduction
   const int64_t* order;   // CSR edge order or null (identity)
+  const int64_t* grow;    // row of every edge in the gate table, or null (row = edge id)
   int64_t N, E;
   int C;
   int* status;          // device status word for kernels with bounded waits (may be null)
@@ -141,8 +142,9 @@ __global__ void __launch_bounds__(128) tp_graph_forward_kernel(TpArgs a) {
     for (int i = 0; i < S::NX; ++i) x[i] = ldg(a.x + (s * S::NX + i) * a.C + c);
 #pragma unroll
     for (int j = 0; j < S::NH; ++j) sh[j] = ldg(a.sh + e * S::NH + j);
+    const int64_t gr = a.grow ? ldg(a.grow + e) : e;
 #pragma unroll
-    for (int p = 0; p < S::NP; ++p) ge[p] = ldg(a.g + (e * S::NP + p) * a.C + c) * (wv[p] * mu);
+    for (int p = 0; p < S::NP; ++p) ge[p] = ldg(a.g + (gr * S::NP + p) * a.C + c) * (wv[p] * mu);
     S::couple(x, sh, t);
     S::gate_acc(t, ge, acc);
   }
@@ -190,12 +192,13 @@ __global__ void tp_adjoint_kernel(TpArgs a) {
     for (int q = 0; q < cnt; ++q) {
       const int64_t e = (GRAPH && a.order) ? ldg(a.order + base + q) : base + q;
       const int64_t vrow = GRAPH ? ldg(a.nbr + e) : e;
+      const int64_t gr = a.grow ? ldg(a.grow + e) : e;
       const float mu = a.mask ? ldg(a.mask + e) : 1.f;
       float sh[S::NH], ge[S::NP], v[S::NO];
 #pragma unroll
       for (int j = 0; j < S::NH; ++j) sh[j] = ldg(a.sh + e * S::NH + j);
 #pragma unroll
-      for (int p = 0; p < S::NP; ++p) ge[p] = ldg(a.g + (e * S::NP + p) * a.C + cc) * (wv[p] * mu);
+      for (int p = 0; p < S::NP; ++p) ge[p] = ldg(a.g + (gr * S::NP + p) * a.C + cc) * (wv[p] * mu);
 #pragma unroll
       for (int k = 0; k < S::NO; ++k) v[k] = on ? ldg(a.v + (vrow * S::NO + k) * a.C + cc) : 0.f;
       if (NEEDX || NEEDG) {

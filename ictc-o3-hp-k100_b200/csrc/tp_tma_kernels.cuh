@@ -110,7 +110,8 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_graph_forward_tma_kernel(T
       const unsigned bar = bars + slot * 8;
       unsigned char* dst = mine + slot * L::SLOT_BYTES;
       mbar_expect_tx(bar, L::SLOT_BYTES);
-      bulk_g2s(smem_addr(dst), a.g + e * (S::NP * C), L::GATE_BYTES, bar);
+      const int64_t gr = a.grow ? ldg(a.grow + e) : e;
+      bulk_g2s(smem_addr(dst), a.g + gr * (S::NP * C), L::GATE_BYTES, bar);
       if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.x + s * (S::NX * C), L::ROW_BYTES, bar);
     }
   };
@@ -234,7 +235,8 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs 
       const unsigned bar = bars + slot * 8;
       unsigned char* dst = mine + slot * L::SLOT_BYTES;
       mbar_expect_tx(bar, L::SLOT_BYTES);
-      bulk_g2s(smem_addr(dst), a.g + e * (S::NP * C), L::GATE_BYTES, bar);
+      const int64_t gr = a.grow ? ldg(a.grow + e) : e;
+      bulk_g2s(smem_addr(dst), a.g + gr * (S::NP * C), L::GATE_BYTES, bar);
       if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.v + d * (S::NO * C), L::ROW_BYTES, bar);
     }
   };

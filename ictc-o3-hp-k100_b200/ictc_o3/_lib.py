@@ -27,6 +27,9 @@ SIGNATURES = {
     "ictc_tp_edge_adjoint": (_I, [_I, _I, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_tp_graph_forward": (_I, [_I, _I, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_tp_graph_adjoint": (_I, [_I, _I, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "ictc_tp_graph_forward_shared": (_I, [_I, _I, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "ictc_tp_graph_adjoint_shared": (_I, [_I, _I, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "ictc_radial_mlp_backward_paired": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_csr_scratch_bytes": (_L, [_L, _L]),
     "ictc_csr_build": (_I, [_P, _L, _L, _P, _P, _P, _P, _P]),
     "ictc_csr_build_static": (_I, [_P, _L, _L, _P, _P, _P, _P]),
@@ -39,6 +42,7 @@ SIGNATURES = {
     "ictc_neighbor_fill": (_I, [_P, _L, _L, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
                                 C.POINTER(C.c_int), C.c_double, _P, _L, _P, _P, _P, _P, _P, _P]),
     "ictc_neighbor_pad": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P]),
+    "ictc_neighbor_pairs": (_I, [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_md_kick": (_I, [_L, C.c_float, _P, _P, _P, _P, _P, _I, _P]),
     "ictc_edge_geometry_forward": (_I, [_P, _P, _P, _P, C.POINTER(C.c_float), C.c_float, _I, _I, _L, _P, _P, _P, _P, _P]),
     "ictc_edge_geometry_backward": (_I, [_P, _P, C.c_float, _I, _I, _L, _P, _P, _P, _P]),

@@ -135,16 +135,24 @@ class ForceEngine:
             else:
                 return z, pre
 
-    def _mlp_bwd(self, dgates, pre, L):
+    def _mlp_bwd(self, dgates, pre, L, pairs=None):
+        if pairs is not None and not self._fused_mlp_ok(L):
+            dgates = dgates.index_select(0, pairs[1]) + torch.where(
+                (pairs[2] >= 0).unsqueeze(1), dgates.index_select(0, pairs[2].clamp_min(0)), dgates.new_zeros(()))
+            pairs = None
         if self._fused_mlp_ok(L):
-            e, ft = dgates.shape[0], L["fc_t"]
+            ft = L["fc_t"]
+            e = pre[0].shape[0]
             nb = ft[0].shape[0]
             drb = torch.empty(e, nb, dtype=torch.float32, device=self.dev)
             t0 = self._mark()
-            _lib.check(self.lib.ictc_radial_mlp_backward(e, nb, dgates.shape[1], _lib.ptr(dgates), ft[0].data_ptr(),
-                                                         ft[1].data_ptr(), ft[2].data_ptr(), L["w3t_split"].data_ptr(),
-                                                         _lib.ptr(pre[0]), _lib.ptr(pre[1]), _lib.ptr(pre[2]),
-                                                         _lib.ptr(drb), self._st()), "radial_mlp_backward")
+            pa, pb = (None, None) if pairs is None else (pairs[1], pairs[2])
+            _lib.check(self.lib.ictc_radial_mlp_backward_paired(e, nb, dgates.shape[1], _lib.ptr(dgates), _lib.ptr(pa),
+                                                                _lib.ptr(pb), ft[0].data_ptr(),
+                                                                ft[1].data_ptr(), ft[2].data_ptr(),
+                                                                L["w3t_split"].data_ptr(), _lib.ptr(pre[0]),
+                                                                _lib.ptr(pre[1]), _lib.ptr(pre[2]), _lib.ptr(drb),
+                                                                self._st()), "radial_mlp_backward")
             self._done(f"radial_mlp_backward_{dgates.shape[1]}", t0)
             return drb
         d = torch.mm(dgates, L["fc"][-1])
@@ -168,27 +176,29 @@ class ForceEngine:
         if start is not None:
             self.profile.append((name, start, self._mark()))
 
-    def _tp_forward(self, layer, x, sh, g, src, rowptr, rows, e, tpw):
+    def _tp_forward(self, layer, x, sh, g, src, rowptr, rows, e, tpw, grow=None):
         c = self.c
         out = torch.empty(rows, (9 if layer == 0 else 35) * c, dtype=torch.float32, device=self.dev)
         t0 = self._mark()
-        _lib.check(self.lib.ictc_tp_graph_forward(self._spec[layer], c, rows, e, x.data_ptr(), sh.data_ptr(),
-                                                  _lib.ptr(tpw), g.data_ptr(), src.data_ptr(), rowptr.data_ptr(),
-                                                  None, None, out.data_ptr(), self._st()), "tp_graph_forward")
+        _lib.check(self.lib.ictc_tp_graph_forward_shared(self._spec[layer], c, rows, e, x.data_ptr(), sh.data_ptr(),
+                                                         _lib.ptr(tpw), g.data_ptr(), _lib.ptr(grow), src.data_ptr(),
+                                                         rowptr.data_ptr(), None, None, out.data_ptr(), self._st()),
+                   "tp_graph_forward")
         self._done(f"graph_forward_l{layer}", t0)
         return out
 
-    def _tp_adjoint(self, layer, x, sh, g, dst, src_csr, v, n_rows, e, tpw, need_x):
+    def _tp_adjoint(self, layer, x, sh, g, dst, src_csr, v, n_rows, e, tpw, need_x, grow=None):
         c = self.c
         dx = torch.empty_like(x) if need_x else None
         dsh = torch.empty_like(sh)
-        dg = torch.empty_like(g)
+        dg = torch.empty(e, g.shape[1], dtype=torch.float32, device=self.dev)
         rowptr, order = src_csr
         t0 = self._mark()
-        _lib.check(self.lib.ictc_tp_graph_adjoint(self._spec[layer], c, n_rows, e, x.data_ptr(), sh.data_ptr(),
-                                                  _lib.ptr(tpw), g.data_ptr(), dst.data_ptr(), rowptr.data_ptr(),
-                                                  _lib.ptr(order), None, v.data_ptr(), _lib.ptr(dx), dsh.data_ptr(),
-                                                  dg.data_ptr(), self._st()), "tp_graph_adjoint")
+        _lib.check(self.lib.ictc_tp_graph_adjoint_shared(self._spec[layer], c, n_rows, e, x.data_ptr(), sh.data_ptr(),
+                                                         _lib.ptr(tpw), g.data_ptr(), _lib.ptr(grow), dst.data_ptr(),
+                                                         rowptr.data_ptr(), _lib.ptr(order), None, v.data_ptr(),
+                                                         _lib.ptr(dx), dsh.data_ptr(), dg.data_ptr(), self._st()),
+                   "tp_graph_adjoint")
         self._done(f"graph_adjoint_l{layer}", t0)
         return dx, dsh, dg
 
@@ -199,11 +209,13 @@ class ForceEngine:
 
     # ---------------------------------------------------------------- the sweep
     @torch.no_grad()
-    def energy_and_gradient(self, pos, species, src, dst, shifts, box, n_owned, dst_rowptr, plan=None, n_rows=None):
+    def energy_and_gradient(self, pos, species, src, dst, shifts, box, n_owned, dst_rowptr, plan=None, n_rows=None,
+                            pairs=None):
         """pos [N_local,3] (owned rows first), species [N_local] (index), edges sorted by receiver with all
         receivers < n_owned, dst_rowptr [n_owned+1].  Returns (energy of owned atoms, dE/dpos [N_local,3],
         per-atom energies [n_owned]).  ``n_rows`` < N_local marks trailing rows of ``pos`` as padding: they may
-        be named by inert edges (whose sender index is then outside the sender CSR) but carry no features."""
+        be named by inert edges (whose sender index is then outside the sender CSR) but carry no features.
+        ``pairs`` = (gate_row [E], rep_edge [U], other_edge [U]) evaluates the radial MLP once per edge pair."""
         self.refresh()
         m, c, lib, dev = self.model, self.c, self.lib, self.dev
         n_local, e = (pos.shape[0] if n_rows is None else int(n_rows)), int(src.numel())
@@ -222,13 +234,15 @@ class ForceEngine:
                                                       box_c, rmax, nb, pcut, e, _lib.ptr(sh), _lib.ptr(rb),
                                                       _lib.ptr(unit), _lib.ptr(length), st), "edge_geometry_forward")
             src_csr = build_csr(src, n_local, assume_sorted=False)
+            grow = None if pairs is None else pairs[0]
+            rb_u = rb if pairs is None else rb.index_select(0, pairs[1])
             sp_owned = species[:n_owned]
             s_count = self.emb.shape[0]
             # ---- layer 0
             x0 = self.emb.index_select(0, species)                               # [N_local, C]
             u0 = torch.mm(x0, L0["up_t"][0])
-            g0, pre0 = self._mlp(rb, L0)
-            M0 = self._tp_forward(0, u0, sh, g0, src, dst_rowptr, n_owned, e, L0["tpw"])   # [n, 9C]
+            g0, pre0 = self._mlp(rb_u, L0)
+            M0 = self._tp_forward(0, u0, sh, g0, src, dst_rowptr, n_owned, e, L0["tpw"], grow)   # [n, 9C]
             m0 = torch.empty_like(M0)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 m0[:, off * c:(off + mm) * c] = torch.mm(M0[:, off * c:(off + mm) * c].reshape(-1, c),
@@ -249,8 +263,8 @@ class ForceEngine:
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 u1[:, off * c:(off + mm) * c] = torch.mm(h1_full[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L1["up_t"][l]).view(n_local, mm * c)
-            g1, pre1 = self._mlp(rb, L1)
-            M1 = self._tp_forward(1, u1, sh, g1, src, dst_rowptr, n_owned, e, L1["tpw"])   # [n, 35C]
+            g1, pre1 = self._mlp(rb_u, L1)
+            M1 = self._tp_forward(1, u1, sh, g1, src, dst_rowptr, n_owned, e, L1["tpw"], grow)   # [n, 35C]
             m1 = torch.empty(n_owned, 9 * c, dtype=torch.float32, device=dev)
             in_off = 0
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
@@ -282,8 +296,8 @@ class ForceEngine:
                 buf = torch.mm(dm1[:, off * c:(off + mm) * c].reshape(-1, c), L1["ml"][l])   # [n*mm, cnt*C]
                 self._transpose(n_owned, cnt, mm, buf, 0, mm * cnt * c, v1, out_off, 35 * c, False)
                 out_off += cnt * mm * c
-            du1, dsh1, dg1 = self._tp_adjoint(1, u1, sh, g1, dst, src_csr, v1, n_local, e, L1["tpw"], True)
-            drb = self._mlp_bwd(dg1, pre1, L1)
+            du1, dsh1, dg1 = self._tp_adjoint(1, u1, sh, g1, dst, src_csr, v1, n_local, e, L1["tpw"], True, grow)
+            drb = self._mlp_bwd(dg1, pre1, L1, pairs)
             del dg1, g1, pre1
             dh1_full = torch.empty(n_local, 9 * c, dtype=torch.float32, device=dev)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
@@ -307,8 +321,10 @@ class ForceEngine:
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 v0[:, off * c:(off + mm) * c] = torch.mm(dm0[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L0["ml"][l]).view(n_owned, mm * c)
-            _, dsh0, dg0 = self._tp_adjoint(0, u0, sh, g0, dst, src_csr, v0, n_local, e, L0["tpw"], False)
-            drb += self._mlp_bwd(dg0, pre0, L0)
+            _, dsh0, dg0 = self._tp_adjoint(0, u0, sh, g0, dst, src_csr, v0, n_local, e, L0["tpw"], False, grow)
+            drb += self._mlp_bwd(dg0, pre0, L0, pairs)
+            if pairs is not None:      # the pair's length gradient is carried by its representative edge
+                drb = torch.zeros(e, nb, dtype=torch.float32, device=dev).index_copy_(0, pairs[1], drb)
             dsh1 += dsh0
             dvec = torch.empty(e, 3, dtype=torch.float32, device=dev)
             _lib.check(lib.ictc_edge_geometry_backward(_lib.ptr(unit), _lib.ptr(length), rmax, nb, pcut, e,

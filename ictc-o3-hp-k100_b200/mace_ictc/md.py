@@ -24,7 +24,7 @@ ACCEL = 9.64853321e-3
 MASSES = {1: 1.008, 6: 12.011, 8: 15.999}
 
 
-def neighbor_list(pos, num_centres, lo, hi, box, periodic, cutoff):
+def neighbor_list(pos, num_centres, lo, hi, box, periodic, cutoff, return_keys=False):
     """Edges (src=j, dst=i) of the first ``num_centres`` rows, sorted by (dst, src, shift).
 
     pos [N,3] fp32 CUDA; lo/hi: bounds of the cell grid; box: periodic lengths; periodic: 3 flags.
@@ -56,7 +56,30 @@ def neighbor_list(pos, num_centres, lo, hi, box, periodic, cutoff):
         _lib.check(lib.ictc_neighbor_fill(pos.data_ptr(), n, num_centres, lo_c, hi_c, box_c, per_c, float(cutoff),
                                           rowptr.data_ptr(), e, _lib.ptr(src), _lib.ptr(dst), _lib.ptr(shifts),
                                           _lib.ptr(keys), scratch.data_ptr(), st), "ictc_neighbor_fill")
+    if return_keys:
+        return src, dst, shifts, rowptr, keys
     return src, dst, shifts, rowptr
+
+
+def edge_pairs(rowptr, dst, keys, num_centres):
+    """Radial pairing of a neighbour list (edge and reverse edge share their length): returns
+    (gate_row [E], rep_edge [U], other_edge [U]); see ``ictc_neighbor_pairs``."""
+    lib, dev = _lib.load(), dst.device
+    e = int(dst.numel())
+    rev = torch.empty(e, dtype=torch.int64, device=dev)
+    scan = torch.empty(e, dtype=torch.int64, device=dev)
+    gate_row = torch.empty(e, dtype=torch.int64, device=dev)
+    rep = torch.empty(e, dtype=torch.int64, device=dev)
+    other = torch.empty(e, dtype=torch.int64, device=dev)
+    num = torch.zeros(1, dtype=torch.int64, device=dev)
+    scratch = torch.empty(int(lib.ictc_scan_scratch_bytes(e)), dtype=torch.uint8, device=dev)
+    with _lib.on_device(dev):
+        _lib.check(lib.ictc_neighbor_pairs(rowptr.data_ptr(), _lib.ptr(dst), _lib.ptr(keys), num_centres, e, e,
+                                           rowptr.data_ptr() + 8 * num_centres, _lib.ptr(rev), _lib.ptr(scan),
+                                           _lib.ptr(gate_row), _lib.ptr(rep), _lib.ptr(other), num.data_ptr(),
+                                           scratch.data_ptr(), _lib.stream(dev)), "ictc_neighbor_pairs")
+    u = int(num.item())
+    return gate_row, rep[:u], other[:u]
 
 
 class StaticNeighborList:
@@ -82,6 +105,15 @@ class StaticNeighborList:
         self.shifts = torch.zeros(self.cap, 3, dtype=torch.float32, device=device)
         self.keys = torch.zeros(self.cap, dtype=torch.int64, device=device)
         self.overflow = torch.zeros(1, dtype=torch.int32, device=device)
+        # radial pairing: on one GPU every edge has its reverse in the list, so there are E/2 pairs
+        self.ucap = self.cap // 2 + 1024
+        self.rev = torch.zeros(self.cap, dtype=torch.int64, device=device)
+        self.pscan = torch.zeros(self.cap, dtype=torch.int64, device=device)
+        self.gate_row = torch.zeros(self.cap, dtype=torch.int64, device=device)
+        self.rep = torch.zeros(self.ucap, dtype=torch.int64, device=device)
+        self.other = torch.zeros(self.ucap, dtype=torch.int64, device=device)
+        self.num_unique = torch.zeros(1, dtype=torch.int64, device=device)
+        self.pscratch = torch.empty(int(lib.ictc_scan_scratch_bytes(self.cap)), dtype=torch.uint8, device=device)
 
     def build(self, pos_ext):
         """pos_ext [n+1, 3]: the real atoms followed by the dummy row (far away from every atom)."""
@@ -98,6 +130,14 @@ class StaticNeighborList:
         _lib.check(lib.ictc_neighbor_pad(self.rowptr.data_ptr() + 8 * n, self.cap, n, 0, self.src.data_ptr(),
                                          self.dst.data_ptr(), self.shifts.data_ptr(), self.overflow.data_ptr(), st),
                    "ictc_neighbor_pad")
+        _lib.check(lib.ictc_neighbor_pairs(self.rowptr.data_ptr(), self.dst.data_ptr(), self.keys.data_ptr(), n,
+                                           self.cap, self.ucap, self.rowptr.data_ptr() + 8 * n, self.rev.data_ptr(),
+                                           self.pscan.data_ptr(), self.gate_row.data_ptr(), self.rep.data_ptr(),
+                                           self.other.data_ptr(), self.num_unique.data_ptr(),
+                                           self.pscratch.data_ptr(), st), "ictc_neighbor_pairs")
+
+    def pairs(self):
+        return self.gate_row, self.rep, self.other
 
 
 def maxwell_boltzmann(masses: np.ndarray, temperature: float, seed: int) -> np.ndarray:
@@ -122,7 +162,7 @@ class MolecularDynamics:
     """
 
     def __init__(self, model, positions, atomic_numbers, box, *, dt=1.0, temperature=300.0, seed=0,
-                 velocities=None, distributed=False, use_engine=True):
+                 velocities=None, distributed=False, use_engine=True, share_gates=True):
         self.model = model
         dev = next(model.parameters()).device
         self.device = dev
@@ -159,6 +199,7 @@ class MolecularDynamics:
         self.launches = 0
         self.graph = None
         self._static = None
+        self.share_gates = bool(share_gates)     # evaluate the radial MLP once per (edge, reverse edge) pair
 
     # ------------------------------------------------------------------ forces
     def compute_forces(self):
@@ -169,10 +210,12 @@ class MolecularDynamics:
     def _forces_single(self):
         n = self.pos.shape[0]
         box = self.box.tolist()
-        src, dst, shifts, rowptr = neighbor_list(self.pos, n, [0, 0, 0], box, box, (1, 1, 1), self.cutoff)
+        src, dst, shifts, rowptr, keys = neighbor_list(self.pos, n, [0, 0, 0], box, box, (1, 1, 1), self.cutoff, True)
         self.num_edges = int(src.numel())
         if self.engine is not None:
-            energy, grad, _ = self.engine.energy_and_gradient(self.pos, self.species, src, dst, shifts, box, n, rowptr)
+            pairs = edge_pairs(rowptr, dst, keys, n) if self.share_gates else None
+            energy, grad, _ = self.engine.energy_and_gradient(self.pos, self.species, src, dst, shifts, box, n, rowptr,
+                                                              pairs=pairs)
             if self._static is not None:            # keep the buffers the recorded graph reads and writes
                 self._static["energy"].copy_(energy.reshape(1))
                 self.forces.copy_(grad).neg_()
@@ -204,12 +247,14 @@ class MolecularDynamics:
         ids = dom.local_ids()
         lo = (dom.lo - self.cutoff).tolist()
         hi = (dom.hi + self.cutoff).tolist()
-        src, dst, shifts, rowptr = neighbor_list(local, n_owned, lo, hi, self.box.tolist(), (0, 0, 0), self.cutoff)
+        src, dst, shifts, rowptr, keys = neighbor_list(local, n_owned, lo, hi, self.box.tolist(), (0, 0, 0),
+                                                       self.cutoff, True)
         self.num_edges = int(src.numel())
         n_local = local.shape[0]
         if self.engine is not None:
+            pairs = edge_pairs(rowptr, dst, keys, n_owned) if self.share_gates else None
             energy, grad, _ = self.engine.energy_and_gradient(local, self.species.index_select(0, ids), src, dst, None,
-                                                              self.box.tolist(), n_owned, rowptr, plan)
+                                                              self.box.tolist(), n_owned, rowptr, plan, pairs=pairs)
             total = torch.zeros_like(self.pos)
             total.index_add_(0, ids, grad)
             e = energy.reshape(1).clone()
@@ -254,7 +299,8 @@ class MolecularDynamics:
         st["nl"].build(st["pos_ext"])
         nl = st["nl"]
         energy, grad, _ = self.engine.energy_and_gradient(st["pos_ext"], st["species_ext"], nl.src, nl.dst, nl.shifts,
-                                                          self.box.tolist(), n, nl.rowptr, n_rows=n)
+                                                          self.box.tolist(), n, nl.rowptr, n_rows=n,
+                                                          pairs=nl.pairs() if self.share_gates else None)
         st["energy"].copy_(energy.reshape(1))
         self.forces.copy_(grad).neg_()
         self._kick(False)

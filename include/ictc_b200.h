@@ -95,6 +95,18 @@ int ictc_tp_graph_adjoint(int spec, int channels, int64_t num_nodes, int64_t num
                           const int64_t* src_rowptr, const int64_t* src_order, const float* mask,
                           const float* v, float* dx, float* dsh, float* dg, void* stream);
 
+/* Variants with a shared gate table: gate_row [E] names, for every edge, its row in g (several edges may
+ * share one row, see ictc_neighbor_pairs); NULL = row e.  dg of the adjoint stays per edge [E, np*C].
+ * No counterpart in the reference. */
+int ictc_tp_graph_forward_shared(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                                 const float* sh, const float* w, const float* g, const int64_t* gate_row,
+                                 const int64_t* src, const int64_t* dst_rowptr, const int64_t* dst_order,
+                                 const float* mask, float* out, void* stream);
+int ictc_tp_graph_adjoint_shared(int spec, int channels, int64_t num_nodes, int64_t num_edges, const float* x,
+                                 const float* sh, const float* w, const float* g, const int64_t* gate_row,
+                                 const int64_t* dst, const int64_t* src_rowptr, const int64_t* src_order,
+                                 const float* mask, const float* v, float* dx, float* dsh, float* dg, void* stream);
+
 /* ------------------------------------------------------------------ CSR topology
  * Counting sort of edges by an int64 key in [0, num_nodes): rowptr [N+1], order [E] (edge ids,
  * ascending inside a row, i.e. a stable sort), *sorted_flag (device int32) = 1 when the keys were
@@ -159,6 +171,18 @@ int ictc_neighbor_fill(const float* pos, int64_t num_atoms, int64_t num_centres,
  * This lets a whole MD step run without the host ever learning the edge count (CUDA-graph replay). */
 int ictc_neighbor_pad(const int64_t* count, int64_t capacity, int64_t pad_src, int64_t pad_dst, int64_t* src,
                       int64_t* dst, float* shifts, int32_t* overflow, void* stream);
+/* Radial pairing of a neighbour list built by ictc_neighbor_fill (edge_keys = its work array, untouched
+ * since): the edge (j -> i, S) and its reverse (i -> j, -S) have bitwise the same length, so length-only
+ * quantities (radial basis, gate MLP) are evaluated once per pair.  Outputs: gate_row [capacity] = pair id
+ * of every edge, rep_edge / other_edge [unique_capacity] = the representative edge of each pair and its
+ * reverse (-1 when the reverse is not in the list, e.g. the sender is a ghost), *num_unique (device) =
+ * number of pairs.  Rows of the pair table beyond *num_unique name the last edge slot (capacity - 1).
+ * rev, scan [capacity]: work arrays; scan_scratch: ictc_scan_scratch_bytes(capacity) bytes.
+ * No counterpart in the reference (it evaluates the radial MLP per directed edge). */
+int ictc_neighbor_pairs(const int64_t* rowptr, const int64_t* dst, const int64_t* edge_keys, int64_t num_centres,
+                        int64_t capacity, int64_t unique_capacity, const int64_t* count, int64_t* rev, int64_t* scan,
+                        int64_t* gate_row, int64_t* rep_edge, int64_t* other_edge, int64_t* num_unique,
+                        void* scan_scratch, void* stream);
 /* Half step of velocity Verlet: vel += dt/2 * F/m (A, fs, eV, amu); with drift != 0 also
  * pos += dt * vel, wrapped into [0, box) on axes with box > 0.  The reference leaves integration to
  * LAMMPS `fix nve` (examples/in.hco); this is the stand-alone equivalent. */
@@ -211,6 +235,13 @@ int ictc_radial_mlp_forward(int64_t num_edges, int num_basis, int num_out, const
 int ictc_radial_mlp_backward(int64_t num_edges, int num_basis, int num_out, const float* dgates, const float* w0t,
                              const float* w1t, const float* w2t, const float* w3t_split, const float* z1,
                              const float* z2, const float* z3, float* drb, void* stream);
+
+/* Backward of the gate MLP over a pair table: row u reads dgates[pair_a[u]] + dgates[pair_b[u]]
+ * (pair_b[u] < 0: single edge); z1..z3 and drb are indexed by u.  No counterpart in the reference. */
+int ictc_radial_mlp_backward_paired(int64_t num_rows, int num_basis, int num_out, const float* dgates,
+                                    const int64_t* pair_a, const int64_t* pair_b, const float* w0t, const float* w1t,
+                                    const float* w2t, const float* w3t_split, const float* z1, const float* z2,
+                                    const float* z3, float* drb, void* stream);
 
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).

@@ -128,3 +128,40 @@ def test_graph_replay_matches_eager_steps():
     assert float((fast.pos - eager.pos).abs().max()) < 2e-5
     assert float((fast.forces - eager.forces).abs().max()) < 2e-5 * float(eager.forces.abs().max())
     assert abs(float(fast.energy) - float(eager.energy)) < 1e-5 * abs(float(eager.energy))
+
+
+def test_radial_pairs_are_exact_and_do_not_change_forces():
+    """Every edge and its reverse share one gate row, their lengths are bitwise equal, and evaluating the
+    radial MLP per pair gives the same forces as evaluating it per directed edge."""
+    from mace_ictc import synthetic as S
+    from mace_ictc.hp import create_model
+    from mace_ictc.md import MolecularDynamics, edge_pairs, neighbor_list
+    pos, box, species = S.jittered_lattice(9, 7, 8, 2.15, 0.1, 12)
+    z = np.array([1, 6, 8])[species]
+    p = torch.as_tensor(pos).cuda()
+    n = p.shape[0]
+    src, dst, shifts, rowptr, keys = neighbor_list(p, n, [0, 0, 0], box, box, (1, 1, 1), 4.5, True)
+    gate_row, rep, other = edge_pairs(rowptr, dst, keys, n)
+    e = src.numel()
+    assert rep.numel() * 2 == e and bool((other >= 0).all())          # single GPU: all edges are paired
+    assert torch.equal(gate_row[rep], torch.arange(rep.numel(), device="cuda"))
+    assert torch.equal(gate_row[other], torch.arange(rep.numel(), device="cuda"))
+    assert torch.equal(src[other], dst[rep]) and torch.equal(dst[other], src[rep])
+    assert torch.equal(shifts[other], -shifts[rep])
+    vec = p[dst] - p[src] + shifts * torch.as_tensor(box, dtype=torch.float32, device="cuda")
+    length = vec.norm(dim=1)
+    assert torch.equal(length[rep], length[other])
+    # centres restricted to a prefix: edges whose sender is not a centre stay single
+    half = n // 2
+    s2, d2, sh2, rp2, k2 = neighbor_list(p, half, [0, 0, 0], box, box, (1, 1, 1), 4.5, True)
+    g2, r2, o2 = edge_pairs(rp2, d2, k2, half)
+    single = o2 < 0
+    assert bool((s2[r2[single]] >= half).all()) and bool((s2[r2[~single]] < half).all())
+    assert int(g2.max()) + 1 == r2.numel()
+    torch.manual_seed(3)
+    model = create_model(channels=64, lmax=2, cutoff=4.5, avg_num_neighbors=32.0)
+    a = MolecularDynamics(model, pos, z, box, seed=1, share_gates=True)
+    b = MolecularDynamics(model, pos, z, box, seed=1, share_gates=False)
+    fa, fb = a.compute_forces(), b.compute_forces()
+    assert float((fa - fb).abs().max()) < 5e-6 * float(fb.abs().max())
+    assert abs(float(a.energy) - float(b.energy)) < 1e-6 * abs(float(b.energy))
