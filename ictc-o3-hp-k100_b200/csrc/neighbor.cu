@@ -111,9 +111,10 @@ __global__ void nb_fill_kernel(NbGrid g, const float* __restrict__ pos, const in
   const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= centres) return;
   const int64_t begin = rowptr[i], end = rowptr[i + 1];
-  if (end > capacity) return;   // caller sees rowptr[centres] > capacity
+  if (end > capacity || begin > end) return;   // offsets must have been clamped to the capacity
   int64_t w = begin;
   nb_visit(g, pos, cell_start, cell_atoms, i, [&](int64_t j, int sx, int sy, int sz) {
+    if (w >= end) return;       // row truncated by the capacity clamp: extra neighbours are dropped
     // insertion into the sorted prefix [begin, w) by key (src, shift)
     const int64_t key = nb_key(j, sx, sy, sz);
     int64_t p = w;
@@ -133,6 +134,17 @@ __global__ void nb_fill_kernel(NbGrid g, const float* __restrict__ pos, const in
     shifts[3 * p + 1] = float((code / 3) % 3 - 1);
     shifts[3 * p + 2] = float(code % 3 - 1);
   }
+}
+
+// Clamps row offsets to the capacity of fixed-size edge buffers (rows beyond it become empty, the row that
+// straddles it is truncated) and raises *overflow when anything had to be clamped.  The flag is sticky (never
+// cleared here) so that a host that looks only every few steps still sees an earlier overflow.
+__global__ void nb_clamp_kernel(int64_t* rowptr, int64_t n1, int64_t capacity, int32_t* overflow) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n1) return;
+  const int64_t v = rowptr[i];
+  if (i == n1 - 1 && v > capacity) *overflow = 1;
+  if (v > capacity) rowptr[i] = capacity;
 }
 
 // Fills the unused tail [count, capacity) of fixed-capacity edge buffers with inert edges so that every
@@ -191,7 +203,8 @@ __global__ void nb_pair_assign_kernel(const int64_t* __restrict__ scan, const in
       const int64_t r = rev[e];
       const bool rep = r < 0 || e < r;
       const int64_t u = (rep ? scan[e] : scan[r]) - 1;
-      gate_row[e] = u;
+      // a pair table that is too small is reported through num_unique > unique_capacity; rows stay in range
+      gate_row[e] = u < unique_capacity ? u : (unique_capacity > 0 ? unique_capacity - 1 : 0);
       if (rep && u < unique_capacity) {
         rep_edge[u] = e;
         other_edge[u] = r;
@@ -338,6 +351,16 @@ int ictc_neighbor_fill(const float* pos, int64_t num_atoms, int64_t num_centres,
   nb_fill_kernel<<<(unsigned)((num_centres + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
       g, pos, s.cell_start, s.cell_atoms, num_centres, rowptr, capacity, src, dst, shifts, edge_keys);
   return finish_launch("neighbor_fill");
+}
+
+int ictc_neighbor_clamp(int64_t* rowptr, int64_t num_centres, int64_t capacity, int32_t* overflow, void* stream) {
+  if (num_centres < 0 || capacity < 0 || !rowptr || !overflow) {
+    set_error("neighbor_clamp: invalid arguments");
+    return ICTC_ERR_BAD_ARG;
+  }
+  nb_clamp_kernel<<<(unsigned)((num_centres + 1 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(rowptr, num_centres + 1,
+                                                                                             capacity, overflow);
+  return finish_launch("neighbor_clamp");
 }
 
 int ictc_neighbor_pad(const int64_t* count, int64_t capacity, int64_t pad_src, int64_t pad_dst, int64_t* src,

@@ -41,6 +41,7 @@ SIGNATURES = {
                                  C.POINTER(C.c_int), C.c_double, _P, _P, _P]),
     "ictc_neighbor_fill": (_I, [_P, _L, _L, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
                                 C.POINTER(C.c_int), C.c_double, _P, _L, _P, _P, _P, _P, _P, _P]),
+    "ictc_neighbor_clamp": (_I, [_P, _L, _L, _P, _P]),
     "ictc_neighbor_pad": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P]),
     "ictc_neighbor_pairs": (_I, [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_md_kick": (_I, [_L, C.c_float, _P, _P, _P, _P, _P, _I, _P]),

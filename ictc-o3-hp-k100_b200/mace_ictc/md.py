@@ -123,12 +123,14 @@ class StaticNeighborList:
                                            self.cutoff, self.rowptr.data_ptr(), self.scratch.data_ptr(), st),
                    "ictc_neighbor_count")
         _lib.check(lib.ictc_inclusive_scan_i64(self.rowptr.data_ptr(), n + 1, self.scan.data_ptr(), st), "scan")
+        _lib.check(lib.ictc_neighbor_clamp(self.rowptr.data_ptr(), n, self.cap - 1, self.overflow.data_ptr(), st),
+                   "ictc_neighbor_clamp")       # cap - 1: the last slot always stays an inert edge
         _lib.check(lib.ictc_neighbor_fill(pos_ext.data_ptr(), n1, n, self.lo, self.hi, self.box, self.per, self.cutoff,
                                           self.rowptr.data_ptr(), self.cap, self.src.data_ptr(), self.dst.data_ptr(),
                                           self.shifts.data_ptr(), self.keys.data_ptr(), self.scratch.data_ptr(), st),
                    "ictc_neighbor_fill")
         _lib.check(lib.ictc_neighbor_pad(self.rowptr.data_ptr() + 8 * n, self.cap, n, 0, self.src.data_ptr(),
-                                         self.dst.data_ptr(), self.shifts.data_ptr(), self.overflow.data_ptr(), st),
+                                         self.dst.data_ptr(), self.shifts.data_ptr(), None, st),
                    "ictc_neighbor_pad")
         _lib.check(lib.ictc_neighbor_pairs(self.rowptr.data_ptr(), self.dst.data_ptr(), self.keys.data_ptr(), n,
                                            self.cap, self.ucap, self.rowptr.data_ptr() + 8 * n, self.rev.data_ptr(),
@@ -305,23 +307,50 @@ class MolecularDynamics:
         self.forces.copy_(grad).neg_()
         self._kick(False)
 
-    def enable_graph(self, margin=1.04, warmup=2):
+    graph_rebuilds = 0
+
+    def run(self, steps, check_every=25, margin=1.10):
+        """Advance ``steps`` MD steps.  With a recorded graph the edge-capacity flag is read every
+        ``check_every`` steps; if the neighbour list outgrew the recorded buffers the block of steps is
+        repeated from a snapshot with a larger capacity (steps run after an overflow are invalid)."""
+        if self.graph is None:
+            for _ in range(steps):
+                self.step()
+            return
+        done = 0
+        while done < steps:
+            block = min(check_every, steps - done)
+            snap = (self.pos.clone(), self.vel.clone())
+            for _ in range(block):
+                self.graph.replay()
+            if self.check_overflow():
+                self.pos.copy_(snap[0])
+                self.vel.copy_(snap[1])
+                self.graph, self._static = None, None
+                self.compute_forces()
+                self.enable_graph(margin=margin)
+                self.graph_rebuilds += 1
+                continue
+            done += block
+
+    def enable_graph(self, margin=1.10, warmup=2, spare=1024):
         """Record the whole MD step (integration, neighbour build, forces) as one CUDA graph.
 
-        Edge buffers get a fixed capacity of ``margin`` times the current edge count; the device-side
+        Edge buffers get a fixed capacity of ``margin`` times the current edge count plus ``spare``; the device-side
         overflow flag is checked by ``check_overflow``.  Single-GPU, engine path only."""
         if self.world != 1 or self.engine is None:
             raise RuntimeError("graph replay covers the single-GPU engine path")
         if self.forces is None:
             self.compute_forces()
         n, dev = self.pos.shape[0], self.device
-        cap = int(self.num_edges * margin) + 1024
+        cap = int(self.num_edges * margin) + int(spare)
         pos_ext = torch.zeros(n + 1, 3, dtype=torch.float32, device=dev)
         pos_ext[n] = -1.0e6          # the dummy row sits far outside every cutoff sphere
         species_ext = torch.cat((self.species, self.species.new_zeros(1)))
         self._static = {"nl": StaticNeighborList(n, self.box.tolist(), self.cutoff, cap, dev), "pos_ext": pos_ext,
                         "species_ext": species_ext, "energy": torch.zeros(1, device=dev), "cap": cap}
         self.forces = self.forces.clone()
+        keep = (self.pos.clone(), self.vel.clone(), self.forces.clone(), self.energy.detach().clone().reshape(1))
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
@@ -332,6 +361,12 @@ class MolecularDynamics:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self._step_static()
+        # the warm-up steps advanced the state: put it back so that recording is invisible to the caller
+        self.pos.copy_(keep[0])
+        self.vel.copy_(keep[1])
+        self.forces.copy_(keep[2])
+        self._static["energy"].copy_(keep[3])
+        self._static["nl"].overflow.zero_()
         self.energy = self._static["energy"][0]
         return cap
 
@@ -339,7 +374,8 @@ class MolecularDynamics:
         """True when a replayed step needed more edges than the recorded capacity (results invalid)."""
         if self._static is None:
             return False
-        return bool(int(self._static["nl"].overflow.item()))
+        nl = self._static["nl"]
+        return bool(int(nl.overflow.item())) or int(nl.num_unique.item()) > nl.ucap
 
     # ------------------------------------------------------------------ integration
     def _kick(self, drift):

@@ -165,6 +165,11 @@ int ictc_neighbor_fill(const float* pos, int64_t num_atoms, int64_t num_centres,
                        const double* host_hi, const double* host_box, const int* host_periodic, double cutoff,
                        const int64_t* rowptr, int64_t capacity, int64_t* src, int64_t* dst, float* shifts,
                        int64_t* edge_keys, void* scratch, void* stream);
+/* Fixed-capacity edge buffers, step 0: after the prefix sum, clamp the row offsets to `capacity` so that
+ * ictc_neighbor_fill and every consumer stay inside the buffers; *overflow (device int32) is set to 1 when the
+ * list did not fit (rows were dropped: the caller must redo the step with a larger capacity) and is never
+ * cleared by this call, so the caller zeroes it and may poll it every few steps. */
+int ictc_neighbor_clamp(int64_t* rowptr, int64_t num_centres, int64_t capacity, int32_t* overflow, void* stream);
 /* Fixed-capacity edge buffers: after ictc_neighbor_fill, rows [*count, capacity) of src/dst/shifts are set
  * to the inert edge (pad_src, pad_dst, zero shift) and *overflow (device int32, may be NULL) tells
  * whether *count exceeded the capacity.  `count` is a DEVICE pointer (normally &rowptr[num_centres]).

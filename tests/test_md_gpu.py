@@ -118,9 +118,7 @@ def test_graph_replay_matches_eager_steps():
     p0, v0 = fast.pos.clone(), fast.vel.clone()
     cap = fast.enable_graph()
     assert cap > fast.num_edges
-    fast.pos.copy_(p0)          # recording advanced the state; rewind to the common start
-    fast.vel.copy_(v0)
-    fast.compute_forces()       # writes into the buffers the graph was recorded with
+    assert torch.equal(fast.pos, p0) and torch.equal(fast.vel, v0)     # recording leaves the state alone
     for _ in range(5):
         eager.step()
         fast.step()
@@ -128,6 +126,62 @@ def test_graph_replay_matches_eager_steps():
     assert float((fast.pos - eager.pos).abs().max()) < 2e-5
     assert float((fast.forces - eager.forces).abs().max()) < 2e-5 * float(eager.forces.abs().max())
     assert abs(float(fast.energy) - float(eager.energy)) < 1e-5 * abs(float(eager.energy))
+
+
+def test_edge_capacity_overflow_is_flagged_and_stays_in_bounds():
+    """A neighbour list that does not fit the fixed buffers is truncated inside them and raises the sticky
+    device flag; every index the consumers read stays in range."""
+    from mace_ictc import synthetic as S
+    from mace_ictc.md import StaticNeighborList, neighbor_list
+    pos, box, _ = S.jittered_lattice(8, 8, 8, 2.15, 0.1, 3)
+    dev = torch.device("cuda:0")
+    p = torch.as_tensor(pos, dtype=torch.float32, device=dev)
+    n = p.shape[0]
+    full = neighbor_list(p, n, [0, 0, 0], list(box), list(box), [1, 1, 1], 4.5)[0].shape[0]
+    cap = full // 2
+    nl = StaticNeighborList(n, list(box), 4.5, cap, dev)
+    ext = torch.cat((p, torch.full((1, 3), -1.0e6, device=dev)))
+    nl.build(ext)
+    if hasattr(nl, "pairs"):
+        nl.pairs()
+    torch.cuda.synchronize()
+    assert int(nl.overflow.item()) == 1
+    rp = nl.rowptr.cpu()
+    assert int(rp[-1]) == cap - 1 and bool((rp[1:] >= rp[:-1]).all())
+    assert int(nl.src.min()) >= 0 and int(nl.src.max()) <= n
+    assert int(nl.dst.min()) >= 0 and int(nl.dst.max()) < n
+    assert int(nl.gate_row.min()) >= 0 and int(nl.gate_row.max()) < nl.ucap
+    assert int(nl.rep.min()) >= 0 and int(nl.rep.max()) < cap and int(nl.other.max()) < cap
+    # a list that fits leaves the flag alone (it is sticky) and a fresh one reports no overflow
+    ok = StaticNeighborList(n, list(box), 4.5, full + 8, dev)
+    ok.build(ext)
+    torch.cuda.synchronize()
+    assert int(ok.overflow.item()) == 0 and int(ok.rowptr[-1]) == full
+
+
+def test_run_recovers_from_edge_capacity_overflow():
+    """``run`` notices that the recorded capacity was exceeded, re-records with a larger one and repeats the
+    block, so the trajectory equals the eager one."""
+    from mace_ictc import synthetic as S
+    from mace_ictc.hp import create_model
+    from mace_ictc.md import MolecularDynamics
+    torch.manual_seed(2)
+    # spacing 2.02: the (2,1,0) shell sits 0.017 A outside the cutoff, so thermal motion adds edges quickly
+    pos, box, species = S.jittered_lattice(8, 8, 8, 2.02, 0.02, 6)
+    z = np.array([1, 6, 8])[species]
+    model = create_model(channels=64, lmax=2, cutoff=4.5, avg_num_neighbors=32.0)
+    eager = MolecularDynamics(model, pos, z, box, dt=1.0, temperature=600.0, seed=4)
+    fast = MolecularDynamics(model, pos, z, box, dt=1.0, temperature=600.0, seed=4)
+    eager.compute_forces()
+    fast.compute_forces()
+    e0 = fast.num_edges
+    fast.enable_graph(margin=1.0, spare=16)
+    eager.run(12)
+    fast.run(12, check_every=4, margin=1.5)
+    assert eager.num_edges > e0 + 16, "the test system must outgrow the first capacity"
+    assert fast.graph_rebuilds >= 1 and not fast.check_overflow()
+    assert float((fast.pos - eager.pos).abs().max()) < 5e-5
+    assert float((fast.forces - eager.forces).abs().max()) < 5e-5 * float(eager.forces.abs().max())
 
 
 def test_radial_pairs_are_exact_and_do_not_change_forces():
