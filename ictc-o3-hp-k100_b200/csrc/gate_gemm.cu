@@ -1,0 +1,571 @@
+// Wide last layer of the radial gate MLP on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+//   forward :  gates[r, :] = act(z3[r, :]) @ W3^T            K = 64,    N = P*C (192 or 704)
+//   backward:  da3[r, :]   = (dG[a(r), :] + dG[b(r), :]) @ W3   K = P*C,  N = 64
+//
+// Reference: last `F.linear` of the interaction block's radial stack (mace_ictc/models/mace/layers.py:825-835),
+// tiled per edge chunk by ictc_o3/ops/streamed_gate_message.py:112-116, and its input gradient
+// (streamed_gate_message.py:224-260).  The reference forbids TF32 (ictc_o3/backends/k100/fp32_policy.py:6-11),
+// so every operand is split into two TF32-representable parts, x = x_big + x_small, and a product is the sum of
+// the three tcgen05.mma passes big*big + big*small + small*big into one fp32 TMEM accumulator.
+//
+// One persistent CTA per SM works on tiles of 128 rows.  Warp roles:
+//   warp 0      streams pre-packed 64-unit weight chunks (32 KB: big and small part) into a 2-stage ring
+//               with cp.async.bulk, completing on mbarriers;
+//   warp 1      allocates TMEM and issues the MMAs (one thread), committing to mbarriers;
+//   warps 2-5   epilogue: tcgen05.ld (thread = row), then coalesced row stores;
+//   warps 6-13  A-operand producers: global rows -> (activation | pair sum) -> split -> shared memory in the
+//               canonical K-major no-swizzle UMMA layout.
+// Shared-memory operand layout (both A and B): element (row r, k) of a [rows x 64] part lives at byte
+// (k / 4) * (rows * 16) + r * 16 + (k % 4) * 4, i.e. 16-byte K chunks, each chunk row-contiguous.  In descriptor
+// terms: 8-row core matrices of 128 contiguous bytes, stride between core matrices along the rows (SBO) 128 B,
+// stride between the two K chunks of one K = 8 MMA (LBO) rows * 16 B.
+// Every mbarrier wait is bounded; a wait that runs out raises the library's status word and the CTA leaves
+// through the common exit (TMEM is always released).
+#include "ictc_common.cuh"
+
+namespace ictc {
+namespace gg {
+
+constexpr int kRows = 128;             // tile rows = UMMA M
+constexpr int kK = 64;                 // hidden width
+constexpr int kChunk = 64;             // weight chunk: 64 units (N of the forward MMA, K step of the backward)
+constexpr int kPartBytes = kRows * kK * 4;          // 32 KB: one [128 x 64] operand part
+constexpr int kWPartBytes = kChunk * kK * 4;        // 16 KB
+constexpr int kWStageBytes = 2 * kWPartBytes;       // big + small
+constexpr int kThreads = 14 * 32;
+constexpr int kProducerWarp0 = 6, kProducerWarps = 8;
+constexpr int kEpilogueWarp0 = 2;
+constexpr long long kWaitCycles = 2000000000LL;     // ~1 s
+constexpr float kSiluScale = 1.6791767923989418f;
+constexpr int kStagePitch = 272;                    // bytes per staged output row (256 + 16: conflict-free)
+
+// instruction descriptor: D fp32, A and B TF32, both K-major, M = 128, N = 64
+constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(kChunk >> 3) << 17) | (uint32_t(kRows >> 4) << 24);
+
+__device__ __forceinline__ unsigned saddr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+  if (mbar_try(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try(bar, parity))
+    if (clock64() - start > kWaitCycles) return false;
+  return true;
+}
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, unsigned src, unsigned bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major, no swizzle (layout type 0), descriptor version 1
+__device__ __forceinline__ uint64_t smem_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+  return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) | (uint64_t(sbo_bytes >> 4) << 32) |
+         (1ull << 46);
+}
+__device__ __forceinline__ void umma_tf32(unsigned d_tmem, uint64_t a_desc, uint64_t b_desc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+  unsigned r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ float silu_s(float v) { return v / (1.f + expf(-v)) * kSiluScale; }
+
+// Writes one 16-byte K chunk (4 consecutive k of one row), split into its big and small parts.
+__device__ __forceinline__ void store_split(unsigned char* a_big, unsigned char* a_small, int row, int kc, float4 v) {
+  float4 b, s;
+  b.x = to_tf32(v.x); s.x = to_tf32(v.x - b.x);
+  b.y = to_tf32(v.y); s.y = to_tf32(v.y - b.y);
+  b.z = to_tf32(v.z); s.z = to_tf32(v.z - b.z);
+  b.w = to_tf32(v.w); s.w = to_tf32(v.w - b.w);
+  const int off = kc * (kRows * 16) + row * 16;
+  *reinterpret_cast<float4*>(a_big + off) = b;
+  *reinterpret_cast<float4*>(a_small + off) = s;
+}
+
+// The 24 MMAs of one [128 x 64] x [64 x 64]^T product: small*big, big*small, big*big over 8 K steps.
+__device__ __forceinline__ void issue_block(unsigned d_tmem, unsigned a_big, unsigned a_small, unsigned w_big,
+                                            unsigned w_small, bool first) {
+  const unsigned a_part[3] = {a_small, a_big, a_big};
+  const unsigned w_part[3] = {w_big, w_small, w_big};
+#pragma unroll
+  for (int p = 0; p < 3; ++p) {
+#pragma unroll
+    for (int ks = 0; ks < kK / 8; ++ks) {
+      const uint64_t ad = smem_desc(a_part[p] + ks * 2 * (kRows * 16), kRows * 16, 128);
+      const uint64_t bd = smem_desc(w_part[p] + ks * 2 * (kChunk * 16), kChunk * 16, 128);
+      umma_tf32(d_tmem, ad, bd, (first && p == 0 && ks == 0) ? 0u : 1u);
+    }
+  }
+}
+
+struct Args {
+  const float* in;        // forward: z3 [rows, 64]; backward: dgates [*, nout]
+  const float* w;         // packed chunks, 8192 floats each
+  float* out;             // forward: gates [rows, nout]; backward: da3 [rows, 64]
+  const int64_t* pair_a;  // backward, optional
+  const int64_t* pair_b;
+  int64_t rows;
+  int nout;
+  int act;                // forward: apply the scaled SiLU to the input
+  int* status;
+};
+
+struct Barriers {
+  unsigned long long w_full[2], w_empty[2], a_full[2], a_empty[2], d_full[4], d_empty[4];
+  unsigned tmem_base;
+  int failed;
+};
+
+__device__ __forceinline__ void give_up(Barriers* b, int* status, int code) {
+  b->failed = 1;
+  if (status) atomicExch(status, code);
+}
+
+// ------------------------------------------------------------------------------------------------
+// forward: shared memory = A[2][big|small] (128 KB) | W ring [2] (64 KB) | output staging (34 KB) | barriers
+constexpr int kFwdSmem = 2 * 2 * kPartBytes + 2 * kWStageBytes + kRows * kStagePitch + 256;
+
+__global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) {
+  extern __shared__ __align__(128) unsigned char gg_smem[];
+  unsigned char* a_buf = gg_smem;
+  unsigned char* w_buf = a_buf + 2 * 2 * kPartBytes;
+  unsigned char* stage = w_buf + 2 * kWStageBytes;
+  Barriers* bar = reinterpret_cast<Barriers*>(stage + kRows * kStagePitch);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunks = a.nout / kChunk;
+  const int64_t tiles = (a.rows + kRows - 1) / kRows;
+  const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(saddr(&bar->w_full[i]), 1);
+      mbar_init(saddr(&bar->w_empty[i]), 1);
+      mbar_init(saddr(&bar->a_full[i]), kProducerWarps * 32);
+      mbar_init(saddr(&bar->a_empty[i]), 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(saddr(&bar->d_full[i]), 1);
+      mbar_init(saddr(&bar->d_empty[i]), 128);
+    }
+    bar->failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&bar->tmem_base)),
+                 "r"(256u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = bar->tmem_base;
+
+  if (warp == 0) {
+    // ---- weight chunk stream
+    if (lane == 0) {
+      int64_t it = 0;
+      for (int64_t t = 0; t < my_tiles && !bar->failed; ++t) {
+        for (int c = 0; c < chunks; ++c, ++it) {
+          const int s = int(it & 1);
+          if (!mbar_wait(saddr(&bar->w_empty[s]), unsigned((it >> 1) & 1) ^ 1u)) { give_up(bar, a.status, 21); break; }
+          mbar_expect_tx(saddr(&bar->w_full[s]), kWStageBytes);
+          bulk_g2s(saddr(w_buf + s * kWStageBytes), a.w + int64_t(c) * (kWStageBytes / 4), kWStageBytes,
+                   saddr(&bar->w_full[s]));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue
+    if (lane == 0) {
+      int64_t it = 0;
+      for (int64_t t = 0; t < my_tiles && !bar->failed; ++t) {
+        const int ab = int(t & 1);
+        if (!mbar_wait(saddr(&bar->a_full[ab]), unsigned((t >> 1) & 1))) { give_up(bar, a.status, 22); break; }
+        tc_fence_after();
+        const unsigned a_big = saddr(a_buf + ab * 2 * kPartBytes), a_small = a_big + kPartBytes;
+        bool ok = true;
+        for (int c = 0; c < chunks; ++c, ++it) {
+          const int s = int(it & 1), d = int(it & 3);
+          if (!mbar_wait(saddr(&bar->w_full[s]), unsigned((it >> 1) & 1)) ||
+              !mbar_wait(saddr(&bar->d_empty[d]), unsigned((it >> 2) & 1) ^ 1u)) {
+            give_up(bar, a.status, 23);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const unsigned w_big = saddr(w_buf + s * kWStageBytes), w_small = w_big + kWPartBytes;
+          issue_block(tmem + d * kChunk, a_big, a_small, w_big, w_small, true);
+          umma_commit(saddr(&bar->w_empty[s]));
+          umma_commit(saddr(&bar->d_full[d]));
+        }
+        if (!ok) break;
+        umma_commit(saddr(&bar->a_empty[ab]));
+      }
+    }
+  } else if (warp < kProducerWarp0) {
+    // ---- epilogue: thread = row of the tile
+    const int q = warp & 3;                         // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;
+    unsigned char* mine = stage + row * kStagePitch;
+    int64_t it = 0;
+    for (int64_t t = 0; t < my_tiles; ++t) {
+      const int64_t grow = (blockIdx.x + t * gridDim.x) * kRows + row;
+      bool ok = true;
+      for (int c = 0; c < chunks; ++c, ++it) {
+        const int d = int(it & 3);
+        if (bar->failed || !mbar_wait(saddr(&bar->d_full[d]), unsigned((it >> 2) & 1))) {
+          give_up(bar, a.status, 24);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        float v0[32], v1[32];
+        const unsigned taddr = tmem + (unsigned(q * 32) << 16) + d * kChunk;
+        tmem_ld32(taddr, v0);
+        tmem_ld32(taddr + 32, v1);
+        tc_fence_before();
+        mbar_arrive(saddr(&bar->d_empty[d]));
+        bulk_wait_read();                            // my previous row store has left the staging row
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          *reinterpret_cast<float4*>(mine + j * 16) = make_float4(v0[4 * j], v0[4 * j + 1], v0[4 * j + 2], v0[4 * j + 3]);
+          *reinterpret_cast<float4*>(mine + 128 + j * 16) =
+              make_float4(v1[4 * j], v1[4 * j + 1], v1[4 * j + 2], v1[4 * j + 3]);
+        }
+        fence_async_smem();
+        if (grow < a.rows) bulk_s2g(a.out + grow * a.nout + c * kChunk, saddr(mine), kChunk * 4);
+        bulk_commit();
+      }
+      if (!ok) break;
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  } else {
+    // ---- A producers: z3 rows -> activation -> split
+    const int pw = warp - kProducerWarp0;
+    for (int64_t t = 0; t < my_tiles; ++t) {
+      const int ab = int(t & 1);
+      if (bar->failed) break;
+      if (!mbar_wait(saddr(&bar->a_empty[ab]), unsigned((t >> 1) & 1) ^ 1u)) { give_up(bar, a.status, 25); break; }
+      unsigned char* big = a_buf + ab * 2 * kPartBytes;
+      unsigned char* small = big + kPartBytes;
+      const int64_t row0 = (blockIdx.x + t * gridDim.x) * kRows;
+      float4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int qi = pw * 8 + j, row = (qi >> 2) * 8 + (lane & 7), kc = (qi & 3) * 4 + (lane >> 3);
+        const int64_t g = row0 + row;
+        v[j] = g < a.rows ? __ldg(reinterpret_cast<const float4*>(a.in + g * kK + kc * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int qi = pw * 8 + j, row = (qi >> 2) * 8 + (lane & 7), kc = (qi & 3) * 4 + (lane >> 3);
+        float4 x = v[j];
+        if (a.act) { x.x = silu_s(x.x); x.y = silu_s(x.y); x.z = silu_s(x.z); x.w = silu_s(x.w); }
+        store_split(big, small, row, kc, x);
+      }
+      fence_async_smem();
+      mbar_arrive(saddr(&bar->a_full[ab]));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward: shared memory = A ring [2][big|small] (128 KB) | W ring [2] (64 KB) | barriers.  One accumulator
+// [128 x 64] per tile (two TMEM slots alternate between tiles); K runs over the nout / 64 chunks.
+constexpr int kBwdSmem = 2 * 2 * kPartBytes + 2 * kWStageBytes + 256;
+
+__global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a) {
+  extern __shared__ __align__(128) unsigned char gg_smem[];
+  unsigned char* a_buf = gg_smem;
+  unsigned char* w_buf = a_buf + 2 * 2 * kPartBytes;
+  Barriers* bar = reinterpret_cast<Barriers*>(w_buf + 2 * kWStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunks = a.nout / kChunk;
+  const int64_t tiles = (a.rows + kRows - 1) / kRows;
+  const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(saddr(&bar->w_full[i]), 1);
+      mbar_init(saddr(&bar->w_empty[i]), 1);
+      mbar_init(saddr(&bar->a_full[i]), kProducerWarps * 32);
+      mbar_init(saddr(&bar->a_empty[i]), 1);
+      mbar_init(saddr(&bar->d_full[i]), 1);
+      mbar_init(saddr(&bar->d_empty[i]), 128);
+    }
+    bar->failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&bar->tmem_base)),
+                 "r"(128u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = bar->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int64_t it = 0;
+      for (int64_t t = 0; t < my_tiles && !bar->failed; ++t) {
+        for (int c = 0; c < chunks; ++c, ++it) {
+          const int s = int(it & 1);
+          if (!mbar_wait(saddr(&bar->w_empty[s]), unsigned((it >> 1) & 1) ^ 1u)) { give_up(bar, a.status, 31); break; }
+          mbar_expect_tx(saddr(&bar->w_full[s]), kWStageBytes);
+          bulk_g2s(saddr(w_buf + s * kWStageBytes), a.w + int64_t(c) * (kWStageBytes / 4), kWStageBytes,
+                   saddr(&bar->w_full[s]));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int64_t it = 0;
+      for (int64_t t = 0; t < my_tiles && !bar->failed; ++t) {
+        const int d = int(t & 1);
+        if (!mbar_wait(saddr(&bar->d_empty[d]), unsigned((t >> 1) & 1) ^ 1u)) { give_up(bar, a.status, 32); break; }
+        bool ok = true;
+        for (int c = 0; c < chunks; ++c, ++it) {
+          const int s = int(it & 1);
+          if (!mbar_wait(saddr(&bar->w_full[s]), unsigned((it >> 1) & 1)) ||
+              !mbar_wait(saddr(&bar->a_full[s]), unsigned((it >> 1) & 1))) {
+            give_up(bar, a.status, 33);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const unsigned a_big = saddr(a_buf + s * 2 * kPartBytes), a_small = a_big + kPartBytes;
+          const unsigned w_big = saddr(w_buf + s * kWStageBytes), w_small = w_big + kWPartBytes;
+          issue_block(tmem + d * kChunk, a_big, a_small, w_big, w_small, c == 0);
+          umma_commit(saddr(&bar->w_empty[s]));
+          umma_commit(saddr(&bar->a_empty[s]));
+        }
+        if (!ok) break;
+        umma_commit(saddr(&bar->d_full[d]));
+      }
+    }
+  } else if (warp < kProducerWarp0) {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    for (int64_t t = 0; t < my_tiles; ++t) {
+      const int d = int(t & 1);
+      const int64_t grow = (blockIdx.x + t * gridDim.x) * kRows + row;
+      if (bar->failed || !mbar_wait(saddr(&bar->d_full[d]), unsigned((t >> 1) & 1))) { give_up(bar, a.status, 34); break; }
+      tc_fence_after();
+      float v0[32], v1[32];
+      const unsigned taddr = tmem + (unsigned(q * 32) << 16) + d * kChunk;
+      tmem_ld32(taddr, v0);
+      tmem_ld32(taddr + 32, v1);
+      tc_fence_before();
+      mbar_arrive(saddr(&bar->d_empty[d]));
+      if (grow < a.rows) {
+        float4* o = reinterpret_cast<float4*>(a.out + grow * kK);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j] = make_float4(v0[4 * j], v0[4 * j + 1], v0[4 * j + 2], v0[4 * j + 3]);
+          o[8 + j] = make_float4(v1[4 * j], v1[4 * j + 1], v1[4 * j + 2], v1[4 * j + 3]);
+        }
+      }
+    }
+  } else {
+    // ---- A producers: (dG[a] + dG[b]) rows, one 64-column chunk per ring stage
+    const int pw = warp - kProducerWarp0;
+    int64_t it = 0;
+    for (int64_t t = 0; t < my_tiles; ++t) {
+      const int64_t row0 = (blockIdx.x + t * gridDim.x) * kRows;
+      // this thread's two rows of the tile (see the mapping below: qi >> 2 takes two values per warp)
+      int64_t ra[2], rb[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int row = (pw * 2 + h) * 8 + (lane & 7);
+        const int64_t g = row0 + row;
+        ra[h] = g < a.rows ? (a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g) : -1;
+        rb[h] = (g < a.rows && a.pair_b) ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
+      }
+      bool ok = true;
+      for (int c = 0; c < chunks; ++c, ++it) {
+        const int s = int(it & 1);
+        if (bar->failed || !mbar_wait(saddr(&bar->a_empty[s]), unsigned((it >> 1) & 1) ^ 1u)) {
+          give_up(bar, a.status, 35);
+          ok = false;
+          break;
+        }
+        unsigned char* big = a_buf + s * 2 * kPartBytes;
+        unsigned char* small = big + kPartBytes;
+        float4 va[8], vb[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int h = j >> 2, kc = (j & 3) * 4 + (lane >> 3);
+          const int64_t col = int64_t(c) * kChunk + kc * 4;
+          va[j] = ra[h] >= 0 ? __ldg(reinterpret_cast<const float4*>(a.in + ra[h] * a.nout + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          vb[j] = rb[h] >= 0 ? __ldg(reinterpret_cast<const float4*>(a.in + rb[h] * a.nout + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int h = j >> 2, kc = (j & 3) * 4 + (lane >> 3), row = (pw * 2 + h) * 8 + (lane & 7);
+          store_split(big, small, row, kc, make_float4(va[j].x + vb[j].x, va[j].y + vb[j].y, va[j].z + vb[j].z, va[j].w + vb[j].w));
+        }
+        fence_async_smem();
+        mbar_arrive(saddr(&bar->a_full[s]));
+      }
+      if (!ok) break;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+  }
+}
+
+// Packs W3 [nout, 64] into 64-unit chunks in the shared-memory operand layout, big part then small part.
+// transpose = 0 (forward B operand):  block(n, k) = W3[c*64 + n][k]
+// transpose = 1 (backward B operand): block(n, k) = W3[c*64 + k][n]
+__global__ void gate_pack_kernel(int nout, const float* __restrict__ w, int transpose, float* out) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= nout * kK) return;
+  const int c = idx / (kChunk * kK), rem = idx % (kChunk * kK), n = rem / kK, k = rem % kK;
+  const float v = transpose ? w[(c * kChunk + k) * kK + n] : w[(c * kChunk + n) * kK + k];
+  const float big = to_tf32(v), small = to_tf32(v - big);
+  const int off = (k / 4) * (kChunk * 4) + n * 4 + (k % 4);
+  out[c * (2 * kChunk * kK) + off] = big;
+  out[c * (2 * kChunk * kK) + kChunk * kK + off] = small;
+}
+
+static int grid_size(int64_t rows) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t tiles = (rows + kRows - 1) / kRows;
+  return int(tiles < sms ? tiles : sms);
+}
+
+static int check_common(int64_t rows, int nout) {
+  if (rows < 0 || nout < kChunk || nout % kChunk) {
+    set_error("gate gemm: the gate width must be a positive multiple of 64 (got %d)", nout);
+    return ICTC_ERR_BAD_SPEC;
+  }
+  return ICTC_OK;
+}
+
+}  // namespace gg
+}  // namespace ictc
+
+using namespace ictc;
+
+extern "C" {
+
+int ictc_gate_pack_weights(int num_out, const float* w3, int transpose, float* packed, void* stream) {
+  if (int rc = gg::check_common(0, num_out)) return rc;
+  if (!w3 || !packed) { set_error("gate pack: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  const int n = num_out * gg::kK;
+  gg::gate_pack_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(num_out, w3, transpose ? 1 : 0, packed);
+  return finish_launch("gate_pack");
+}
+
+int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const float* w_packed, float* gates,
+                           int apply_silu, void* stream) {
+  if (int rc = gg::check_common(num_rows, num_out)) return rc;
+  if (num_rows == 0) return ICTC_OK;
+  if (!z3 || !w_packed || !gates) { set_error("gate gemm forward: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  if ((reinterpret_cast<uintptr_t>(z3) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(gates)) & 15) {
+    set_error("gate gemm forward: buffers must be 16-byte aligned");
+    return ICTC_ERR_BAD_ARG;
+  }
+  static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_forward_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kFwdSmem);
+  if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
+  gg::Args a{};
+  a.in = z3; a.w = w_packed; a.out = gates; a.rows = num_rows; a.nout = num_out; a.act = apply_silu ? 1 : 0;
+  a.status = kernel_status_word();
+  gg::gate_gemm_forward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kFwdSmem, (cudaStream_t)stream>>>(a);
+  return finish_launch("gate_gemm_forward");
+}
+
+int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, const int64_t* pair_a,
+                            const int64_t* pair_b, const float* w_packed_t, float* da3, void* stream) {
+  if (int rc = gg::check_common(num_rows, num_out)) return rc;
+  if (num_rows == 0) return ICTC_OK;
+  if (!dgates || !w_packed_t || !da3) { set_error("gate gemm backward: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  if ((reinterpret_cast<uintptr_t>(dgates) | reinterpret_cast<uintptr_t>(w_packed_t) | reinterpret_cast<uintptr_t>(da3)) & 15) {
+    set_error("gate gemm backward: buffers must be 16-byte aligned");
+    return ICTC_ERR_BAD_ARG;
+  }
+  static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_backward_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kBwdSmem);
+  if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
+  gg::Args a{};
+  a.in = dgates; a.w = w_packed_t; a.out = da3; a.pair_a = pair_a; a.pair_b = pair_b; a.rows = num_rows; a.nout = num_out;
+  a.status = kernel_status_word();
+  gg::gate_gemm_backward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kBwdSmem, (cudaStream_t)stream>>>(a);
+  return finish_launch("gate_gemm_backward");
+}
+
+}  // extern "C"

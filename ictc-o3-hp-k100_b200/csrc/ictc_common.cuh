@@ -9,6 +9,9 @@ namespace ictc {
 
 void set_error(const char* fmt, ...);
 
+// Device address of the status word that kernels with bounded waits report through (ictc_kernel_status).
+int* kernel_status_word();
+
 // Records a CUDA launch error (if any) and maps it to the C-ABI return code.
 inline int finish_launch(const char* what) {
   cudaError_t err = cudaGetLastError();

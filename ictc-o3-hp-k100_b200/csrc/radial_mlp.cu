@@ -134,6 +134,7 @@ struct MlpArgs {
   const int64_t* pair_a;  // optional: row u of the MLP reads dgates[pair_a[u]] + dgates[pair_b[u]] (pair_b < 0: none)
   const int64_t* pair_b;
   float* drb;           // [E, nb]
+  const float* da3;     // backward, optional [E, 64]: gradient of the last hidden activation computed elsewhere
   int64_t E;
   int nb, nout;
 };
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(kMlpWarps * 32, 1) radial_mlp_forward_kernel(M
     const int64_t r_lo = row0 + g, r_hi = row0 + g + 8;
     const bool ok_lo = r_lo < a.E, ok_hi = r_hi < a.E;
     // first chunk of the last layer is staged while the hidden layers run
-    stage_split_async(w3s, a.w3, kH);
+    if (a.gates) stage_split_async(w3s, a.w3, kH);
     // ---- layer 0: radial basis rows into the warp buffer (zero padded to 8 columns)
     for (int idx = lane; idx < 16 * 8; idx += 32) {
       const int r = idx / 8, k = idx % 8;
@@ -204,6 +205,7 @@ __global__ void __launch_bounds__(kMlpWarps * 32, 1) radial_mlp_forward_kernel(M
         if (ok_hi) *reinterpret_cast<float2*>(a.z3 + r_hi * kH + nt * 8 + 2 * t) = make_float2(acc[nt][2], acc[nt][3]);
       }
     }
+    if (!a.gates) continue;                              // hidden layers only: the wide layer runs elsewhere
     store_c(mine, g, t, acc);
     __syncwarp();
     // ---- layer 3: A fragments of the last hidden activation stay in registers for all chunks
@@ -268,13 +270,23 @@ __global__ void __launch_bounds__(kMlpWarps * 32, 1) radial_mlp_backward_kernel(
     const int64_t c_lo = ok_lo ? r_lo : 0, c_hi = ok_hi ? r_hi : 0;   // clamped rows for loads
     const int64_t da_lo = a.pair_a ? a.pair_a[c_lo] : c_lo, da_hi = a.pair_a ? a.pair_a[c_hi] : c_hi;
     const int64_t db_lo = a.pair_b ? a.pair_b[c_lo] : -1, db_hi = a.pair_b ? a.pair_b[c_hi] : -1;
-    stage_split_async(w3s, a.w3, a.nout);
-    wait_async();
-    __syncthreads();
-    // ---- da3 = dgates @ W3 : K = nout streamed in 64-wide chunks, A fragments straight from global
     float acc[8][4];
     zero_acc<8>(acc);
-    for (int ch = 0; ch < chunks; ++ch) {
+    if (a.da3) {
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int col = nt * 8 + 2 * t;
+        const float2 lo = ok_lo ? *reinterpret_cast<const float2*>(a.da3 + r_lo * kH + col) : make_float2(0.f, 0.f);
+        const float2 hi = ok_hi ? *reinterpret_cast<const float2*>(a.da3 + r_hi * kH + col) : make_float2(0.f, 0.f);
+        acc[nt][0] = lo.x; acc[nt][1] = lo.y; acc[nt][2] = hi.x; acc[nt][3] = hi.y;
+      }
+    } else {
+      stage_split_async(w3s, a.w3, a.nout);
+      wait_async();
+      __syncthreads();
+    }
+    // ---- da3 = dgates @ W3 : K = nout streamed in 64-wide chunks, A fragments straight from global
+    for (int ch = 0; ch < (a.da3 ? 0 : chunks); ++ch) {
       const float2* wc = w3s + (ch & 1) * kH * kWS;
       if (ch + 1 < chunks) stage_split_async(w3s + ((ch + 1) & 1) * kH * kWS, a.w3 + (ch + 1) * kH, a.nout);
 #pragma unroll
@@ -392,7 +404,10 @@ int ictc_radial_mlp_forward(int64_t num_edges, int num_basis, int num_out, const
                             float* z2, float* z3, void* stream) {
   if (int rc = mlp_check(num_edges, num_basis, num_out)) return rc;
   if (num_edges == 0) return ICTC_OK;
-  if (!rb || !w0 || !w1 || !w2 || !w3_split || !gates) { set_error("radial mlp: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  if (!rb || !w0 || !w1 || !w2 || (gates && !w3_split) || (!gates && !z3)) {
+    set_error("radial mlp: NULL buffer");
+    return ICTC_ERR_BAD_ARG;
+  }
   MlpArgs a{};
   a.rb = rb; a.w0 = w0; a.w1 = w1; a.w2 = w2; a.w3 = reinterpret_cast<const float2*>(w3_split); a.gates = gates; a.z1 = z1; a.z2 = z2; a.z3 = z3;
   a.E = num_edges; a.nb = num_basis; a.nout = num_out;
@@ -418,18 +433,46 @@ int ictc_radial_mlp_backward(int64_t num_edges, int num_basis, int num_out, cons
                                          w3t_split, z1, z2, z3, drb, stream);
 }
 
+static int mlp_backward_launch(int64_t num_edges, int num_basis, int num_out, const float* dgates, const float* da3,
+                               const int64_t* pair_a, const int64_t* pair_b, const float* w0t, const float* w1t,
+                               const float* w2t, const float* w3t_split, const float* z1, const float* z2,
+                               const float* z3, float* drb, void* stream);
+
 int ictc_radial_mlp_backward_paired(int64_t num_edges, int num_basis, int num_out, const float* dgates,
                                     const int64_t* pair_a, const int64_t* pair_b, const float* w0t, const float* w1t,
                                     const float* w2t, const float* w3t_split, const float* z1, const float* z2,
                                     const float* z3, float* drb, void* stream) {
+  if (!dgates || !w3t_split) { set_error("radial mlp backward: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  return mlp_backward_launch(num_edges, num_basis, num_out, dgates, nullptr, pair_a, pair_b, w0t, w1t, w2t, w3t_split,
+                             z1, z2, z3, drb, stream);
+}
+
+int ictc_radial_mlp_hidden_forward(int64_t num_edges, int num_basis, const float* rb, const float* w0, const float* w1,
+                                   const float* w2, float* z1, float* z2, float* z3, void* stream) {
+  return ictc_radial_mlp_forward(num_edges, num_basis, kH, rb, w0, w1, w2, nullptr, nullptr, z1, z2, z3, stream);
+}
+
+int ictc_radial_mlp_hidden_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0t,
+                                    const float* w1t, const float* w2t, const float* z1, const float* z2,
+                                    const float* z3, float* drb, void* stream) {
+  if (!da3) { set_error("radial mlp hidden backward: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  return mlp_backward_launch(num_edges, num_basis, kH, nullptr, da3, nullptr, nullptr, w0t, w1t, w2t, nullptr, z1, z2,
+                             z3, drb, stream);
+}
+
+static int mlp_backward_launch(int64_t num_edges, int num_basis, int num_out, const float* dgates, const float* da3,
+                               const int64_t* pair_a, const int64_t* pair_b, const float* w0t, const float* w1t,
+                               const float* w2t, const float* w3t_split, const float* z1, const float* z2,
+                               const float* z3, float* drb, void* stream) {
   if (int rc = mlp_check(num_edges, num_basis, num_out)) return rc;
   if (num_edges == 0) return ICTC_OK;
-  if (!dgates || !w0t || !w1t || !w2t || !w3t_split || !z1 || !z2 || !z3 || !drb) {
+  if (!w0t || !w1t || !w2t || !z1 || !z2 || !z3 || !drb) {
     set_error("radial mlp backward: NULL buffer");
     return ICTC_ERR_BAD_ARG;
   }
   MlpArgs a{};
   a.w0 = w0t; a.w1 = w1t; a.w2 = w2t; a.w3 = reinterpret_cast<const float2*>(w3t_split); a.dgates = dgates; a.drb = drb;
+  a.da3 = da3;
   a.pair_a = pair_a; a.pair_b = pair_b;
   a.z1 = const_cast<float*>(z1); a.z2 = const_cast<float*>(z2); a.z3 = const_cast<float*>(z3);
   a.E = num_edges; a.nb = num_basis; a.nout = num_out;

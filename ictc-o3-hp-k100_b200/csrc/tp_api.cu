@@ -39,7 +39,7 @@ static const TpOps* find_ops(int spec) {
 }
 
 // Device address of the status word of the current device (looked up once per device).
-static int* status_word() {
+int* kernel_status_word() {
   static int* cache[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
@@ -122,7 +122,7 @@ int ictc_tp_edge_adjoint(int spec, int channels, int64_t num_edges, const float*
   if (!check(x && sh && g && v, "x, sh, g, v must not be NULL")) return ICTC_ERR_BAD_ARG;
   TpArgs a{};
   a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.v = v; a.dx = dx; a.dsh = dsh; a.dg = dg;
-  a.E = num_edges; a.N = num_edges; a.C = channels; a.status = status_word();
+  a.E = num_edges; a.N = num_edges; a.C = channels; a.status = kernel_status_word();
   return o->adjoint(a, false, (cudaStream_t)stream);
 }
 
@@ -151,7 +151,7 @@ int ictc_tp_graph_forward_shared(int spec, int channels, int64_t num_nodes, int6
   if (num_edges > 0 && !check(x && sh && g && src, "x, sh, g, src must not be NULL")) return ICTC_ERR_BAD_ARG;
   TpArgs a{};
   a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.out = out; a.nbr = src; a.rowptr = dst_rowptr;
-  a.grow = gate_row; a.order = dst_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = status_word();
+  a.grow = gate_row; a.order = dst_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = kernel_status_word();
   return o->graph_forward(a, (cudaStream_t)stream);
 }
 
@@ -180,7 +180,7 @@ int ictc_tp_graph_adjoint_shared(int spec, int channels, int64_t num_nodes, int6
   if (num_edges > 0 && !check(sh && g && dst && v, "sh, g, dst, v must not be NULL")) return ICTC_ERR_BAD_ARG;
   TpArgs a{};
   a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.v = v; a.dx = dx; a.dsh = dsh; a.dg = dg; a.nbr = dst;
-  a.grow = gate_row; a.rowptr = src_rowptr; a.order = src_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = status_word();
+  a.grow = gate_row; a.rowptr = src_rowptr; a.order = src_order; a.E = num_edges; a.N = num_nodes; a.C = channels; a.status = kernel_status_word();
   return o->adjoint(a, true, (cudaStream_t)stream);
 }
 

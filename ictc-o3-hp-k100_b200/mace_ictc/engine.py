@@ -41,6 +41,7 @@ class ForceEngine:
         self._versions = None
         self._spec = {0: _lib.tp_spec(0, 2, 2), 1: _lib.tp_spec(2, 2, 2)}
         self.fused_mlp = True
+        self.gate_gemm = True    # last MLP layer on the tcgen05 tensor cores (False: single mma.sync kernel)
         self.profile = None      # list of (kernel name, start event, end event) when enabled by a benchmark
         self.refresh()
 
@@ -69,6 +70,9 @@ class ForceEngine:
                 L["ml_t"] = [w.t().contiguous() for w in L["ml"]]
                 L["w3_split"] = self._split(L["fc"][-1])
                 L["w3t_split"] = self._split(L["fc_t"][-1])
+                if self._fused_mlp_ok(L) and self.gate_gemm:
+                    L["w3_umma"] = self._pack_umma(L["fc"][-1], 0)
+                    L["w3t_umma"] = self._pack_umma(L["fc"][-1], 1)
                 wsc = inter.self_connection.weights["0"]                                 # [S, C(out), C(in)]
                 s = wsc.shape[0]
                 L["sc_fwd"] = wsc.permute(2, 0, 1).reshape(c, s * c).contiguous()          # x @ -> [n, S*C(out)]
@@ -89,6 +93,14 @@ class ForceEngine:
         with _lib.on_device(w.device):
             _lib.check(self.lib.ictc_split_tf32(w.numel(), w.data_ptr(), out.data_ptr(), _lib.stream(w.device)),
                        "split_tf32")
+        return out
+
+    def _pack_umma(self, w, transpose):
+        """Last-layer weights in the shared-memory operand layout of the tcgen05 gate GEMM kernels."""
+        out = torch.empty(2 * w.numel(), dtype=torch.float32, device=w.device)
+        with _lib.on_device(w.device):
+            _lib.check(self.lib.ictc_gate_pack_weights(w.shape[0], w.data_ptr(), transpose, out.data_ptr(),
+                                                       _lib.stream(w.device)), "gate_pack_weights")
         return out
 
     # ---------------------------------------------------------------- small launch helpers
@@ -120,6 +132,17 @@ class ForceEngine:
             gates = torch.empty(e, nout, dtype=torch.float32, device=self.dev)
             pre = [torch.empty(e, 64, dtype=torch.float32, device=self.dev) for _ in range(3)]
             t0 = self._mark()
+            if "w3_umma" in L:
+                _lib.check(self.lib.ictc_radial_mlp_hidden_forward(e, rb.shape[1], _lib.ptr(rb), fc[0].data_ptr(),
+                                                                   fc[1].data_ptr(), fc[2].data_ptr(), _lib.ptr(pre[0]),
+                                                                   _lib.ptr(pre[1]), _lib.ptr(pre[2]), self._st()),
+                           "radial_mlp_hidden_forward")
+                self._done(f"radial_mlp_hidden_forward_{nout}", t0)
+                t0 = self._mark()
+                _lib.check(self.lib.ictc_gate_gemm_forward(e, nout, _lib.ptr(pre[2]), L["w3_umma"].data_ptr(),
+                                                           _lib.ptr(gates), 1, self._st()), "gate_gemm_forward")
+                self._done(f"gate_gemm_forward_{nout}", t0)
+                return gates, pre
             _lib.check(self.lib.ictc_radial_mlp_forward(e, rb.shape[1], nout, _lib.ptr(rb), fc[0].data_ptr(),
                                                         fc[1].data_ptr(), fc[2].data_ptr(), L["w3_split"].data_ptr(),
                                                         _lib.ptr(gates), _lib.ptr(pre[0]), _lib.ptr(pre[1]),
@@ -147,6 +170,20 @@ class ForceEngine:
             drb = torch.empty(e, nb, dtype=torch.float32, device=self.dev)
             t0 = self._mark()
             pa, pb = (None, None) if pairs is None else (pairs[1], pairs[2])
+            if "w3t_umma" in L:
+                da3 = torch.empty(e, 64, dtype=torch.float32, device=self.dev)
+                _lib.check(self.lib.ictc_gate_gemm_backward(e, dgates.shape[1], _lib.ptr(dgates), _lib.ptr(pa),
+                                                            _lib.ptr(pb), L["w3t_umma"].data_ptr(), _lib.ptr(da3),
+                                                            self._st()), "gate_gemm_backward")
+                self._done(f"gate_gemm_backward_{dgates.shape[1]}", t0)
+                t0 = self._mark()
+                _lib.check(self.lib.ictc_radial_mlp_hidden_backward(e, nb, _lib.ptr(da3), ft[0].data_ptr(),
+                                                                    ft[1].data_ptr(), ft[2].data_ptr(),
+                                                                    _lib.ptr(pre[0]), _lib.ptr(pre[1]),
+                                                                    _lib.ptr(pre[2]), _lib.ptr(drb), self._st()),
+                           "radial_mlp_hidden_backward")
+                self._done(f"radial_mlp_hidden_backward_{dgates.shape[1]}", t0)
+                return drb
             _lib.check(self.lib.ictc_radial_mlp_backward_paired(e, nb, dgates.shape[1], _lib.ptr(dgates), _lib.ptr(pa),
                                                                 _lib.ptr(pb), ft[0].data_ptr(),
                                                                 ft[1].data_ptr(), ft[2].data_ptr(),

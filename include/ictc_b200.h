@@ -248,6 +248,30 @@ int ictc_radial_mlp_backward_paired(int64_t num_rows, int num_basis, int num_out
                                     const float* w2t, const float* w3t_split, const float* z1, const float* z2,
                                     const float* z3, float* drb, void* stream);
 
+/* The same MLP with the wide last layer taken out: the three hidden layers only (pre-activations z1..z3 are
+ * the output of the forward; the backward starts from da3 = d loss / d silu(z3), [num_edges, 64]).  The last
+ * layer then runs as ictc_gate_gemm_forward / ictc_gate_gemm_backward on the tcgen05 tensor cores. */
+int ictc_radial_mlp_hidden_forward(int64_t num_edges, int num_basis, const float* rb, const float* w0, const float* w1,
+                                   const float* w2, float* z1, float* z2, float* z3, void* stream);
+int ictc_radial_mlp_hidden_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0t,
+                                    const float* w1t, const float* w2t, const float* z1, const float* z2,
+                                    const float* z3, float* drb, void* stream);
+
+/* Last layer of the gate MLP (reference: mace_ictc/models/mace/layers.py:825-835, tiled by
+ * ictc_o3/ops/streamed_gate_message.py:112-116; input gradient streamed_gate_message.py:224-260) as
+ * tcgen05.mma TF32 products with a three-term operand split (fp32-level accuracy), accumulators in TMEM.
+ * ictc_gate_pack_weights: W3 [num_out, 64] -> `packed` [2 * num_out * 64] floats in the shared-memory operand
+ *   layout, 64-unit chunks, transpose = 0 for the forward, 1 for the backward.  num_out % 64 == 0.
+ * ictc_gate_gemm_forward: gates[r, :] = act(z3[r, :]) @ W3^T, act = scaled SiLU when apply_silu != 0.
+ * ictc_gate_gemm_backward: da3[r, :] = (dgates[pair_a[r], :] + dgates[pair_b[r], :]) @ W3; pair_a == NULL means
+ *   row r itself, pair_b == NULL or pair_b[r] < 0 means no second row.
+ * All buffers 16-byte aligned.  Bounded waits report through ictc_kernel_status (codes 21-25, 31-35). */
+int ictc_gate_pack_weights(int num_out, const float* w3, int transpose, float* packed, void* stream);
+int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const float* w_packed, float* gates,
+                           int apply_silu, void* stream);
+int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, const int64_t* pair_a,
+                            const int64_t* pair_b, const float* w_packed_t, float* da3, void* stream);
+
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).
  * Replaces the harmonics<MODE> kernel run(n,g,h,y,dn,dg,mode,needn,needg):

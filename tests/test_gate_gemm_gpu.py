@@ -1,0 +1,123 @@
+"""Last layer of the gate MLP on the tcgen05 tensor cores (three-term TF32 split) against fp64."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SCALE = 1.6791767923989418
+
+
+def _status(lib):
+    import ctypes
+    s = ctypes.c_int(0)
+    assert lib.ictc_kernel_status(ctypes.byref(s), 1) == 0
+    return s.value
+
+
+def _pack(lib, w, transpose):
+    from ictc_o3 import _lib
+    out = torch.empty(2 * w.numel(), device="cuda")
+    _lib.check(lib.ictc_gate_pack_weights(w.shape[0], w.data_ptr(), transpose, out.data_ptr(), None), "pack")
+    return out
+
+
+@pytest.mark.parametrize("rows,nout,act", [(128, 64, 0), (1000, 192, 1), (1, 704, 1), (70001, 704, 1), (148 * 128 * 3 + 5, 192, 0)])
+def test_gate_gemm_forward(rows, nout, act):
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    torch.manual_seed(rows + nout)
+    z3 = torch.randn(rows, 64).cuda()
+    w3 = (torch.randn(nout, 64) / 8).cuda().contiguous()
+    gates = torch.full((rows, nout), float("nan"), device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.ictc_gate_gemm_forward(rows, nout, z3.data_ptr(), _pack(lib, w3, 0).data_ptr(), gates.data_ptr(),
+                                          act, st), "fwd")
+    assert _status(lib) == 0
+    sample = torch.arange(0, rows, max(1, rows // 4000))
+    h = z3[sample].double().cpu()
+    if act:
+        h = torch.nn.functional.silu(h) * SCALE
+    ref = h @ w3.double().cpu().t()
+    got = gates[sample].double().cpu()
+    assert torch.isfinite(gates).all()
+    err = float((got - ref).abs().max() / ref.abs().max())
+    assert err < 2e-6, err
+
+
+@pytest.mark.parametrize("rows,nout,paired", [(128, 64, False), (1000, 192, True), (1, 704, False), (70001, 704, True)])
+def test_gate_gemm_backward(rows, nout, paired):
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    torch.manual_seed(rows + nout + 1)
+    src_rows = 2 * rows + 3 if paired else rows
+    dg = torch.randn(src_rows, nout).cuda()
+    w3 = (torch.randn(nout, 64) / 8).cuda().contiguous()
+    da3 = torch.full((rows, 64), float("nan"), device="cuda")
+    if paired:
+        pa = torch.randint(0, src_rows, (rows,)).cuda()
+        pb = torch.randint(-1, src_rows, (rows,)).cuda()
+        pa_p, pb_p = pa.data_ptr(), pb.data_ptr()
+    else:
+        pa_p = pb_p = None
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.ictc_gate_gemm_backward(rows, nout, dg.data_ptr(), pa_p, pb_p, _pack(lib, w3, 1).data_ptr(),
+                                           da3.data_ptr(), st), "bwd")
+    assert _status(lib) == 0
+    sample = torch.arange(0, rows, max(1, rows // 4000))
+    if paired:
+        a, b = pa.cpu()[sample], pb.cpu()[sample]
+        d = dg.cpu().double()
+        summed = d[a] + torch.where((b >= 0)[:, None], d[b.clamp(min=0)], torch.zeros(1, dtype=torch.float64))
+    else:
+        summed = dg[sample].double().cpu()
+    ref = summed @ w3.double().cpu()
+    got = da3[sample].double().cpu()
+    assert torch.isfinite(da3).all()
+    err = float((got - ref).abs().max() / ref.abs().max())
+    # K = num_out products per output, accumulated by the tensor cores without rounding to nearest
+    assert err < 1e-5, err
+
+
+def test_hidden_layers_plus_gate_gemm_equal_the_single_kernel_mlp():
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    torch.manual_seed(5)
+    edges, nb, nout = 3000, 8, 704
+    rb = (torch.randn(edges, nb) * 0.7).cuda()
+    ws = [torch.randn(64, nb) / nb ** 0.5, torch.randn(64, 64) / 8, torch.randn(64, 64) / 8, torch.randn(nout, 64) / 8]
+    ws = [w.cuda().contiguous() for w in ws]
+    wt = [w.t().contiguous() for w in ws]
+
+    def split(w):
+        out = torch.empty(*w.shape, 2, device="cuda")
+        _lib.check(lib.ictc_split_tf32(w.numel(), w.data_ptr(), out.data_ptr(), None), "split")
+        return out
+    st = torch.cuda.current_stream().cuda_stream
+    gates_a = torch.empty(edges, nout, device="cuda")
+    za = [torch.empty(edges, 64, device="cuda") for _ in range(3)]
+    _lib.check(lib.ictc_radial_mlp_forward(edges, nb, nout, rb.data_ptr(), *[w.data_ptr() for w in ws[:3]],
+                                           split(ws[3]).data_ptr(), gates_a.data_ptr(), *[z.data_ptr() for z in za], st),
+               "fwd")
+    gates_b = torch.empty(edges, nout, device="cuda")
+    zb = [torch.empty(edges, 64, device="cuda") for _ in range(3)]
+    _lib.check(lib.ictc_radial_mlp_hidden_forward(edges, nb, rb.data_ptr(), *[w.data_ptr() for w in ws[:3]],
+                                                  *[z.data_ptr() for z in zb], st), "hidden fwd")
+    _lib.check(lib.ictc_gate_gemm_forward(edges, nout, zb[2].data_ptr(), _pack(lib, ws[3], 0).data_ptr(),
+                                          gates_b.data_ptr(), 1, st), "gate fwd")
+    for x, y in zip(za, zb):
+        assert torch.equal(x, y)
+    assert float((gates_a - gates_b).abs().max()) < 3e-6 * float(gates_a.abs().max())
+    dg = torch.randn(edges, nout, device="cuda")
+    drb_a = torch.empty(edges, nb, device="cuda")
+    _lib.check(lib.ictc_radial_mlp_backward(edges, nb, nout, dg.data_ptr(), *[w.data_ptr() for w in wt[:3]],
+                                            split(wt[3]).data_ptr(), *[z.data_ptr() for z in za], drb_a.data_ptr(), st),
+               "bwd")
+    da3 = torch.empty(edges, 64, device="cuda")
+    drb_b = torch.empty(edges, nb, device="cuda")
+    _lib.check(lib.ictc_gate_gemm_backward(edges, nout, dg.data_ptr(), None, None, _pack(lib, ws[3], 1).data_ptr(),
+                                           da3.data_ptr(), st), "gate bwd")
+    _lib.check(lib.ictc_radial_mlp_hidden_backward(edges, nb, da3.data_ptr(), *[w.data_ptr() for w in wt[:3]],
+                                                   *[z.data_ptr() for z in zb], drb_b.data_ptr(), st), "hidden bwd")
+    assert _status(lib) == 0
+    assert float((drb_a - drb_b).abs().max()) < 5e-6 * float(drb_a.abs().max())
+    assert lib.ictc_gate_gemm_forward(10, 100, *([None] * 3), 1, None) == -1
