@@ -14,12 +14,12 @@
 //               with cp.async.bulk, completing on mbarriers;
 //   warp 1      allocates TMEM and issues the MMAs (one thread), committing to mbarriers;
 //   warps 2-5   epilogue: tcgen05.ld (thread = row), then coalesced row stores;
-//   warps 6-13  A-operand producers: global rows -> (activation | pair sum) -> split -> shared memory in the
-//               canonical K-major no-swizzle UMMA layout.
-// Shared-memory operand layout (both A and B): element (row r, k) of a [rows x 64] part lives at byte
-// (k / 4) * (rows * 16) + r * 16 + (k % 4) * 4, i.e. 16-byte K chunks, each chunk row-contiguous.  In descriptor
-// terms: 8-row core matrices of 128 contiguous bytes, stride between core matrices along the rows (SBO) 128 B,
-// stride between the two K chunks of one K = 8 MMA (LBO) rows * 16 B.
+//   warps 6-13  A-operand producers: global rows -> (activation | pair sum) -> split -> tcgen05.st into TMEM
+//               (the A operand is read from TMEM: lane = row, column = k; no shared memory for A at all).
+// Shared-memory layout of the B operand: element (n, k) of a [64 x 64] part lives at byte
+// (k / 4) * 1024 + n * 16 + (k % 4) * 4, i.e. 16-byte K chunks, each chunk row-contiguous (canonical K-major
+// no-swizzle layout).  In descriptor terms: 8-row core matrices of 128 contiguous bytes, stride between core
+// matrices along n (SBO) 128 B, stride between the two K chunks of one K = 8 MMA (LBO) 1024 B.
 // Every mbarrier wait is bounded; a wait that runs out raises the library's status word and the CTA leaves
 // through the common exit (TMEM is always released).
 #include "ictc_common.cuh"
@@ -30,12 +30,10 @@ namespace gg {
 constexpr int kRows = 128;             // tile rows = UMMA M
 constexpr int kK = 64;                 // hidden width
 constexpr int kChunk = 64;             // weight chunk: 64 units (N of the forward MMA, K step of the backward)
-constexpr int kPartBytes = kRows * kK * 4;          // 32 KB: one [128 x 64] operand part
 constexpr int kWPartBytes = kChunk * kK * 4;        // 16 KB
 constexpr int kWStageBytes = 2 * kWPartBytes;       // big + small
 constexpr int kThreads = 14 * 32;
 constexpr int kProducerWarp0 = 6, kProducerWarps = 8;
-constexpr int kEpilogueWarp0 = 2;
 constexpr long long kWaitCycles = 2000000000LL;     // ~1 s
 constexpr float kSiluScale = 1.6791767923989418f;
 constexpr int kStagePitch = 272;                    // bytes per staged output row (256 + 16: conflict-free)
@@ -126,30 +124,59 @@ __device__ __forceinline__ float to_tf32(float x) {
 }
 __device__ __forceinline__ float silu_s(float v) { return v / (1.f + expf(-v)) * kSiluScale; }
 
-// Writes one 16-byte K chunk (4 consecutive k of one row), split into its big and small parts.
-__device__ __forceinline__ void store_split(unsigned char* a_big, unsigned char* a_small, int row, int kc, float4 v) {
-  float4 b, s;
-  b.x = to_tf32(v.x); s.x = to_tf32(v.x - b.x);
-  b.y = to_tf32(v.y); s.y = to_tf32(v.y - b.y);
-  b.z = to_tf32(v.z); s.z = to_tf32(v.z - b.z);
-  b.w = to_tf32(v.w); s.w = to_tf32(v.w - b.w);
-  const int off = kc * (kRows * 16) + row * 16;
-  *reinterpret_cast<float4*>(a_big + off) = b;
-  *reinterpret_cast<float4*>(a_small + off) = s;
+__device__ __forceinline__ void umma_tf32_ts(unsigned d_tmem, unsigned a_tmem, uint64_t b_desc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+      "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+      "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 32-byte read-only load that bypasses L1 (every thread streams its own row)
+__device__ __forceinline__ void ldg256(const float* p, float* v) {
+  asm volatile("ld.global.nc.L1::no_allocate.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+               : "l"(p));
+}
+
+// Splits 32 values of one row and writes the two parts into the TMEM A operand (lane = row, column = k).
+__device__ __forceinline__ void store_split_tmem(unsigned t_big, unsigned t_small, const float (&x)[32]) {
+  unsigned b[32], sm[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float big = to_tf32(x[i]);
+    b[i] = __float_as_uint(big);
+    sm[i] = __float_as_uint(to_tf32(x[i] - big));
+  }
+  tmem_st32(t_big, b);
+  tmem_st32(t_small, sm);
+  tmem_st_wait();
 }
 
 // The 24 MMAs of one [128 x 64] x [64 x 64]^T product: small*big, big*small, big*big over 8 K steps.
-__device__ __forceinline__ void issue_block(unsigned d_tmem, unsigned a_big, unsigned a_small, unsigned w_big,
-                                            unsigned w_small, bool first) {
-  const unsigned a_part[3] = {a_small, a_big, a_big};
+// A comes from TMEM (big part at a_tmem, small part 64 columns further), B from shared memory.
+__device__ __forceinline__ void issue_block(unsigned d_tmem, unsigned a_tmem, unsigned w_big, unsigned w_small,
+                                            bool first) {
+  const unsigned a_part[3] = {a_tmem + kK, a_tmem, a_tmem};
   const unsigned w_part[3] = {w_big, w_small, w_big};
 #pragma unroll
   for (int p = 0; p < 3; ++p) {
 #pragma unroll
     for (int ks = 0; ks < kK / 8; ++ks) {
-      const uint64_t ad = smem_desc(a_part[p] + ks * 2 * (kRows * 16), kRows * 16, 128);
       const uint64_t bd = smem_desc(w_part[p] + ks * 2 * (kChunk * 16), kChunk * 16, 128);
-      umma_tf32(d_tmem, ad, bd, (first && p == 0 && ks == 0) ? 0u : 1u);
+      umma_tf32_ts(d_tmem, a_part[p] + ks * 8, bd, (first && p == 0 && ks == 0) ? 0u : 1u);
     }
   }
 }
@@ -166,8 +193,11 @@ struct Args {
   int* status;
 };
 
+constexpr int kWStages = 4;      // weight ring
+constexpr int kAStagesBwd = 3;   // TMEM A ring of the backward kernel
+
 struct Barriers {
-  unsigned long long w_full[2], w_empty[2], a_full[2], a_empty[2], d_full[4], d_empty[4];
+  unsigned long long w_full[kWStages], w_empty[kWStages], a_full[4], a_empty[4], d_full[4], d_empty[4];
   unsigned tmem_base;
   int failed;
 };
@@ -178,14 +208,14 @@ __device__ __forceinline__ void give_up(Barriers* b, int* status, int code) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// forward: shared memory = A[2][big|small] (128 KB) | W ring [2] (64 KB) | output staging (34 KB) | barriers
-constexpr int kFwdSmem = 2 * 2 * kPartBytes + 2 * kWStageBytes + kRows * kStagePitch + 256;
+// forward.  Shared memory: W ring (4 x 32 KB) | output staging (34 KB) | barriers.
+// TMEM (512 columns): accumulator ring 4 x 64 | A operand of two tiles, each big (64) + small (64).
+constexpr int kFwdSmem = kWStages * kWStageBytes + kRows * kStagePitch + 256;
 
 __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) {
   extern __shared__ __align__(128) unsigned char gg_smem[];
-  unsigned char* a_buf = gg_smem;
-  unsigned char* w_buf = a_buf + 2 * 2 * kPartBytes;
-  unsigned char* stage = w_buf + 2 * kWStageBytes;
+  unsigned char* w_buf = gg_smem;
+  unsigned char* stage = w_buf + kWStages * kWStageBytes;
   Barriers* bar = reinterpret_cast<Barriers*>(stage + kRows * kStagePitch);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = a.nout / kChunk;
@@ -193,9 +223,11 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
   const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kWStages; ++i) {
       mbar_init(saddr(&bar->w_full[i]), 1);
       mbar_init(saddr(&bar->w_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(saddr(&bar->a_full[i]), kProducerWarps * 32);
       mbar_init(saddr(&bar->a_empty[i]), 1);
     }
@@ -208,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&bar->tmem_base)),
-                 "r"(256u)
+                 "r"(512u)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -216,6 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
   __syncthreads();
   tc_fence_after();
   const unsigned tmem = bar->tmem_base;
+  const unsigned tmem_a = tmem + 4 * kChunk;       // A operands start after the accumulator ring
 
   if (warp == 0) {
     // ---- weight chunk stream
@@ -223,8 +256,8 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
       int64_t it = 0;
       for (int64_t t = 0; t < my_tiles && !bar->failed; ++t) {
         for (int c = 0; c < chunks; ++c, ++it) {
-          const int s = int(it & 1);
-          if (!mbar_wait(saddr(&bar->w_empty[s]), unsigned((it >> 1) & 1) ^ 1u)) { give_up(bar, a.status, 21); break; }
+          const int s = int(it % kWStages);
+          if (!mbar_wait(saddr(&bar->w_empty[s]), unsigned((it / kWStages) & 1) ^ 1u)) { give_up(bar, a.status, 21); break; }
           mbar_expect_tx(saddr(&bar->w_full[s]), kWStageBytes);
           bulk_g2s(saddr(w_buf + s * kWStageBytes), a.w + int64_t(c) * (kWStageBytes / 4), kWStageBytes,
                    saddr(&bar->w_full[s]));
@@ -239,11 +272,10 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
         const int ab = int(t & 1);
         if (!mbar_wait(saddr(&bar->a_full[ab]), unsigned((t >> 1) & 1))) { give_up(bar, a.status, 22); break; }
         tc_fence_after();
-        const unsigned a_big = saddr(a_buf + ab * 2 * kPartBytes), a_small = a_big + kPartBytes;
         bool ok = true;
         for (int c = 0; c < chunks; ++c, ++it) {
-          const int s = int(it & 1), d = int(it & 3);
-          if (!mbar_wait(saddr(&bar->w_full[s]), unsigned((it >> 1) & 1)) ||
+          const int s = int(it % kWStages), d = int(it & 3);
+          if (!mbar_wait(saddr(&bar->w_full[s]), unsigned((it / kWStages) & 1)) ||
               !mbar_wait(saddr(&bar->d_empty[d]), unsigned((it >> 2) & 1) ^ 1u)) {
             give_up(bar, a.status, 23);
             ok = false;
@@ -251,7 +283,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
           }
           tc_fence_after();
           const unsigned w_big = saddr(w_buf + s * kWStageBytes), w_small = w_big + kWPartBytes;
-          issue_block(tmem + d * kChunk, a_big, a_small, w_big, w_small, true);
+          issue_block(tmem + d * kChunk, tmem_a + ab * 2 * kK, w_big, w_small, true);
           umma_commit(saddr(&bar->w_empty[s]));
           umma_commit(saddr(&bar->d_full[d]));
         }
@@ -297,30 +329,30 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
     }
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
-    // ---- A producers: z3 rows -> activation -> split
-    const int pw = warp - kProducerWarp0;
+    // ---- A producers: thread = (row, half of the 64 columns); z3 -> activation -> split -> TMEM
+    const int q = warp & 3, half = (warp - kProducerWarp0) >> 2;
+    const int row = q * 32 + lane;
     for (int64_t t = 0; t < my_tiles; ++t) {
       const int ab = int(t & 1);
+      const int64_t g = (blockIdx.x + t * gridDim.x) * kRows + row;
+      float x[32];
+      if (g < a.rows) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ldg256(a.in + g * kK + half * 32 + j * 8, x + j * 8);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = 0.f;
+      }
+      if (a.act) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = silu_s(x[i]);
+      }
       if (bar->failed) break;
       if (!mbar_wait(saddr(&bar->a_empty[ab]), unsigned((t >> 1) & 1) ^ 1u)) { give_up(bar, a.status, 25); break; }
-      unsigned char* big = a_buf + ab * 2 * kPartBytes;
-      unsigned char* small = big + kPartBytes;
-      const int64_t row0 = (blockIdx.x + t * gridDim.x) * kRows;
-      float4 v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int qi = pw * 8 + j, row = (qi >> 2) * 8 + (lane & 7), kc = (qi & 3) * 4 + (lane >> 3);
-        const int64_t g = row0 + row;
-        v[j] = g < a.rows ? __ldg(reinterpret_cast<const float4*>(a.in + g * kK + kc * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int qi = pw * 8 + j, row = (qi >> 2) * 8 + (lane & 7), kc = (qi & 3) * 4 + (lane >> 3);
-        float4 x = v[j];
-        if (a.act) { x.x = silu_s(x.x); x.y = silu_s(x.y); x.z = silu_s(x.z); x.w = silu_s(x.w); }
-        store_split(big, small, row, kc, x);
-      }
-      fence_async_smem();
+      tc_fence_after();
+      const unsigned t_big = tmem_a + (unsigned(q * 32) << 16) + ab * 2 * kK + half * 32;
+      store_split_tmem(t_big, t_big + kK, x);
+      tc_fence_before();
       mbar_arrive(saddr(&bar->a_full[ab]));
     }
   }
@@ -329,31 +361,34 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
   }
 }
 
 // ------------------------------------------------------------------------------------------------
-// backward: shared memory = A ring [2][big|small] (128 KB) | W ring [2] (64 KB) | barriers.  One accumulator
-// [128 x 64] per tile (two TMEM slots alternate between tiles); K runs over the nout / 64 chunks.
-constexpr int kBwdSmem = 2 * 2 * kPartBytes + 2 * kWStageBytes + 256;
+// backward.  Shared memory: W ring (4 x 32 KB) | barriers.  TMEM: two accumulators [128 x 64] that alternate
+// between tiles | A ring of three stages (big + small, 128 columns each); K runs over the nout / 64 chunks.
+constexpr int kBwdSmem = kWStages * kWStageBytes + 256;
 
 __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a) {
   extern __shared__ __align__(128) unsigned char gg_smem[];
-  unsigned char* a_buf = gg_smem;
-  unsigned char* w_buf = a_buf + 2 * 2 * kPartBytes;
-  Barriers* bar = reinterpret_cast<Barriers*>(w_buf + 2 * kWStageBytes);
+  unsigned char* w_buf = gg_smem;
+  Barriers* bar = reinterpret_cast<Barriers*>(w_buf + kWStages * kWStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = a.nout / kChunk;
   const int64_t tiles = (a.rows + kRows - 1) / kRows;
   const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kWStages; ++i) {
       mbar_init(saddr(&bar->w_full[i]), 1);
       mbar_init(saddr(&bar->w_empty[i]), 1);
+    }
+    for (int i = 0; i < kAStagesBwd; ++i) {
       mbar_init(saddr(&bar->a_full[i]), kProducerWarps * 32);
       mbar_init(saddr(&bar->a_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(saddr(&bar->d_full[i]), 1);
       mbar_init(saddr(&bar->d_empty[i]), 128);
     }
@@ -362,7 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&bar->tmem_base)),
-                 "r"(128u)
+                 "r"(512u)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -370,14 +405,15 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
   __syncthreads();
   tc_fence_after();
   const unsigned tmem = bar->tmem_base;
+  const unsigned tmem_a = tmem + 2 * kChunk;
 
   if (warp == 0) {
     if (lane == 0) {
       int64_t it = 0;
       for (int64_t t = 0; t < my_tiles && !bar->failed; ++t) {
         for (int c = 0; c < chunks; ++c, ++it) {
-          const int s = int(it & 1);
-          if (!mbar_wait(saddr(&bar->w_empty[s]), unsigned((it >> 1) & 1) ^ 1u)) { give_up(bar, a.status, 31); break; }
+          const int s = int(it % kWStages);
+          if (!mbar_wait(saddr(&bar->w_empty[s]), unsigned((it / kWStages) & 1) ^ 1u)) { give_up(bar, a.status, 31); break; }
           mbar_expect_tx(saddr(&bar->w_full[s]), kWStageBytes);
           bulk_g2s(saddr(w_buf + s * kWStageBytes), a.w + int64_t(c) * (kWStageBytes / 4), kWStageBytes,
                    saddr(&bar->w_full[s]));
@@ -392,19 +428,18 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
         if (!mbar_wait(saddr(&bar->d_empty[d]), unsigned((t >> 1) & 1) ^ 1u)) { give_up(bar, a.status, 32); break; }
         bool ok = true;
         for (int c = 0; c < chunks; ++c, ++it) {
-          const int s = int(it & 1);
-          if (!mbar_wait(saddr(&bar->w_full[s]), unsigned((it >> 1) & 1)) ||
-              !mbar_wait(saddr(&bar->a_full[s]), unsigned((it >> 1) & 1))) {
+          const int s = int(it % kWStages), sa = int(it % kAStagesBwd);
+          if (!mbar_wait(saddr(&bar->w_full[s]), unsigned((it / kWStages) & 1)) ||
+              !mbar_wait(saddr(&bar->a_full[sa]), unsigned((it / kAStagesBwd) & 1))) {
             give_up(bar, a.status, 33);
             ok = false;
             break;
           }
           tc_fence_after();
-          const unsigned a_big = saddr(a_buf + s * 2 * kPartBytes), a_small = a_big + kPartBytes;
           const unsigned w_big = saddr(w_buf + s * kWStageBytes), w_small = w_big + kWPartBytes;
-          issue_block(tmem + d * kChunk, a_big, a_small, w_big, w_small, c == 0);
+          issue_block(tmem + d * kChunk, tmem_a + sa * 2 * kK, w_big, w_small, c == 0);
           umma_commit(saddr(&bar->w_empty[s]));
-          umma_commit(saddr(&bar->a_empty[s]));
+          umma_commit(saddr(&bar->a_empty[sa]));
         }
         if (!ok) break;
         umma_commit(saddr(&bar->d_full[d]));
@@ -434,45 +469,44 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
       }
     }
   } else {
-    // ---- A producers: (dG[a] + dG[b]) rows, one 64-column chunk per ring stage
-    const int pw = warp - kProducerWarp0;
+    // ---- A producers: thread = (row, half of a 64-column chunk); (dG[a] + dG[b]) -> split -> TMEM ring
+    const int q = warp & 3, half = (warp - kProducerWarp0) >> 2;
+    const int row = q * 32 + lane;
     int64_t it = 0;
     for (int64_t t = 0; t < my_tiles; ++t) {
-      const int64_t row0 = (blockIdx.x + t * gridDim.x) * kRows;
-      // this thread's two rows of the tile (see the mapping below: qi >> 2 takes two values per warp)
-      int64_t ra[2], rb[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int row = (pw * 2 + h) * 8 + (lane & 7);
-        const int64_t g = row0 + row;
-        ra[h] = g < a.rows ? (a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g) : -1;
-        rb[h] = (g < a.rows && a.pair_b) ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
-      }
+      const int64_t g = (blockIdx.x + t * gridDim.x) * kRows + row;
+      const int64_t ra = g < a.rows ? (a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g) : -1;
+      const int64_t rb = (g < a.rows && a.pair_b) ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
+      const float* pa = a.in + (ra >= 0 ? ra : 0) * a.nout + half * 32;
+      const float* pb = a.in + (rb >= 0 ? rb : 0) * a.nout + half * 32;
       bool ok = true;
       for (int c = 0; c < chunks; ++c, ++it) {
-        const int s = int(it & 1);
-        if (bar->failed || !mbar_wait(saddr(&bar->a_empty[s]), unsigned((it >> 1) & 1) ^ 1u)) {
+        const int sa = int(it % kAStagesBwd);
+        float x[32];
+        if (ra >= 0) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ldg256(pa + c * kChunk + j * 8, x + j * 8);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = 0.f;
+        }
+        if (rb >= 0) {
+          float y[32];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ldg256(pb + c * kChunk + j * 8, y + j * 8);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] += y[i];
+        }
+        if (bar->failed || !mbar_wait(saddr(&bar->a_empty[sa]), unsigned((it / kAStagesBwd) & 1) ^ 1u)) {
           give_up(bar, a.status, 35);
           ok = false;
           break;
         }
-        unsigned char* big = a_buf + s * 2 * kPartBytes;
-        unsigned char* small = big + kPartBytes;
-        float4 va[8], vb[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int h = j >> 2, kc = (j & 3) * 4 + (lane >> 3);
-          const int64_t col = int64_t(c) * kChunk + kc * 4;
-          va[j] = ra[h] >= 0 ? __ldg(reinterpret_cast<const float4*>(a.in + ra[h] * a.nout + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
-          vb[j] = rb[h] >= 0 ? __ldg(reinterpret_cast<const float4*>(a.in + rb[h] * a.nout + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int h = j >> 2, kc = (j & 3) * 4 + (lane >> 3), row = (pw * 2 + h) * 8 + (lane & 7);
-          store_split(big, small, row, kc, make_float4(va[j].x + vb[j].x, va[j].y + vb[j].y, va[j].z + vb[j].z, va[j].w + vb[j].w));
-        }
-        fence_async_smem();
-        mbar_arrive(saddr(&bar->a_full[s]));
+        tc_fence_after();
+        const unsigned t_big = tmem_a + (unsigned(q * 32) << 16) + sa * 2 * kK + half * 32;
+        store_split_tmem(t_big, t_big + kK, x);
+        tc_fence_before();
+        mbar_arrive(saddr(&bar->a_full[sa]));
       }
       if (!ok) break;
     }
@@ -482,7 +516,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
   }
 }
 
@@ -535,8 +569,8 @@ int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const
   if (int rc = gg::check_common(num_rows, num_out)) return rc;
   if (num_rows == 0) return ICTC_OK;
   if (!z3 || !w_packed || !gates) { set_error("gate gemm forward: NULL buffer"); return ICTC_ERR_BAD_ARG; }
-  if ((reinterpret_cast<uintptr_t>(z3) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(gates)) & 15) {
-    set_error("gate gemm forward: buffers must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(z3) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(gates)) & 31) {
+    set_error("gate gemm forward: buffers must be 32-byte aligned");
     return ICTC_ERR_BAD_ARG;
   }
   static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_forward_kernel,
@@ -554,8 +588,8 @@ int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, 
   if (int rc = gg::check_common(num_rows, num_out)) return rc;
   if (num_rows == 0) return ICTC_OK;
   if (!dgates || !w_packed_t || !da3) { set_error("gate gemm backward: NULL buffer"); return ICTC_ERR_BAD_ARG; }
-  if ((reinterpret_cast<uintptr_t>(dgates) | reinterpret_cast<uintptr_t>(w_packed_t) | reinterpret_cast<uintptr_t>(da3)) & 15) {
-    set_error("gate gemm backward: buffers must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(dgates) | reinterpret_cast<uintptr_t>(w_packed_t) | reinterpret_cast<uintptr_t>(da3)) & 31) {
+    set_error("gate gemm backward: buffers must be 32-byte aligned");
     return ICTC_ERR_BAD_ARG;
   }
   static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_backward_kernel,

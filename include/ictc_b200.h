@@ -265,7 +265,7 @@ int ictc_radial_mlp_hidden_backward(int64_t num_edges, int num_basis, const floa
  * ictc_gate_gemm_forward: gates[r, :] = act(z3[r, :]) @ W3^T, act = scaled SiLU when apply_silu != 0.
  * ictc_gate_gemm_backward: da3[r, :] = (dgates[pair_a[r], :] + dgates[pair_b[r], :]) @ W3; pair_a == NULL means
  *   row r itself, pair_b == NULL or pair_b[r] < 0 means no second row.
- * All buffers 16-byte aligned.  Bounded waits report through ictc_kernel_status (codes 21-25, 31-35). */
+ * All buffers 32-byte aligned.  Bounded waits report through ictc_kernel_status (codes 21-25, 31-35). */
 int ictc_gate_pack_weights(int num_out, const float* w3, int transpose, float* packed, void* stream);
 int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const float* w_packed, float* gates,
                            int apply_silu, void* stream);
