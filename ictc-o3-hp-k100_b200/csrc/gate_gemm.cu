@@ -74,13 +74,6 @@ __device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void bulk_s2g(void* dst, unsigned src, unsigned bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -88,14 +81,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ uint64_t smem_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
   return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) | (uint64_t(sbo_bytes >> 4) << 32) |
          (1ull << 46);
-}
-__device__ __forceinline__ void umma_tf32(unsigned d_tmem, uint64_t a_desc, uint64_t b_desc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
-      : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -292,13 +277,15 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
       }
     }
   } else if (warp < kProducerWarp0) {
-    // ---- epilogue: thread = row of the tile
+    // ---- epilogue: tcgen05.ld gives thread = row; the warp's 32 rows go through a padded staging buffer and
+    // leave as coalesced 256-byte row segments (two rows per store instruction)
     const int q = warp & 3;                         // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;
     unsigned char* mine = stage + row * kStagePitch;
+    const unsigned char* warp_rows = stage + q * 32 * kStagePitch;
     int64_t it = 0;
     for (int64_t t = 0; t < my_tiles; ++t) {
-      const int64_t grow = (blockIdx.x + t * gridDim.x) * kRows + row;
+      const int64_t row0 = (blockIdx.x + t * gridDim.x) * kRows + q * 32;
       bool ok = true;
       for (int c = 0; c < chunks; ++c, ++it) {
         const int d = int(it & 3);
@@ -314,20 +301,24 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
         tmem_ld32(taddr + 32, v1);
         tc_fence_before();
         mbar_arrive(saddr(&bar->d_empty[d]));
-        bulk_wait_read();                            // my previous row store has left the staging row
+        __syncwarp();                                // the previous chunk's read-back is complete
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           *reinterpret_cast<float4*>(mine + j * 16) = make_float4(v0[4 * j], v0[4 * j + 1], v0[4 * j + 2], v0[4 * j + 3]);
           *reinterpret_cast<float4*>(mine + 128 + j * 16) =
               make_float4(v1[4 * j], v1[4 * j + 1], v1[4 * j + 2], v1[4 * j + 3]);
         }
-        fence_async_smem();
-        if (grow < a.rows) bulk_s2g(a.out + grow * a.nout + c * kChunk, saddr(mine), kChunk * 4);
-        bulk_commit();
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int r = 2 * i + (lane >> 4), ch = lane & 15;
+          const float4 v = *reinterpret_cast<const float4*>(warp_rows + r * kStagePitch + ch * 16);
+          if (row0 + r < a.rows)
+            __stcs(reinterpret_cast<float4*>(a.out + (row0 + r) * a.nout + c * kChunk + ch * 4), v);
+        }
       }
       if (!ok) break;
     }
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ---- A producers: thread = (row, half of the 64 columns); z3 -> activation -> split -> TMEM
     const int q = warp & 3, half = (warp - kProducerWarp0) >> 2;
