@@ -13,8 +13,9 @@
 //   warp 0      streams pre-packed 64-unit weight chunks (32 KB: big and small part) into a 2-stage ring
 //               with cp.async.bulk, completing on mbarriers;
 //   warp 1      allocates TMEM and issues the MMAs (one thread), committing to mbarriers;
-//   warps 2-5   epilogue: tcgen05.ld (thread = row), then coalesced row stores;
-//   warps 6-13  A-operand producers: global rows -> (activation | pair sum) -> split -> tcgen05.st into TMEM
+//   warps 2-9   epilogue (forward: two groups taking alternate chunks; backward: warps 2-5 only):
+//               tcgen05.ld (thread = row), then coalesced row stores;
+//   warps 10-17 A-operand producers: global rows -> (activation | pair sum) -> split -> tcgen05.st into TMEM
 //               (the A operand is read from TMEM: lane = row, column = k; no shared memory for A at all).
 // Shared-memory layout of the B operand: element (n, k) of a [64 x 64] part lives at byte
 // (k / 4) * 1024 + n * 16 + (k % 4) * 4, i.e. 16-byte K chunks, each chunk row-contiguous (canonical K-major
@@ -32,8 +33,8 @@ constexpr int kK = 64;                 // hidden width
 constexpr int kChunk = 64;             // weight chunk: 64 units (N of the forward MMA, K step of the backward)
 constexpr int kWPartBytes = kChunk * kK * 4;        // 16 KB
 constexpr int kWStageBytes = 2 * kWPartBytes;       // big + small
-constexpr int kThreads = 14 * 32;
-constexpr int kProducerWarp0 = 6, kProducerWarps = 8;
+constexpr int kThreads = 18 * 32;
+constexpr int kProducerWarp0 = 10, kProducerWarps = 8;   // warps 2-5 and 6-9: two epilogue groups
 constexpr long long kWaitCycles = 2000000000LL;     // ~1 s
 constexpr float kSiluScale = 1.6791767923989418f;
 constexpr int kStagePitch = 272;                    // bytes per staged output row (256 + 16: conflict-free)
@@ -114,7 +115,7 @@ __device__ __forceinline__ void umma_tf32_ts(unsigned d_tmem, unsigned a_tmem, u
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "n"(kIdesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
@@ -151,19 +152,19 @@ __device__ __forceinline__ void store_split_tmem(unsigned t_big, unsigned t_smal
 }
 
 // The 24 MMAs of one [128 x 64] x [64 x 64]^T product: small*big, big*small, big*big over 8 K steps.
-// A comes from TMEM (big part at a_tmem, small part 64 columns further), B from shared memory.
+// A comes from TMEM (big part at a_tmem, small part 64 columns further), B from shared memory.  The issuing
+// thread is a single lane, so the per-MMA instruction count matters: descriptors are advanced by adding the
+// K-step offset to a base descriptor (the start-address field never overflows inside one stage).
 __device__ __forceinline__ void issue_block(unsigned d_tmem, unsigned a_tmem, unsigned w_big, unsigned w_small,
                                             bool first) {
-  const unsigned a_part[3] = {a_tmem + kK, a_tmem, a_tmem};
-  const unsigned w_part[3] = {w_big, w_small, w_big};
+  const uint64_t desc_big = smem_desc(w_big, kChunk * 16, 128), desc_small = smem_desc(w_small, kChunk * 16, 128);
+  constexpr uint64_t kStep = (2 * kChunk * 16) >> 4;        // two 16-byte K chunks per MMA
 #pragma unroll
-  for (int p = 0; p < 3; ++p) {
+  for (int ks = 0; ks < kK / 8; ++ks) umma_tf32_ts(d_tmem, a_tmem + kK + ks * 8, desc_big + ks * kStep, (first && ks == 0) ? 0u : 1u);
 #pragma unroll
-    for (int ks = 0; ks < kK / 8; ++ks) {
-      const uint64_t bd = smem_desc(w_part[p] + ks * 2 * (kChunk * 16), kChunk * 16, 128);
-      umma_tf32_ts(d_tmem, a_part[p] + ks * 8, bd, (first && p == 0 && ks == 0) ? 0u : 1u);
-    }
-  }
+  for (int ks = 0; ks < kK / 8; ++ks) umma_tf32_ts(d_tmem, a_tmem + ks * 8, desc_small + ks * kStep, 1u);
+#pragma unroll
+  for (int ks = 0; ks < kK / 8; ++ks) umma_tf32_ts(d_tmem, a_tmem + ks * 8, desc_big + ks * kStep, 1u);
 }
 
 struct Args {
@@ -176,7 +177,20 @@ struct Args {
   int nout;
   int act;                // forward: apply the scaled SiLU to the input
   int* status;
+  // Row addressing (units: floats).  Row g is sub-row g % mm of node g / mm; its 64-float block number b
+  // (the only block of the 64-wide side, chunk c * cs of the wide side) starts at
+  //   base + (g / mm) * ld + (b + g % mm) * 64.
+  // Plain matrices: mm = 1, ld = row length, cs = 1.  Per-degree feature blocks [node][path slot][m][C]:
+  // mm = 2l+1, ld = node stride, cs = mm (the slot-major layout is read and written in place).
+  int in_mm, out_mm, in_cs, out_cs;
+  int64_t in_ld, out_ld;
 };
+
+__device__ __forceinline__ int64_t row_offset(int64_t g, int mm, int64_t ld) {
+  if (mm == 1) return g * ld;
+  const int64_t node = g / mm;
+  return node * ld + (g - node * mm) * kK;
+}
 
 constexpr int kWStages = 4;      // weight ring
 constexpr int kAStagesBwd = 3;   // TMEM A ring of the backward kernel
@@ -193,15 +207,15 @@ __device__ __forceinline__ void give_up(Barriers* b, int* status, int code) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// forward.  Shared memory: W ring (4 x 32 KB) | output staging (34 KB) | barriers.
+// forward.  Shared memory: W ring (4 x 32 KB) | output staging (2 x 34 KB) | barriers.
 // TMEM (512 columns): accumulator ring 4 x 64 | A operand of two tiles, each big (64) + small (64).
-constexpr int kFwdSmem = kWStages * kWStageBytes + kRows * kStagePitch + 256;
+constexpr int kFwdSmem = kWStages * kWStageBytes + 2 * kRows * kStagePitch + 256;
 
 __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) {
   extern __shared__ __align__(128) unsigned char gg_smem[];
   unsigned char* w_buf = gg_smem;
   unsigned char* stage = w_buf + kWStages * kWStageBytes;
-  Barriers* bar = reinterpret_cast<Barriers*>(stage + kRows * kStagePitch);
+  Barriers* bar = reinterpret_cast<Barriers*>(stage + 2 * kRows * kStagePitch);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = a.nout / kChunk;
   const int64_t tiles = (a.rows + kRows - 1) / kRows;
@@ -277,17 +291,27 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
       }
     }
   } else if (warp < kProducerWarp0) {
-    // ---- epilogue: tcgen05.ld gives thread = row; the warp's 32 rows go through a padded staging buffer and
-    // leave as coalesced 256-byte row segments (two rows per store instruction)
+    // ---- epilogue, two groups of four warps that take alternate chunks: tcgen05.ld gives thread = row; the
+    // warp's 32 rows go through a padded staging buffer and leave as coalesced 256-byte row segments (two rows
+    // per store instruction)
     const int q = warp & 3;                         // TMEM lane quarter this warp may read
+    const int group = (warp - 2) >> 2;
     const int row = q * 32 + lane;
-    unsigned char* mine = stage + row * kStagePitch;
-    const unsigned char* warp_rows = stage + q * 32 * kStagePitch;
+    unsigned char* gstage = stage + group * (kRows * kStagePitch);
+    unsigned char* mine = gstage + row * kStagePitch;
+    const unsigned char* warp_rows = gstage + q * 32 * kStagePitch;
+    const int mm = a.out_mm;
     int64_t it = 0;
     for (int64_t t = 0; t < my_tiles; ++t) {
       const int64_t row0 = (blockIdx.x + t * gridDim.x) * kRows + q * 32;
+      // rows 2i + (lane >> 4) of this warp are stored by this lane: walk their offsets without dividing
+      const int64_t g0 = row0 + (lane >> 4);
+      const int64_t node0 = mm == 1 ? g0 : g0 / mm;
+      const int sub0 = mm == 1 ? 0 : int(g0 - node0 * mm);
+      const int64_t off0 = node0 * a.out_ld + sub0 * kK + (lane & 15) * 4;
       bool ok = true;
       for (int c = 0; c < chunks; ++c, ++it) {
+        if (int(it & 1) != group) continue;
         const int d = int(it & 3);
         if (bar->failed || !mbar_wait(saddr(&bar->d_full[d]), unsigned((it >> 2) & 1))) {
           give_up(bar, a.status, 24);
@@ -309,12 +333,21 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
               make_float4(v1[4 * j], v1[4 * j + 1], v1[4 * j + 2], v1[4 * j + 3]);
         }
         __syncwarp();
+        float* base = a.out + int64_t(c) * a.out_cs * kChunk;
+        int64_t off = off0;
+        int sub = sub0;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int r = 2 * i + (lane >> 4), ch = lane & 15;
-          const float4 v = *reinterpret_cast<const float4*>(warp_rows + r * kStagePitch + ch * 16);
-          if (row0 + r < a.rows)
-            __stcs(reinterpret_cast<float4*>(a.out + (row0 + r) * a.nout + c * kChunk + ch * 4), v);
+          const int r = 2 * i + (lane >> 4);
+          const float4 v = *reinterpret_cast<const float4*>(warp_rows + r * kStagePitch + (lane & 15) * 16);
+          if (row0 + r < a.rows) __stcs(reinterpret_cast<float4*>(base + off), v);
+          if (mm == 1) {
+            off += 2 * a.out_ld;
+          } else {
+            sub += 2;
+            off += 2 * kK;
+            while (sub >= mm) { sub -= mm; off += a.out_ld - int64_t(mm) * kK; }
+          }
         }
       }
       if (!ok) break;
@@ -329,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
       float x[32];
       if (g < a.rows) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) ldg256(a.in + g * kK + half * 32 + j * 8, x + j * 8);
+        for (int j = 0; j < 4; ++j) ldg256(a.in + row_offset(g, a.in_mm, a.in_ld) + half * 32 + j * 8, x + j * 8);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) x[i] = 0.f;
@@ -436,7 +469,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
         umma_commit(saddr(&bar->d_full[d]));
       }
     }
-  } else if (warp < kProducerWarp0) {
+  } else if (warp < 6) {
     const int q = warp & 3;
     const int row = q * 32 + lane;
     for (int64_t t = 0; t < my_tiles; ++t) {
@@ -451,7 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
       tc_fence_before();
       mbar_arrive(saddr(&bar->d_empty[d]));
       if (grow < a.rows) {
-        float4* o = reinterpret_cast<float4*>(a.out + grow * kK);
+        float4* o = reinterpret_cast<float4*>(a.out + row_offset(grow, a.out_mm, a.out_ld));
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           o[j] = make_float4(v0[4 * j], v0[4 * j + 1], v0[4 * j + 2], v0[4 * j + 3]);
@@ -459,7 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
         }
       }
     }
-  } else {
+  } else if (warp >= kProducerWarp0) {
     // ---- A producers: thread = (row, half of a 64-column chunk); (dG[a] + dG[b]) -> split -> TMEM ring
     const int q = warp & 3, half = (warp - kProducerWarp0) >> 2;
     const int row = q * 32 + lane;
@@ -468,15 +501,16 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
       const int64_t g = (blockIdx.x + t * gridDim.x) * kRows + row;
       const int64_t ra = g < a.rows ? (a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g) : -1;
       const int64_t rb = (g < a.rows && a.pair_b) ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
-      const float* pa = a.in + (ra >= 0 ? ra : 0) * a.nout + half * 32;
-      const float* pb = a.in + (rb >= 0 ? rb : 0) * a.nout + half * 32;
+      const float* pa = a.in + row_offset(ra >= 0 ? ra : 0, a.in_mm, a.in_ld) + half * 32;
+      const float* pb = a.in + row_offset(rb >= 0 ? rb : 0, a.in_mm, a.in_ld) + half * 32;
+      const int64_t cstep = int64_t(a.in_cs) * kChunk;
       bool ok = true;
       for (int c = 0; c < chunks; ++c, ++it) {
         const int sa = int(it % kAStagesBwd);
         float x[32];
         if (ra >= 0) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) ldg256(pa + c * kChunk + j * 8, x + j * 8);
+          for (int j = 0; j < 4; ++j) ldg256(pa + c * cstep + j * 8, x + j * 8);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] = 0.f;
@@ -484,7 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
         if (rb >= 0) {
           float y[32];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) ldg256(pb + c * kChunk + j * 8, y + j * 8);
+          for (int j = 0; j < 4; ++j) ldg256(pb + c * cstep + j * 8, y + j * 8);
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] += y[i];
         }
@@ -569,6 +603,7 @@ int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const
   if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   gg::Args a{};
   a.in = z3; a.w = w_packed; a.out = gates; a.rows = num_rows; a.nout = num_out; a.act = apply_silu ? 1 : 0;
+  a.in_mm = a.out_mm = a.in_cs = a.out_cs = 1; a.in_ld = gg::kK; a.out_ld = num_out;
   a.status = kernel_status_word();
   gg::gate_gemm_forward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kFwdSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("gate_gemm_forward");
@@ -588,9 +623,46 @@ int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, 
   if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   gg::Args a{};
   a.in = dgates; a.w = w_packed_t; a.out = da3; a.pair_a = pair_a; a.pair_b = pair_b; a.rows = num_rows; a.nout = num_out;
+  a.in_mm = a.out_mm = a.in_cs = a.out_cs = 1; a.in_ld = num_out; a.out_ld = gg::kK;
   a.status = kernel_status_word();
   gg::gate_gemm_backward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kBwdSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("gate_gemm_backward");
+}
+
+
+int ictc_channel_linear_tc(int64_t num_rows, int k_chunks, int n_chunks, const float* in, int in_mm, int64_t in_ld,
+                           const float* w_packed, float* out, int out_mm, int64_t out_ld, void* stream) {
+  if (num_rows < 0 || k_chunks < 1 || n_chunks < 1 || (k_chunks > 1 && n_chunks > 1) || in_mm < 1 || out_mm < 1 ||
+      in_ld < 0 || out_ld < 0) {
+    set_error("channel linear: one side must be 64 wide, the other a multiple of 64 (got %d x %d chunks)", k_chunks,
+              n_chunks);
+    return ICTC_ERR_BAD_SPEC;
+  }
+  if (num_rows == 0) return ICTC_OK;
+  if (!in || !w_packed || !out) { set_error("channel linear: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  if (((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(out)) & 31) ||
+      (in_ld & 7) || (out_ld & 7)) {
+    set_error("channel linear: buffers must be 32-byte aligned and strides multiples of 8 floats");
+    return ICTC_ERR_BAD_ARG;
+  }
+  gg::Args a{};
+  a.in = in; a.w = w_packed; a.out = out; a.rows = num_rows; a.status = kernel_status_word();
+  a.in_mm = in_mm; a.out_mm = out_mm; a.in_ld = in_ld; a.out_ld = out_ld;
+  a.in_cs = in_mm; a.out_cs = out_mm;
+  if (k_chunks == 1) {
+    static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_forward_kernel,
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kFwdSmem);
+    if (attr != cudaSuccess) { set_error("channel linear smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
+    a.nout = n_chunks * gg::kChunk;
+    gg::gate_gemm_forward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kFwdSmem, (cudaStream_t)stream>>>(a);
+  } else {
+    static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_backward_kernel,
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kBwdSmem);
+    if (attr != cudaSuccess) { set_error("channel linear smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
+    a.nout = k_chunks * gg::kChunk;
+    gg::gate_gemm_backward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kBwdSmem, (cudaStream_t)stream>>>(a);
+  }
+  return finish_launch("channel_linear_tc");
 }
 
 }  // extern "C"

@@ -42,6 +42,7 @@ class ForceEngine:
         self._spec = {0: _lib.tp_spec(0, 2, 2), 1: _lib.tp_spec(2, 2, 2)}
         self.fused_mlp = True
         self.gate_gemm = True    # last MLP layer on the tcgen05 tensor cores (False: single mma.sync kernel)
+        self.tc_linear = True    # per-degree channel linears on the same kernels (False: library fp32 GEMM)
         self.profile = None      # list of (kernel name, start event, end event) when enabled by a benchmark
         self.refresh()
 
@@ -81,6 +82,19 @@ class ForceEngine:
                 L["target"] = prod.target_lmax
                 L["pl"] = [(prod.linear[str(l)] / math.sqrt(c)).contiguous() for l in range(prod.target_lmax + 1)]
                 L["pl_t"] = [w.t().contiguous() for w in L["pl"]]
+                if self.tc_linear and c == 64:
+                    # operand-layout copies for the tensor-core channel linears: key -> (packed, k_chunks, n_chunks)
+                    P = {}
+                    for l in range(lin + 1):
+                        P["up", l] = self._pack_lin(L["up"][l], L["up_t"][l])
+                        P["up_b", l] = self._pack_lin(L["up_t"][l], L["up"][l])
+                    for l in range(3):
+                        P["ml", l] = self._pack_lin(L["ml"][l], L["ml_t"][l])        # x @ ml_t
+                        P["ml_b", l] = self._pack_lin(L["ml_t"][l], L["ml"][l])      # x @ ml
+                    for l in range(prod.target_lmax + 1):
+                        P["pl", l] = self._pack_lin(L["pl_t"][l], L["pl"][l])        # x @ pl
+                        P["pl_b", l] = self._pack_lin(L["pl"][l], L["pl_t"][l])      # x @ pl_t
+                    L["packed"] = P
                 self.layers.append(L)
             self.ro0 = m.layer_energy_readouts[0].readout.weight.reshape(-1).contiguous()  # [C]
             self.ro1_w1 = m.last_layer_energy_readout.linear_1.weight.contiguous()          # [16, C]
@@ -102,6 +116,24 @@ class ForceEngine:
             _lib.check(self.lib.ictc_gate_pack_weights(w.shape[0], w.data_ptr(), transpose, out.data_ptr(),
                                                        _lib.stream(w.device)), "gate_pack_weights")
         return out
+
+    def _pack_lin(self, w_out_major, w_in_major):
+        """Operand copy for out = x @ w_in_major, where w_in_major is [K, N] and w_out_major its transpose."""
+        k, n = w_in_major.shape
+        if k == 64:
+            return self._pack_umma(w_out_major.contiguous(), 0), 1, n // 64
+        if n != 64:
+            raise ValueError("tensor-core channel linear needs a 64-wide side")
+        return self._pack_umma(w_in_major.contiguous(), 1), k // 64, 1
+
+    def _lin(self, L, key, rows, in_t, in_off, in_mm, in_ld, out_t, out_off, out_mm, out_ld):
+        """out rows = in rows @ W on the tensor cores, reading / writing per-degree blocks in place."""
+        packed, kc, nc = L["packed"][key]
+        t0 = self._mark()
+        _lib.check(self.lib.ictc_channel_linear_tc(rows, kc, nc, in_t.data_ptr() + 4 * in_off, in_mm, in_ld,
+                                                   packed.data_ptr(), out_t.data_ptr() + 4 * out_off, out_mm, out_ld,
+                                                   self._st()), "channel_linear_tc")
+        self._done("channel_linear_tc", t0)
 
     # ---------------------------------------------------------------- small launch helpers
     def _st(self):
@@ -277,11 +309,19 @@ class ForceEngine:
             s_count = self.emb.shape[0]
             # ---- layer 0
             x0 = self.emb.index_select(0, species)                               # [N_local, C]
-            u0 = torch.mm(x0, L0["up_t"][0])
+            tc = "packed" in L0 and "packed" in L1
+            if tc:
+                u0 = torch.empty(n_local, c, dtype=torch.float32, device=dev)
+                self._lin(L0, ("up", 0), n_local, x0, 0, 1, c, u0, 0, 1, c)
+            else:
+                u0 = torch.mm(x0, L0["up_t"][0])
             g0, pre0 = self._mlp(rb_u, L0)
             M0 = self._tp_forward(0, u0, sh, g0, src, dst_rowptr, n_owned, e, L0["tpw"], grow)   # [n, 9C]
             m0 = torch.empty_like(M0)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                if tc:
+                    self._lin(L0, ("ml", l), n_owned * mm, M0, off * c, mm, 9 * c, m0, off * c, mm, 9 * c)
+                    continue
                 m0[:, off * c:(off + mm) * c] = torch.mm(M0[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L0["ml_t"][l]).view(n_owned, mm * c)
             sc0 = self._species_linear(x0[:n_owned], sp_owned, L0["sc_fwd"], s_count)
@@ -289,6 +329,9 @@ class ForceEngine:
             y0 = call0.forward(m0, L0["bank"])                                    # [n, 9C]
             h1 = torch.empty_like(y0)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                if tc:
+                    self._lin(L0, ("pl", l), n_owned * mm, y0, off * c, mm, 9 * c, h1, off * c, mm, 9 * c)
+                    continue
                 h1[:, off * c:(off + mm) * c] = torch.mm(y0[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L0["pl"][l]).view(n_owned, mm * c)
             h1[:, :c] += sc0
@@ -298,6 +341,9 @@ class ForceEngine:
             # ---- layer 1
             u1 = torch.empty(n_local, 9 * c, dtype=torch.float32, device=dev)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                if tc:
+                    self._lin(L1, ("up", l), n_local * mm, h1_full, off * c, mm, 9 * c, u1, off * c, mm, 9 * c)
+                    continue
                 u1[:, off * c:(off + mm) * c] = torch.mm(h1_full[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L1["up_t"][l]).view(n_local, mm * c)
             g1, pre1 = self._mlp(rb_u, L1)
@@ -306,9 +352,12 @@ class ForceEngine:
             in_off = 0
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 cnt = L1["counts"][l]
-                buf = torch.empty(n_owned * mm, cnt * c, dtype=torch.float32, device=dev)
-                self._transpose(n_owned, cnt, mm, M1, in_off, 35 * c, buf, 0, mm * cnt * c, True)
-                m1[:, off * c:(off + mm) * c] = torch.mm(buf, L1["ml_t"][l]).view(n_owned, mm * c)
+                if tc:      # the slot-major block is contracted in place: no transposed copy
+                    self._lin(L1, ("ml", l), n_owned * mm, M1, in_off, mm, 35 * c, m1, off * c, mm, 9 * c)
+                else:
+                    buf = torch.empty(n_owned * mm, cnt * c, dtype=torch.float32, device=dev)
+                    self._transpose(n_owned, cnt, mm, M1, in_off, 35 * c, buf, 0, mm * cnt * c, True)
+                    m1[:, off * c:(off + mm) * c] = torch.mm(buf, L1["ml_t"][l]).view(n_owned, mm * c)
                 in_off += cnt * mm * c
             sc1 = self._species_linear(h1[:, :c].contiguous(), sp_owned, L1["sc_fwd"], s_count)
             call1 = _ScCall(c, 0, s_count, sp_owned, True)
@@ -330,14 +379,20 @@ class ForceEngine:
             out_off = 0
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 cnt = L1["counts"][l]
-                buf = torch.mm(dm1[:, off * c:(off + mm) * c].reshape(-1, c), L1["ml"][l])   # [n*mm, cnt*C]
-                self._transpose(n_owned, cnt, mm, buf, 0, mm * cnt * c, v1, out_off, 35 * c, False)
+                if tc:
+                    self._lin(L1, ("ml_b", l), n_owned * mm, dm1, off * c, mm, 9 * c, v1, out_off, mm, 35 * c)
+                else:
+                    buf = torch.mm(dm1[:, off * c:(off + mm) * c].reshape(-1, c), L1["ml"][l])   # [n*mm, cnt*C]
+                    self._transpose(n_owned, cnt, mm, buf, 0, mm * cnt * c, v1, out_off, 35 * c, False)
                 out_off += cnt * mm * c
             du1, dsh1, dg1 = self._tp_adjoint(1, u1, sh, g1, dst, src_csr, v1, n_local, e, L1["tpw"], True, grow)
             drb = self._mlp_bwd(dg1, pre1, L1, pairs)
             del dg1, g1, pre1
             dh1_full = torch.empty(n_local, 9 * c, dtype=torch.float32, device=dev)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                if tc:
+                    self._lin(L1, ("up_b", l), n_local * mm, du1, off * c, mm, 9 * c, dh1_full, off * c, mm, 9 * c)
+                    continue
                 dh1_full[:, off * c:(off + mm) * c] = torch.mm(du1[:, off * c:(off + mm) * c].reshape(-1, c),
                                                                L1["up"][l]).view(n_local, mm * c)
             dh1 = dh1_full[:n_owned]
@@ -351,11 +406,17 @@ class ForceEngine:
             dh1[:, :c] += self.ro0
             dy0 = torch.empty_like(dh1)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                if tc:
+                    self._lin(L0, ("pl_b", l), n_owned * mm, dh1, off * c, mm, 9 * c, dy0, off * c, mm, 9 * c)
+                    continue
                 dy0[:, off * c:(off + mm) * c] = torch.mm(dh1[:, off * c:(off + mm) * c].reshape(-1, c),
                                                           L0["pl_t"][l]).view(n_owned, mm * c)
             dm0, _ = call0.adjoint(m0, L0["bank"], dy0, (True, False))
             v0 = torch.empty_like(dm0)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
+                if tc:
+                    self._lin(L0, ("ml_b", l), n_owned * mm, dm0, off * c, mm, 9 * c, v0, off * c, mm, 9 * c)
+                    continue
                 v0[:, off * c:(off + mm) * c] = torch.mm(dm0[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L0["ml"][l]).view(n_owned, mm * c)
             _, dsh0, dg0 = self._tp_adjoint(0, u0, sh, g0, dst, src_csr, v0, n_local, e, L0["tpw"], False, grow)

@@ -272,6 +272,20 @@ int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const
 int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, const int64_t* pair_a,
                             const int64_t* pair_b, const float* w_packed_t, float* da3, void* stream);
 
+/* Per-degree channel linear map on the same tcgen05 kernels (reference: ictc_o3/operators.py:609-628
+ * channel_linear; mace_ictc/models/mace/layers.py:21-87 linear_up / message_linear; products.py:817): rows are
+ * (node, component) pairs with 64 contiguous channels, out = in @ W with fp32-level accuracy (three-term TF32).
+ * Exactly one side is 64 wide: k_chunks == 1 gives N = 64 * n_chunks outputs per row, n_chunks == 1 contracts
+ * K = 64 * k_chunks inputs.  Row g is component g % mm of node g / mm; the 64-float block b of that row on the
+ * wide side starts at base + (g / mm) * ld + (b * mm + g % mm) * 64 (the path-slot-major layout
+ * [node][slot][component][channel] of the tensor-product output, read or written in place), the block of the
+ * 64-wide side at base + (g / mm) * ld + (g % mm) * 64.  mm = 1 with ld = row length is a plain matrix.
+ * w_packed comes from ictc_gate_pack_weights: W given as [64 * n_chunks, 64] (out unit major) with
+ * transpose = 0 when k_chunks == 1, as [64 * k_chunks, 64] (in unit major) with transpose = 1 otherwise.
+ * Buffers 32-byte aligned, ld a multiple of 8. */
+int ictc_channel_linear_tc(int64_t num_rows, int k_chunks, int n_chunks, const float* in, int in_mm, int64_t in_ld,
+                           const float* w_packed, float* out, int out_mm, int64_t out_ld, void* stream);
+
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).
  * Replaces the harmonics<MODE> kernel run(n,g,h,y,dn,dg,mode,needn,needg):

@@ -121,3 +121,40 @@ def test_hidden_layers_plus_gate_gemm_equal_the_single_kernel_mlp():
     assert _status(lib) == 0
     assert float((drb_a - drb_b).abs().max()) < 5e-6 * float(drb_a.abs().max())
     assert lib.ictc_gate_gemm_forward(10, 100, *([None] * 3), 1, None) == -1
+
+
+@pytest.mark.parametrize("nodes,mm,cnt", [(777, 3, 4), (1000, 5, 4), (300, 1, 3), (513, 3, 1)])
+def test_channel_linear_reads_and_writes_slot_major_blocks_in_place(nodes, mm, cnt):
+    """Message linear (K = cnt * 64 -> 64) and its adjoint (64 -> cnt * 64) on a [node][slot][m][C] block that sits
+    inside a wider row, against fp64 einsum."""
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    torch.manual_seed(nodes + mm)
+    c, ld_wide, ld_narrow, off_wide, off_narrow = 64, 35 * 64, 9 * 64, 2 * 64, 64
+    wide = torch.randn(nodes, ld_wide).cuda()
+    w = (torch.randn(cnt * c, c) / 8).cuda()                  # [K = (slot, channel), N]
+    st = torch.cuda.current_stream().cuda_stream
+    # K-loop direction
+    narrow = torch.zeros(nodes, ld_narrow, device="cuda")
+    _lib.check(lib.ictc_channel_linear_tc(nodes * mm, cnt, 1, wide.data_ptr() + 4 * off_wide, mm, ld_wide,
+                                          _pack(lib, w.contiguous(), 1).data_ptr(), narrow.data_ptr() + 4 * off_narrow,
+                                          mm, ld_narrow, st), "lin")
+    block = wide[:, off_wide:off_wide + cnt * mm * c].view(nodes, cnt, mm, c).double().cpu()
+    ref = torch.einsum("nsic,scd->nid", block, w.view(cnt, c, c).double().cpu())
+    got = narrow[:, off_narrow:off_narrow + mm * c].view(nodes, mm, c).double().cpu()
+    assert float((got - ref).abs().max() / ref.abs().max()) < 5e-6
+    assert float(narrow[:, :off_narrow].abs().max()) == 0 and float(narrow[:, off_narrow + mm * c:].abs().max()) == 0
+    # N-wide direction (adjoint): narrow block -> wide block
+    src = torch.randn(nodes, ld_narrow).cuda()
+    dst = torch.zeros(nodes, ld_wide, device="cuda")
+    wt = w.t().contiguous()                                   # [N = 64 in, cnt*64 out] used as x @ wt
+    _lib.check(lib.ictc_channel_linear_tc(nodes * mm, 1, cnt, src.data_ptr() + 4 * off_narrow, mm, ld_narrow,
+                                          _pack(lib, w.contiguous(), 0).data_ptr(), dst.data_ptr() + 4 * off_wide,
+                                          mm, ld_wide, st), "lin adjoint")
+    assert _status(lib) == 0
+    x = src[:, off_narrow:off_narrow + mm * c].view(nodes, mm, c).double().cpu()
+    ref = torch.einsum("nid,scd->nsic", x, w.view(cnt, c, c).double().cpu())
+    got = dst[:, off_wide:off_wide + cnt * mm * c].view(nodes, cnt, mm, c).double().cpu()
+    assert float((got - ref).abs().max() / ref.abs().max()) < 5e-6
+    assert float(dst[:, :off_wide].abs().max()) == 0
+    assert lib.ictc_channel_linear_tc(10, 2, 2, *([None] * 1), 1, 64, None, None, 1, 64, None) == -1
