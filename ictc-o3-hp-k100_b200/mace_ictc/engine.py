@@ -42,6 +42,7 @@ class ForceEngine:
         self._spec = {0: _lib.tp_spec(0, 2, 2), 1: _lib.tp_spec(2, 2, 2)}
         self.fused_mlp = True
         self.gate_gemm = True    # last MLP layer on the tcgen05 tensor cores (False: single mma.sync kernel)
+        self.mlp_chain = True    # hidden MLP layers as a TMEM chain (False: mma.sync kernels)
         self.tc_linear = True    # per-degree channel linears on the same kernels (False: library fp32 GEMM)
         self.profile = None      # list of (kernel name, start event, end event) when enabled by a benchmark
         self.refresh()
@@ -74,6 +75,8 @@ class ForceEngine:
                 if self._fused_mlp_ok(L) and self.gate_gemm:
                     L["w3_umma"] = self._pack_umma(L["fc"][-1], 0)
                     L["w3t_umma"] = self._pack_umma(L["fc"][-1], 1)
+                    L["hid_umma"] = [self._pack_umma(L["fc"][1], 0), self._pack_umma(L["fc"][2], 0)]
+                    L["hid_t_umma"] = [self._pack_umma(L["fc"][1], 1), self._pack_umma(L["fc"][2], 1)]
                 wsc = inter.self_connection.weights["0"]                                 # [S, C(out), C(in)]
                 s = wsc.shape[0]
                 L["sc_fwd"] = wsc.permute(2, 0, 1).reshape(c, s * c).contiguous()          # x @ -> [n, S*C(out)]
@@ -165,10 +168,17 @@ class ForceEngine:
             pre = [torch.empty(e, 64, dtype=torch.float32, device=self.dev) for _ in range(3)]
             t0 = self._mark()
             if "w3_umma" in L:
-                _lib.check(self.lib.ictc_radial_mlp_hidden_forward(e, rb.shape[1], _lib.ptr(rb), fc[0].data_ptr(),
-                                                                   fc[1].data_ptr(), fc[2].data_ptr(), _lib.ptr(pre[0]),
-                                                                   _lib.ptr(pre[1]), _lib.ptr(pre[2]), self._st()),
-                           "radial_mlp_hidden_forward")
+                if self.mlp_chain:
+                    _lib.check(self.lib.ictc_mlp_chain_forward(e, rb.shape[1], _lib.ptr(rb), fc[0].data_ptr(),
+                                                               L["hid_umma"][0].data_ptr(), L["hid_umma"][1].data_ptr(),
+                                                               _lib.ptr(pre[0]), _lib.ptr(pre[1]), _lib.ptr(pre[2]),
+                                                               self._st()), "mlp_chain_forward")
+                else:
+                    _lib.check(self.lib.ictc_radial_mlp_hidden_forward(e, rb.shape[1], _lib.ptr(rb), fc[0].data_ptr(),
+                                                                       fc[1].data_ptr(), fc[2].data_ptr(),
+                                                                       _lib.ptr(pre[0]), _lib.ptr(pre[1]),
+                                                                       _lib.ptr(pre[2]), self._st()),
+                               "radial_mlp_hidden_forward")
                 self._done(f"radial_mlp_hidden_forward_{nout}", t0)
                 t0 = self._mark()
                 _lib.check(self.lib.ictc_gate_gemm_forward(e, nout, _lib.ptr(pre[2]), L["w3_umma"].data_ptr(),
@@ -209,11 +219,18 @@ class ForceEngine:
                                                             self._st()), "gate_gemm_backward")
                 self._done(f"gate_gemm_backward_{dgates.shape[1]}", t0)
                 t0 = self._mark()
-                _lib.check(self.lib.ictc_radial_mlp_hidden_backward(e, nb, _lib.ptr(da3), ft[0].data_ptr(),
-                                                                    ft[1].data_ptr(), ft[2].data_ptr(),
-                                                                    _lib.ptr(pre[0]), _lib.ptr(pre[1]),
-                                                                    _lib.ptr(pre[2]), _lib.ptr(drb), self._st()),
-                           "radial_mlp_hidden_backward")
+                if self.mlp_chain:
+                    _lib.check(self.lib.ictc_mlp_chain_backward(e, nb, _lib.ptr(da3), L["fc"][0].data_ptr(),
+                                                                L["hid_t_umma"][0].data_ptr(),
+                                                                L["hid_t_umma"][1].data_ptr(), _lib.ptr(pre[0]),
+                                                                _lib.ptr(pre[1]), _lib.ptr(pre[2]), _lib.ptr(drb),
+                                                                self._st()), "mlp_chain_backward")
+                else:
+                    _lib.check(self.lib.ictc_radial_mlp_hidden_backward(e, nb, _lib.ptr(da3), ft[0].data_ptr(),
+                                                                        ft[1].data_ptr(), ft[2].data_ptr(),
+                                                                        _lib.ptr(pre[0]), _lib.ptr(pre[1]),
+                                                                        _lib.ptr(pre[2]), _lib.ptr(drb), self._st()),
+                               "radial_mlp_hidden_backward")
                 self._done(f"radial_mlp_hidden_backward_{dgates.shape[1]}", t0)
                 return drb
             _lib.check(self.lib.ictc_radial_mlp_backward_paired(e, nb, dgates.shape[1], _lib.ptr(dgates), _lib.ptr(pa),

@@ -286,6 +286,19 @@ int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, 
 int ictc_channel_linear_tc(int64_t num_rows, int k_chunks, int n_chunks, const float* in, int in_mm, int64_t in_ld,
                            const float* w_packed, float* out, int out_mm, int64_t out_ld, void* stream);
 
+/* Hidden layers of the gate MLP as a chain through tensor memory (same reference as ictc_radial_mlp_forward):
+ * the two 64 x 64 layers are three-term TF32 tcgen05.mma products with the activations kept in TMEM, the
+ * num_basis-wide layer is fp32 FMA.  w1_packed / w2_packed come from ictc_gate_pack_weights(64, W, 0, ...),
+ * w1t_packed / w2t_packed from ictc_gate_pack_weights(64, W, 1, ...); w0 is the plain [64, num_basis] matrix.
+ * forward: rb [E, num_basis] -> pre-activations z1, z2, z3 [E, 64].
+ * backward: da3 [E, 64] (gradient of silu(z3)) and z1..z3 -> drb [E, num_basis].
+ * z*, da3 and the packed weights 32-byte aligned.  Bounded waits report codes 41-46. */
+int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, const float* w0, const float* w1_packed,
+                           const float* w2_packed, float* z1, float* z2, float* z3, void* stream);
+int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0, const float* w1t_packed,
+                            const float* w2t_packed, const float* z1, const float* z2, const float* z3, float* drb,
+                            void* stream);
+
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).
  * Replaces the harmonics<MODE> kernel run(n,g,h,y,dn,dg,mode,needn,needg):

@@ -158,3 +158,40 @@ def test_channel_linear_reads_and_writes_slot_major_blocks_in_place(nodes, mm, c
     assert float((got - ref).abs().max() / ref.abs().max()) < 5e-6
     assert float(dst[:, :off_wide].abs().max()) == 0
     assert lib.ictc_channel_linear_tc(10, 2, 2, *([None] * 1), 1, 64, None, None, 1, 64, None) == -1
+
+
+@pytest.mark.parametrize("edges,nb", [(1000, 8), (129, 5), (1, 8), (148 * 128 * 2 + 77, 8), (70001, 8)])
+def test_mlp_chain_hidden_layers(edges, nb):
+    """TMEM chain kernels of the hidden layers against fp64 (values and input gradient)."""
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    torch.manual_seed(edges + nb)
+    rb = (torch.randn(edges, nb) * 0.7).cuda()
+    ws = [torch.randn(64, nb) / nb ** 0.5, torch.randn(64, 64) / 8, torch.randn(64, 64) / 8]
+    ws = [w.cuda().contiguous() for w in ws]
+    st = torch.cuda.current_stream().cuda_stream
+    zs = [torch.full((edges, 64), float("nan"), device="cuda") for _ in range(3)]
+    packed = [_pack(lib, ws[1], 0), _pack(lib, ws[2], 0), _pack(lib, ws[1], 1), _pack(lib, ws[2], 1)]
+    _lib.check(lib.ictc_mlp_chain_forward(edges, nb, rb.data_ptr(), ws[0].data_ptr(), packed[0].data_ptr(),
+                                          packed[1].data_ptr(), *[z.data_ptr() for z in zs], st), "chain fwd")
+    assert _status(lib) == 0
+    x = rb.double().cpu().requires_grad_(True)
+    h, ref = x, []
+    for w in ws:
+        z = h @ w.double().cpu().t()
+        ref.append(z)
+        h = torch.nn.functional.silu(z) * SCALE
+    errs = [float((z.double().cpu() - r.detach()).abs().max() / r.detach().abs().max()) for z, r in zip(zs, ref)]
+    assert all(torch.isfinite(z).all() for z in zs)
+    assert max(errs) < 4e-6, errs
+    da3 = torch.randn(edges, 64)
+    (ref_d,) = torch.autograd.grad((h * da3.double()).sum(), x)
+    drb = torch.full((edges, nb), float("nan"), device="cuda")
+    da3d = da3.cuda()
+    _lib.check(lib.ictc_mlp_chain_backward(edges, nb, da3d.data_ptr(), ws[0].data_ptr(), packed[2].data_ptr(),
+                                           packed[3].data_ptr(), *[z.data_ptr() for z in zs], drb.data_ptr(),
+                                           st), "chain bwd")
+    assert _status(lib) == 0
+    assert torch.isfinite(drb).all()
+    err = float((drb.double().cpu() - ref_d).abs().max() / ref_d.abs().max())
+    assert err < 5e-6, err
