@@ -39,6 +39,8 @@ struct Args {
   float* z2;
   float* z3;
   float* drb;          // backward output [E, nb]
+  const int64_t* rows; // optional row index: forward reads rb[rows[r]], backward writes / adds to drb[rows[r]]
+  int accumulate;      // backward: drb[...] += instead of =
   int64_t E;
   int nb;
   int* status;
@@ -154,7 +156,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_forward_kernel(Args a) 
       // ---- layer 0 in fp32: z1[n] = sum_k rb[k] W0[n][k] for this thread's 32 units
       float rb[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) rb[k] = (valid && k < a.nb) ? __ldg(a.in + g * a.nb + k) : 0.f;
+      const int64_t src_row = (valid && a.rows) ? __ldg(reinterpret_cast<const long long*>(a.rows + g)) : g;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) rb[k] = (valid && k < a.nb) ? __ldg(a.in + src_row * a.nb + k) : 0.f;
       float x[32];
 #pragma unroll
       for (int n = 0; n < 32; ++n) {
@@ -289,9 +293,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_backward_kernel(Args a)
         p[0] += lo.x; p[1] += lo.y; p[2] += lo.z; p[3] += lo.w;
         p[4] += hi.x; p[5] += hi.y; p[6] += hi.z; p[7] += hi.w;
         if (valid) {
+          float* o = a.drb + (a.rows ? __ldg(reinterpret_cast<const long long*>(a.rows + g)) : g) * a.nb;
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            if (k < a.nb) a.drb[g * a.nb + k] = p[k];
+            if (k < a.nb) o[k] = a.accumulate ? o[k] + p[k] : p[k];
         }
       }
       ++xphase;
@@ -314,8 +319,9 @@ using namespace ictc;
 
 extern "C" {
 
-int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, const float* w0, const float* w1_packed,
-                           const float* w2_packed, float* z1, float* z2, float* z3, void* stream) {
+int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, const int64_t* rb_rows, const float* w0,
+                           const float* w1_packed, const float* w2_packed, float* z1, float* z2, float* z3,
+                           void* stream) {
   if (num_edges < 0 || num_basis < 1 || num_basis > 8) {
     set_error("mlp chain: needs 1..8 basis functions (got %d)", num_basis);
     return ICTC_ERR_BAD_SPEC;
@@ -331,7 +337,7 @@ int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, co
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, chain::kSmem);
   if (attr != cudaSuccess) { set_error("mlp chain smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   chain::Args a{};
-  a.in = rb; a.w0 = w0; a.wa = w1_packed; a.wb = w2_packed; a.z1 = z1; a.z2 = z2; a.z3 = z3; a.E = num_edges; a.nb = num_basis;
+  a.in = rb; a.rows = rb_rows; a.w0 = w0; a.wa = w1_packed; a.wb = w2_packed; a.z1 = z1; a.z2 = z2; a.z3 = z3; a.E = num_edges; a.nb = num_basis;
   a.status = kernel_status_word();
   chain::mlp_chain_forward_kernel<<<chain::grid_size(num_edges), chain::kThreads, chain::kSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("mlp_chain_forward");
@@ -339,7 +345,7 @@ int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, co
 
 int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0, const float* w1t_packed,
                             const float* w2t_packed, const float* z1, const float* z2, const float* z3, float* drb,
-                            void* stream) {
+                            const int64_t* drb_rows, int accumulate, void* stream) {
   if (num_edges < 0 || num_basis < 1 || num_basis > 8) {
     set_error("mlp chain: needs 1..8 basis functions (got %d)", num_basis);
     return ICTC_ERR_BAD_SPEC;
@@ -356,7 +362,7 @@ int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, 
   if (attr != cudaSuccess) { set_error("mlp chain smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   chain::Args a{};
   a.in = da3; a.w0 = w0; a.wa = w2t_packed; a.wb = w1t_packed; a.z1 = const_cast<float*>(z1); a.z2 = const_cast<float*>(z2);
-  a.z3 = const_cast<float*>(z3); a.drb = drb; a.E = num_edges; a.nb = num_basis;
+  a.z3 = const_cast<float*>(z3); a.drb = drb; a.rows = drb_rows; a.accumulate = accumulate ? 1 : 0; a.E = num_edges; a.nb = num_basis;
   a.status = kernel_status_word();
   chain::mlp_chain_backward_kernel<<<chain::grid_size(num_edges), chain::kThreads, chain::kSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("mlp_chain_backward");

@@ -159,17 +159,22 @@ class ForceEngine:
                 and tuple(fc[1].shape) == (64, 64) and tuple(fc[2].shape) == (64, 64)
                 and fc[3].shape[1] == 64 and fc[3].shape[0] % 64 == 0)
 
-    def _mlp(self, rb, L):
-        """Radial MLP: returns gates and the pre-activations needed by the reverse sweep."""
+    def _chain_ok(self, L):
+        return self._fused_mlp_ok(L) and "w3_umma" in L and self.mlp_chain
+
+    def _mlp(self, rb, L, rows=None):
+        """Radial MLP: returns gates and the pre-activations needed by the reverse sweep.  ``rows`` (tensor-memory
+        chain kernels only) makes row r of the MLP read rb[rows[r]]."""
         if self._fused_mlp_ok(L):
-            e, fc = rb.shape[0], L["fc"]
+            e, fc = (rb.shape[0] if rows is None else rows.numel()), L["fc"]
             nout = fc[3].shape[0]
             gates = torch.empty(e, nout, dtype=torch.float32, device=self.dev)
             pre = [torch.empty(e, 64, dtype=torch.float32, device=self.dev) for _ in range(3)]
             t0 = self._mark()
             if "w3_umma" in L:
                 if self.mlp_chain:
-                    _lib.check(self.lib.ictc_mlp_chain_forward(e, rb.shape[1], _lib.ptr(rb), fc[0].data_ptr(),
+                    _lib.check(self.lib.ictc_mlp_chain_forward(e, rb.shape[1], _lib.ptr(rb), _lib.ptr(rows),
+                                                               fc[0].data_ptr(),
                                                                L["hid_umma"][0].data_ptr(), L["hid_umma"][1].data_ptr(),
                                                                _lib.ptr(pre[0]), _lib.ptr(pre[1]), _lib.ptr(pre[2]),
                                                                self._st()), "mlp_chain_forward")
@@ -200,7 +205,9 @@ class ForceEngine:
             else:
                 return z, pre
 
-    def _mlp_bwd(self, dgates, pre, L, pairs=None):
+    def _mlp_bwd(self, dgates, pre, L, pairs=None, out=None, accumulate=False):
+        """Input gradient of the radial MLP.  With ``out`` [E, num_basis] (chain kernels, paired rows) the result of
+        pair u is written or added to out[rep_edge[u]] and ``out`` is returned."""
         if pairs is not None and not self._fused_mlp_ok(L):
             dgates = dgates.index_select(0, pairs[1]) + torch.where(
                 (pairs[2] >= 0).unsqueeze(1), dgates.index_select(0, pairs[2].clamp_min(0)), dgates.new_zeros(()))
@@ -209,7 +216,7 @@ class ForceEngine:
             ft = L["fc_t"]
             e = pre[0].shape[0]
             nb = ft[0].shape[0]
-            drb = torch.empty(e, nb, dtype=torch.float32, device=self.dev)
+            drb = torch.empty(e, nb, dtype=torch.float32, device=self.dev) if out is None else out
             t0 = self._mark()
             pa, pb = (None, None) if pairs is None else (pairs[1], pairs[2])
             if "w3t_umma" in L:
@@ -224,7 +231,8 @@ class ForceEngine:
                                                                 L["hid_t_umma"][0].data_ptr(),
                                                                 L["hid_t_umma"][1].data_ptr(), _lib.ptr(pre[0]),
                                                                 _lib.ptr(pre[1]), _lib.ptr(pre[2]), _lib.ptr(drb),
-                                                                self._st()), "mlp_chain_backward")
+                                                                _lib.ptr(pa) if out is not None else None,
+                                                                int(accumulate), self._st()), "mlp_chain_backward")
                 else:
                     _lib.check(self.lib.ictc_radial_mlp_hidden_backward(e, nb, _lib.ptr(da3), ft[0].data_ptr(),
                                                                         ft[1].data_ptr(), ft[2].data_ptr(),
@@ -321,7 +329,9 @@ class ForceEngine:
                                                       _lib.ptr(unit), _lib.ptr(length), st), "edge_geometry_forward")
             src_csr = build_csr(src, n_local, assume_sorted=False)
             grow = None if pairs is None else pairs[0]
-            rb_u = rb if pairs is None else rb.index_select(0, pairs[1])
+            by_rows = pairs is not None and self._chain_ok(L0) and self._chain_ok(L1)
+            rb_rows = pairs[1] if by_rows else None          # the MLP kernels gather / scatter the pair rows
+            rb_u = rb if (pairs is None or by_rows) else rb.index_select(0, pairs[1])
             sp_owned = species[:n_owned]
             s_count = self.emb.shape[0]
             # ---- layer 0
@@ -332,7 +342,7 @@ class ForceEngine:
                 self._lin(L0, ("up", 0), n_local, x0, 0, 1, c, u0, 0, 1, c)
             else:
                 u0 = torch.mm(x0, L0["up_t"][0])
-            g0, pre0 = self._mlp(rb_u, L0)
+            g0, pre0 = self._mlp(rb_u, L0, rb_rows)
             M0 = self._tp_forward(0, u0, sh, g0, src, dst_rowptr, n_owned, e, L0["tpw"], grow)   # [n, 9C]
             m0 = torch.empty_like(M0)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
@@ -363,7 +373,7 @@ class ForceEngine:
                     continue
                 u1[:, off * c:(off + mm) * c] = torch.mm(h1_full[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L1["up_t"][l]).view(n_local, mm * c)
-            g1, pre1 = self._mlp(rb_u, L1)
+            g1, pre1 = self._mlp(rb_u, L1, rb_rows)
             M1 = self._tp_forward(1, u1, sh, g1, src, dst_rowptr, n_owned, e, L1["tpw"], grow)   # [n, 35C]
             m1 = torch.empty(n_owned, 9 * c, dtype=torch.float32, device=dev)
             in_off = 0
@@ -403,7 +413,8 @@ class ForceEngine:
                     self._transpose(n_owned, cnt, mm, buf, 0, mm * cnt * c, v1, out_off, 35 * c, False)
                 out_off += cnt * mm * c
             du1, dsh1, dg1 = self._tp_adjoint(1, u1, sh, g1, dst, src_csr, v1, n_local, e, L1["tpw"], True, grow)
-            drb = self._mlp_bwd(dg1, pre1, L1, pairs)
+            drb = torch.zeros(e, nb, dtype=torch.float32, device=dev) if by_rows else None
+            drb = self._mlp_bwd(dg1, pre1, L1, pairs, drb, False)
             del dg1, g1, pre1
             dh1_full = torch.empty(n_local, 9 * c, dtype=torch.float32, device=dev)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
@@ -437,9 +448,12 @@ class ForceEngine:
                 v0[:, off * c:(off + mm) * c] = torch.mm(dm0[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L0["ml"][l]).view(n_owned, mm * c)
             _, dsh0, dg0 = self._tp_adjoint(0, u0, sh, g0, dst, src_csr, v0, n_local, e, L0["tpw"], False, grow)
-            drb += self._mlp_bwd(dg0, pre0, L0, pairs)
-            if pairs is not None:      # the pair's length gradient is carried by its representative edge
-                drb = torch.zeros(e, nb, dtype=torch.float32, device=dev).index_copy_(0, pairs[1], drb)
+            if by_rows:
+                self._mlp_bwd(dg0, pre0, L0, pairs, drb, True)
+            else:
+                drb += self._mlp_bwd(dg0, pre0, L0, pairs)
+                if pairs is not None:      # the pair's length gradient is carried by its representative edge
+                    drb = torch.zeros(e, nb, dtype=torch.float32, device=dev).index_copy_(0, pairs[1], drb)
             dsh1 += dsh0
             dvec = torch.empty(e, 3, dtype=torch.float32, device=dev)
             _lib.check(lib.ictc_edge_geometry_backward(_lib.ptr(unit), _lib.ptr(length), rmax, nb, pcut, e,

@@ -290,14 +290,17 @@ int ictc_channel_linear_tc(int64_t num_rows, int k_chunks, int n_chunks, const f
  * the two 64 x 64 layers are three-term TF32 tcgen05.mma products with the activations kept in TMEM, the
  * num_basis-wide layer is fp32 FMA.  w1_packed / w2_packed come from ictc_gate_pack_weights(64, W, 0, ...),
  * w1t_packed / w2t_packed from ictc_gate_pack_weights(64, W, 1, ...); w0 is the plain [64, num_basis] matrix.
- * forward: rb [E, num_basis] -> pre-activations z1, z2, z3 [E, 64].
- * backward: da3 [E, 64] (gradient of silu(z3)) and z1..z3 -> drb [E, num_basis].
+ * forward: rb rows -> pre-activations z1, z2, z3 [E, 64]; row r reads rb[rb_rows[r]] (rb_rows NULL: rb[r]).
+ * backward: da3 [E, 64] (gradient of silu(z3)) and z1..z3 -> drb; row r is written (accumulate == 0) or added
+ *   (accumulate != 0) to drb[drb_rows[r]] (drb_rows NULL: drb[r]); a row index that repeats (the inert padding
+ *   rows of a fixed-capacity pair table) receives an unspecified one of its results.
  * z*, da3 and the packed weights 32-byte aligned.  Bounded waits report codes 41-46. */
-int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, const float* w0, const float* w1_packed,
-                           const float* w2_packed, float* z1, float* z2, float* z3, void* stream);
+int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, const int64_t* rb_rows, const float* w0,
+                           const float* w1_packed, const float* w2_packed, float* z1, float* z2, float* z3,
+                           void* stream);
 int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0, const float* w1t_packed,
                             const float* w2t_packed, const float* z1, const float* z2, const float* z3, float* drb,
-                            void* stream);
+                            const int64_t* drb_rows, int accumulate, void* stream);
 
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).

@@ -172,7 +172,7 @@ def test_mlp_chain_hidden_layers(edges, nb):
     st = torch.cuda.current_stream().cuda_stream
     zs = [torch.full((edges, 64), float("nan"), device="cuda") for _ in range(3)]
     packed = [_pack(lib, ws[1], 0), _pack(lib, ws[2], 0), _pack(lib, ws[1], 1), _pack(lib, ws[2], 1)]
-    _lib.check(lib.ictc_mlp_chain_forward(edges, nb, rb.data_ptr(), ws[0].data_ptr(), packed[0].data_ptr(),
+    _lib.check(lib.ictc_mlp_chain_forward(edges, nb, rb.data_ptr(), None, ws[0].data_ptr(), packed[0].data_ptr(),
                                           packed[1].data_ptr(), *[z.data_ptr() for z in zs], st), "chain fwd")
     assert _status(lib) == 0
     x = rb.double().cpu().requires_grad_(True)
@@ -190,8 +190,44 @@ def test_mlp_chain_hidden_layers(edges, nb):
     da3d = da3.cuda()
     _lib.check(lib.ictc_mlp_chain_backward(edges, nb, da3d.data_ptr(), ws[0].data_ptr(), packed[2].data_ptr(),
                                            packed[3].data_ptr(), *[z.data_ptr() for z in zs], drb.data_ptr(),
-                                           st), "chain bwd")
+                                           None, 0, st), "chain bwd")
     assert _status(lib) == 0
     assert torch.isfinite(drb).all()
     err = float((drb.double().cpu() - ref_d).abs().max() / ref_d.abs().max())
     assert err < 5e-6, err
+
+
+def test_mlp_chain_row_indices_gather_and_scatter():
+    """Row indices: the forward reads rb[rows[r]], the backward writes or adds to drb[rows[r]]."""
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    torch.manual_seed(3)
+    total, edges, nb = 900, 400, 8
+    rb = (torch.randn(total, nb) * 0.7).cuda()
+    rows = torch.randperm(total)[:edges].cuda()
+    ws = [w.cuda().contiguous() for w in (torch.randn(64, nb) / nb ** 0.5, torch.randn(64, 64) / 8, torch.randn(64, 64) / 8)]
+    packed = [_pack(lib, ws[1], 0), _pack(lib, ws[2], 0), _pack(lib, ws[1], 1), _pack(lib, ws[2], 1)]
+    st = torch.cuda.current_stream().cuda_stream
+    za = [torch.empty(edges, 64, device="cuda") for _ in range(3)]
+    zb = [torch.empty(edges, 64, device="cuda") for _ in range(3)]
+    sub = rb[rows].contiguous()
+    _lib.check(lib.ictc_mlp_chain_forward(edges, nb, sub.data_ptr(), None, ws[0].data_ptr(), packed[0].data_ptr(),
+                                          packed[1].data_ptr(), *[z.data_ptr() for z in za], st), "fwd")
+    _lib.check(lib.ictc_mlp_chain_forward(edges, nb, rb.data_ptr(), rows.data_ptr(), ws[0].data_ptr(),
+                                          packed[0].data_ptr(), packed[1].data_ptr(), *[z.data_ptr() for z in zb], st),
+               "fwd rows")
+    for x, y in zip(za, zb):
+        assert torch.equal(x, y)
+    da3 = torch.randn(edges, 64, device="cuda")
+    dense = torch.empty(edges, nb, device="cuda")
+    _lib.check(lib.ictc_mlp_chain_backward(edges, nb, da3.data_ptr(), ws[0].data_ptr(), packed[2].data_ptr(),
+                                           packed[3].data_ptr(), *[z.data_ptr() for z in za], dense.data_ptr(), None, 0,
+                                           st), "bwd")
+    out = torch.ones(total, nb, device="cuda")
+    _lib.check(lib.ictc_mlp_chain_backward(edges, nb, da3.data_ptr(), ws[0].data_ptr(), packed[2].data_ptr(),
+                                           packed[3].data_ptr(), *[z.data_ptr() for z in za], out.data_ptr(),
+                                           rows.data_ptr(), 1, st), "bwd rows")
+    assert _status(lib) == 0
+    expect = torch.ones(total, nb, device="cuda")
+    expect[rows] += dense
+    assert torch.equal(out, expect)
