@@ -65,6 +65,13 @@ template <> __device__ __forceinline__ Vec<2> lds_vec<2>(const unsigned char* p)
 // are mostly L2 hits and are loaded straight into registers, which keeps shared-memory traffic low.
 constexpr bool kStageRows = false;
 
+// Resident blocks per SM the forward kernel is compiled for (caps its registers at 65536 / (128 * blocks);
+// the adjoint kernels would spill at that limit and keep the compiler's choice).
+#ifndef ICTC_TMA_MIN_BLOCKS
+#define ICTC_TMA_MIN_BLOCKS 3
+#endif
+constexpr int kTmaMinBlocks = ICTC_TMA_MIN_BLOCKS;
+
 template <class S, class F, int CPL, int STAGES, bool ADJ> struct TmaLayout {
   static constexpr int C = 32 * CPL;
   static constexpr int R = (F::NB + 31) / 32, NBP = R * 32;
@@ -80,7 +87,7 @@ template <class S, class F, int CPL, int STAGES, bool ADJ> struct TmaLayout {
 
 // ------------------------------------------------------------------------------------------------
 template <class S, class F, int CPL, int STAGES>
-__global__ void __launch_bounds__(kFastWarps * 32) tp_graph_forward_tma_kernel(TpArgs a) {
+__global__ void __launch_bounds__(kFastWarps * 32, kTmaMinBlocks) tp_graph_forward_tma_kernel(TpArgs a) {
   using V = Vec<CPL>;
   using L = TmaLayout<S, F, CPL, STAGES, false>;
   constexpr int C = L::C;
