@@ -26,9 +26,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -78,64 +76,55 @@ def make_inputs(seed, device, num_atoms=NUM_ATOMS, dtype=torch.float32):
 
 
 # ------------------------------------------------------------------------------------ clocks
-_SAMPLER_CODE = r"""
-import sys, time
-import pynvml as N
-N.nvmlInit()
-h = N.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
-mx = N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM)
-bits = {"hw_slowdown": N.nvmlClocksThrottleReasonHwSlowdown, "hw_thermal_slowdown": N.nvmlClocksThrottleReasonHwThermalSlowdown,
-        "sw_thermal_slowdown": N.nvmlClocksThrottleReasonSwThermalSlowdown, "sw_power_cap": N.nvmlClocksThrottleReasonSwPowerCap}
-while True:
-    sm = N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM)
-    r = N.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-    print(sm, mx, ",".join(k for k, b in bits.items() if r & b), flush=True)
-    time.sleep(0.5)
-"""
-
-
 class ClockSampler:
-    """Samples the SM clock and the throttle reasons every 500 ms from a separate small process (NVML:
-    two queries per sample, which disturbs kernel launches far less than an nvidia-smi loop)."""
+    """SM clock and throttle reasons of one GPU, read through NVML from the benchmark's own thread between
+    steps (``tick``; at most one reading per ``period`` seconds).  A separate sampling process or an nvidia-smi
+    loop slows an eager multi-GPU step by tens of per cent on these hosts; two in-process queries do not."""
 
-    def __init__(self, gpu_index):
-        self.rows, self.proc = [], None
+    _BITS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, gpu_index, period=0.25):
+        self.rows, self.period, self.last, self.active = [], period, 0.0, False
+        self.nvml = self.handle = None
         visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-        self.gpu = int(visible.split(",")[gpu_index]) if visible and visible.replace(",", "").isdigit() else gpu_index
+        gpu = int(visible.split(",")[gpu_index]) if visible and visible.replace(",", "").isdigit() else gpu_index
+        try:
+            import pynvml as N
+            N.nvmlInit()
+            self.nvml, self.handle = N, N.nvmlDeviceGetHandleByIndex(gpu)
+            self.max = float(N.nvmlDeviceGetMaxClockInfo(self.handle, N.NVML_CLOCK_SM))
+            self.masks = {"hw_slowdown": N.nvmlClocksThrottleReasonHwSlowdown,
+                          "hw_thermal_slowdown": N.nvmlClocksThrottleReasonHwThermalSlowdown,
+                          "sw_thermal_slowdown": N.nvmlClocksThrottleReasonSwThermalSlowdown,
+                          "sw_power_cap": N.nvmlClocksThrottleReasonSwPowerCap}
+        except Exception:       # noqa: BLE001 - no NVML on this box: the bench line says so
+            self.nvml = None
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_CODE, str(self.gpu)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-            time.sleep(1.0)      # let the sampler import and initialise before the timed region
-        except OSError:
-            self.proc = None
+        self.active, self.last = True, 0.0
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append(line.split())
+    def tick(self):
+        """Called between steps of the timed region."""
+        if not self.active or self.nvml is None:
+            return
+        now = time.perf_counter()
+        if now - self.last < self.period:
+            return
+        self.last = now
+        try:
+            sm = self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)
+            r = self.nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+            self.rows.append((float(sm), [k for k, b in self.masks.items() if r & b]))
+        except Exception:       # noqa: BLE001
+            pass
 
     def stop(self):
-        if self.proc is None:
+        self.active = False
+        if self.nvml is None or not self.rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["sampler unavailable"]}
-        time.sleep(0.25)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, reasons = [], None, set()
-        for row in self.rows:
-            try:
-                sm.append(float(row[0]))
-                smax = float(row[1])
-            except (ValueError, IndexError):
-                continue
-            if len(row) > 2:
-                reasons.update(x for x in row[2].split(",") if x)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        reasons = sorted({x for _, rs in self.rows for x in rs})
+        return {"sm_mhz": float(np.median([sm for sm, _ in self.rows])), "sm_max_mhz": self.max, "reasons": reasons,
+                "samples": len(self.rows)}
 
 
 # ------------------------------------------------------------------------------------ CPU arm
@@ -316,7 +305,7 @@ def main_md(args, rank, world, local):
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    md.run(args.steps, check_every=args.steps)      # one capacity check (a host read-back) at the end
+    md.run(args.steps, check_every=args.steps, on_step=sampler.tick)   # one capacity check (a host read-back) at the end
     stop.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -476,6 +465,7 @@ def main():
     start.record()
     for _ in range(args.steps):
         step()
+        sampler.tick()
     stop.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None

@@ -138,6 +138,22 @@ class ForceEngine:
                                                    self._st()), "channel_linear_tc")
         self._done("channel_linear_tc", t0)
 
+    # ---------------------------------------------------------------- buffers
+    @staticmethod
+    def bucket(rows):
+        """Row count rounded up to 1/16 of its power of two.  Edge and atom counts change a little every MD step;
+        allocating the rounded size keeps the sizes repeating, so the caching allocator reuses its blocks
+        instead of splitting, freeing and re-allocating multi-GB segments."""
+        rows = int(rows)
+        if rows <= 4096:
+            return 4096
+        g = 1 << (rows.bit_length() - 5)
+        return (rows + g - 1) // g * g
+
+    def _rows(self, rows, *cols, zero=False):
+        make = torch.zeros if zero else torch.empty
+        return make(self.bucket(rows), *cols, dtype=torch.float32, device=self.dev)[:rows]
+
     # ---------------------------------------------------------------- small launch helpers
     def _st(self):
         return _lib.stream(self.dev)
@@ -168,8 +184,8 @@ class ForceEngine:
         if self._fused_mlp_ok(L):
             e, fc = (rb.shape[0] if rows is None else rows.numel()), L["fc"]
             nout = fc[3].shape[0]
-            gates = torch.empty(e, nout, dtype=torch.float32, device=self.dev)
-            pre = [torch.empty(e, 64, dtype=torch.float32, device=self.dev) for _ in range(3)]
+            gates = self._rows(e, nout)
+            pre = [self._rows(e, 64) for _ in range(3)]
             t0 = self._mark()
             if "w3_umma" in L:
                 if self.mlp_chain:
@@ -216,11 +232,11 @@ class ForceEngine:
             ft = L["fc_t"]
             e = pre[0].shape[0]
             nb = ft[0].shape[0]
-            drb = torch.empty(e, nb, dtype=torch.float32, device=self.dev) if out is None else out
+            drb = self._rows(e, nb) if out is None else out
             t0 = self._mark()
             pa, pb = (None, None) if pairs is None else (pairs[1], pairs[2])
             if "w3t_umma" in L:
-                da3 = torch.empty(e, 64, dtype=torch.float32, device=self.dev)
+                da3 = self._rows(e, 64)
                 _lib.check(self.lib.ictc_gate_gemm_backward(e, dgates.shape[1], _lib.ptr(dgates), _lib.ptr(pa),
                                                             _lib.ptr(pb), L["w3t_umma"].data_ptr(), _lib.ptr(da3),
                                                             self._st()), "gate_gemm_backward")
@@ -272,7 +288,7 @@ class ForceEngine:
 
     def _tp_forward(self, layer, x, sh, g, src, rowptr, rows, e, tpw, grow=None):
         c = self.c
-        out = torch.empty(rows, (9 if layer == 0 else 35) * c, dtype=torch.float32, device=self.dev)
+        out = self._rows(rows, (9 if layer == 0 else 35) * c)
         t0 = self._mark()
         _lib.check(self.lib.ictc_tp_graph_forward_shared(self._spec[layer], c, rows, e, x.data_ptr(), sh.data_ptr(),
                                                          _lib.ptr(tpw), g.data_ptr(), _lib.ptr(grow), src.data_ptr(),
@@ -283,9 +299,9 @@ class ForceEngine:
 
     def _tp_adjoint(self, layer, x, sh, g, dst, src_csr, v, n_rows, e, tpw, need_x, grow=None):
         c = self.c
-        dx = torch.empty_like(x) if need_x else None
-        dsh = torch.empty_like(sh)
-        dg = torch.empty(e, g.shape[1], dtype=torch.float32, device=self.dev)
+        dx = self._rows(x.shape[0], x.shape[1]) if need_x else None
+        dsh = self._rows(e, 9)
+        dg = self._rows(e, g.shape[1])
         rowptr, order = src_csr
         t0 = self._mark()
         _lib.check(self.lib.ictc_tp_graph_adjoint_shared(self._spec[layer], c, n_rows, e, x.data_ptr(), sh.data_ptr(),
@@ -319,10 +335,10 @@ class ForceEngine:
         nb, pcut, rmax = m.number_of_basis, m.polynomial_cutoff_p, m.max_radius
         with _lib.on_device(dev):
             # ---- edge geometry
-            sh = torch.empty(e, 9, dtype=torch.float32, device=dev)
-            rb = torch.empty(e, nb, dtype=torch.float32, device=dev)
-            unit = torch.empty(e, 3, dtype=torch.float32, device=dev)
-            length = torch.empty(e, dtype=torch.float32, device=dev)
+            sh = self._rows(e, 9)
+            rb = self._rows(e, nb)
+            unit = self._rows(e, 3)
+            length = self._rows(e)
             box_c = (C.c_float * 3)(*[float(b) for b in box])
             _lib.check(lib.ictc_edge_geometry_forward(pos.data_ptr(), _lib.ptr(src), _lib.ptr(dst), _lib.ptr(shifts),
                                                       box_c, rmax, nb, pcut, e, _lib.ptr(sh), _lib.ptr(rb),
@@ -338,13 +354,13 @@ class ForceEngine:
             x0 = self.emb.index_select(0, species)                               # [N_local, C]
             tc = "packed" in L0 and "packed" in L1
             if tc:
-                u0 = torch.empty(n_local, c, dtype=torch.float32, device=dev)
+                u0 = self._rows(n_local, c)
                 self._lin(L0, ("up", 0), n_local, x0, 0, 1, c, u0, 0, 1, c)
             else:
                 u0 = torch.mm(x0, L0["up_t"][0])
             g0, pre0 = self._mlp(rb_u, L0, rb_rows)
             M0 = self._tp_forward(0, u0, sh, g0, src, dst_rowptr, n_owned, e, L0["tpw"], grow)   # [n, 9C]
-            m0 = torch.empty_like(M0)
+            m0 = self._rows(n_owned, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 if tc:
                     self._lin(L0, ("ml", l), n_owned * mm, M0, off * c, mm, 9 * c, m0, off * c, mm, 9 * c)
@@ -354,7 +370,7 @@ class ForceEngine:
             sc0 = self._species_linear(x0[:n_owned], sp_owned, L0["sc_fwd"], s_count)
             call0 = _ScCall(c, 2, s_count, sp_owned, True)
             y0 = call0.forward(m0, L0["bank"])                                    # [n, 9C]
-            h1 = torch.empty_like(y0)
+            h1 = self._rows(n_owned, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 if tc:
                     self._lin(L0, ("pl", l), n_owned * mm, y0, off * c, mm, 9 * c, h1, off * c, mm, 9 * c)
@@ -366,7 +382,7 @@ class ForceEngine:
             # ---- halo
             h1_full = h1 if plan is None else torch.cat((h1, plan.forward(h1)), 0)
             # ---- layer 1
-            u1 = torch.empty(n_local, 9 * c, dtype=torch.float32, device=dev)
+            u1 = self._rows(n_local, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 if tc:
                     self._lin(L1, ("up", l), n_local * mm, h1_full, off * c, mm, 9 * c, u1, off * c, mm, 9 * c)
@@ -375,7 +391,7 @@ class ForceEngine:
                                                          L1["up_t"][l]).view(n_local, mm * c)
             g1, pre1 = self._mlp(rb_u, L1, rb_rows)
             M1 = self._tp_forward(1, u1, sh, g1, src, dst_rowptr, n_owned, e, L1["tpw"], grow)   # [n, 35C]
-            m1 = torch.empty(n_owned, 9 * c, dtype=torch.float32, device=dev)
+            m1 = self._rows(n_owned, 9 * c)
             in_off = 0
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 cnt = L1["counts"][l]
@@ -402,7 +418,7 @@ class ForceEngine:
             dh2 = torch.mm(dz, self.ro1_w1)                                        # [n, C]
             dy1 = torch.mm(dh2, L1["pl_t"][0])
             dm1, _ = call1.adjoint(m1, L1["bank"], dy1, (True, False))             # [n, 9C]
-            v1 = torch.empty(n_owned, 35 * c, dtype=torch.float32, device=dev)
+            v1 = self._rows(n_owned, 35 * c)
             out_off = 0
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 cnt = L1["counts"][l]
@@ -413,10 +429,10 @@ class ForceEngine:
                     self._transpose(n_owned, cnt, mm, buf, 0, mm * cnt * c, v1, out_off, 35 * c, False)
                 out_off += cnt * mm * c
             du1, dsh1, dg1 = self._tp_adjoint(1, u1, sh, g1, dst, src_csr, v1, n_local, e, L1["tpw"], True, grow)
-            drb = torch.zeros(e, nb, dtype=torch.float32, device=dev) if by_rows else None
+            drb = self._rows(e, nb, zero=True) if by_rows else None
             drb = self._mlp_bwd(dg1, pre1, L1, pairs, drb, False)
             del dg1, g1, pre1
-            dh1_full = torch.empty(n_local, 9 * c, dtype=torch.float32, device=dev)
+            dh1_full = self._rows(n_local, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 if tc:
                     self._lin(L1, ("up_b", l), n_local * mm, du1, off * c, mm, 9 * c, dh1_full, off * c, mm, 9 * c)
@@ -432,7 +448,7 @@ class ForceEngine:
             full = torch.mm(dsc1, L1["sc_bwd"]).view(n_owned, s_count, c)
             dh1[:, :c] += full.gather(1, sp_owned.view(-1, 1, 1).expand(-1, 1, c)).squeeze(1)
             dh1[:, :c] += self.ro0
-            dy0 = torch.empty_like(dh1)
+            dy0 = self._rows(n_owned, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 if tc:
                     self._lin(L0, ("pl_b", l), n_owned * mm, dh1, off * c, mm, 9 * c, dy0, off * c, mm, 9 * c)
@@ -440,7 +456,7 @@ class ForceEngine:
                 dy0[:, off * c:(off + mm) * c] = torch.mm(dh1[:, off * c:(off + mm) * c].reshape(-1, c),
                                                           L0["pl_t"][l]).view(n_owned, mm * c)
             dm0, _ = call0.adjoint(m0, L0["bank"], dy0, (True, False))
-            v0 = torch.empty_like(dm0)
+            v0 = self._rows(n_owned, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 if tc:
                     self._lin(L0, ("ml_b", l), n_owned * mm, dm0, off * c, mm, 9 * c, v0, off * c, mm, 9 * c)
@@ -455,11 +471,11 @@ class ForceEngine:
                 if pairs is not None:      # the pair's length gradient is carried by its representative edge
                     drb = torch.zeros(e, nb, dtype=torch.float32, device=dev).index_copy_(0, pairs[1], drb)
             dsh1 += dsh0
-            dvec = torch.empty(e, 3, dtype=torch.float32, device=dev)
+            dvec = self._rows(e, 3)
             _lib.check(lib.ictc_edge_geometry_backward(_lib.ptr(unit), _lib.ptr(length), rmax, nb, pcut, e,
                                                        _lib.ptr(dsh1), _lib.ptr(drb), _lib.ptr(dvec), st),
                        "edge_geometry_backward")
-            grad = torch.empty(n_local, 3, dtype=torch.float32, device=dev)
+            grad = self._rows(n_local, 3)
             _lib.check(lib.ictc_position_gradient(n_local, n_owned, dst_rowptr.data_ptr(), src_csr[0].data_ptr(),
                                                   _lib.ptr(src_csr[1]), _lib.ptr(dvec), grad.data_ptr(), st),
                        "position_gradient")

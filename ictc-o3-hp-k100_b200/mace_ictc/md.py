@@ -24,6 +24,15 @@ ACCEL = 9.64853321e-3
 MASSES = {1: 1.008, 6: 12.011, 8: 15.999}
 
 
+def _bucket(rows):
+    """Allocation size for a per-edge array: see ``ForceEngine.bucket`` (sizes that repeat from step to step)."""
+    rows = int(rows)
+    if rows <= 4096:
+        return 4096
+    g = 1 << (rows.bit_length() - 5)
+    return (rows + g - 1) // g * g
+
+
 def neighbor_list(pos, num_centres, lo, hi, box, periodic, cutoff, return_keys=False):
     """Edges (src=j, dst=i) of the first ``num_centres`` rows, sorted by (dst, src, shift).
 
@@ -49,10 +58,11 @@ def neighbor_list(pos, num_centres, lo, hi, box, periodic, cutoff, return_keys=F
         _lib.check(lib.ictc_inclusive_scan_i64(rowptr.data_ptr(), num_centres + 1, scan.data_ptr(), st),
                    "ictc_inclusive_scan_i64")
         e = int(rowptr[-1].item())
-        src = torch.empty(e, dtype=torch.int64, device=dev)
-        dst = torch.empty(e, dtype=torch.int64, device=dev)
-        shifts = torch.empty(e, 3, dtype=torch.float32, device=dev)
-        keys = torch.empty(e, dtype=torch.int64, device=dev)
+        eb = _bucket(e)
+        src = torch.empty(eb, dtype=torch.int64, device=dev)[:e]
+        dst = torch.empty(eb, dtype=torch.int64, device=dev)[:e]
+        shifts = torch.empty(eb, 3, dtype=torch.float32, device=dev)[:e]
+        keys = torch.empty(eb, dtype=torch.int64, device=dev)[:e]
         _lib.check(lib.ictc_neighbor_fill(pos.data_ptr(), n, num_centres, lo_c, hi_c, box_c, per_c, float(cutoff),
                                           rowptr.data_ptr(), e, _lib.ptr(src), _lib.ptr(dst), _lib.ptr(shifts),
                                           _lib.ptr(keys), scratch.data_ptr(), st), "ictc_neighbor_fill")
@@ -66,13 +76,14 @@ def edge_pairs(rowptr, dst, keys, num_centres):
     (gate_row [E], rep_edge [U], other_edge [U]); see ``ictc_neighbor_pairs``."""
     lib, dev = _lib.load(), dst.device
     e = int(dst.numel())
-    rev = torch.empty(e, dtype=torch.int64, device=dev)
-    scan = torch.empty(e, dtype=torch.int64, device=dev)
-    gate_row = torch.empty(e, dtype=torch.int64, device=dev)
-    rep = torch.empty(e, dtype=torch.int64, device=dev)
-    other = torch.empty(e, dtype=torch.int64, device=dev)
+    eb = _bucket(e)
+    rev = torch.empty(eb, dtype=torch.int64, device=dev)
+    scan = torch.empty(eb, dtype=torch.int64, device=dev)
+    gate_row = torch.empty(eb, dtype=torch.int64, device=dev)[:e]
+    rep = torch.empty(eb, dtype=torch.int64, device=dev)
+    other = torch.empty(eb, dtype=torch.int64, device=dev)
     num = torch.zeros(1, dtype=torch.int64, device=dev)
-    scratch = torch.empty(int(lib.ictc_scan_scratch_bytes(e)), dtype=torch.uint8, device=dev)
+    scratch = torch.empty(int(lib.ictc_scan_scratch_bytes(eb)), dtype=torch.uint8, device=dev)
     with _lib.on_device(dev):
         _lib.check(lib.ictc_neighbor_pairs(rowptr.data_ptr(), _lib.ptr(dst), _lib.ptr(keys), num_centres, e, e,
                                            rowptr.data_ptr() + 8 * num_centres, _lib.ptr(rev), _lib.ptr(scan),
@@ -309,13 +320,16 @@ class MolecularDynamics:
 
     graph_rebuilds = 0
 
-    def run(self, steps, check_every=25, margin=1.10):
+    def run(self, steps, check_every=25, margin=1.10, on_step=None):
         """Advance ``steps`` MD steps.  With a recorded graph the edge-capacity flag is read every
         ``check_every`` steps; if the neighbour list outgrew the recorded buffers the block of steps is
-        repeated from a snapshot with a larger capacity (steps run after an overflow are invalid)."""
+        repeated from a snapshot with a larger capacity (steps run after an overflow are invalid).
+        ``on_step`` is called on the host after every step has been launched."""
         if self.graph is None:
             for _ in range(steps):
                 self.step()
+                if on_step is not None:
+                    on_step()
             return
         done = 0
         while done < steps:
@@ -323,6 +337,8 @@ class MolecularDynamics:
             snap = (self.pos.clone(), self.vel.clone())
             for _ in range(block):
                 self.graph.replay()
+                if on_step is not None:
+                    on_step()
             if self.check_overflow():
                 self.pos.copy_(snap[0])
                 self.vel.copy_(snap[1])
