@@ -209,6 +209,7 @@ class MolecularDynamics:
         self.forces = None
         self.energy = None
         self.num_edges = 0
+        self.num_gate_rows = 0       # rows of the gate table of the last force call (edge pairs, or edges)
         self.launches = 0
         self.graph = None
         self._static = None
@@ -227,6 +228,7 @@ class MolecularDynamics:
         self.num_edges = int(src.numel())
         if self.engine is not None:
             pairs = edge_pairs(rowptr, dst, keys, n) if self.share_gates else None
+            self.num_gate_rows = int(pairs[1].numel()) if pairs is not None else self.num_edges
             energy, grad, _ = self.engine.energy_and_gradient(self.pos, self.species, src, dst, shifts, box, n, rowptr,
                                                               pairs=pairs)
             if self._static is not None:            # keep the buffers the recorded graph reads and writes
@@ -266,6 +268,7 @@ class MolecularDynamics:
         n_local = local.shape[0]
         if self.engine is not None:
             pairs = edge_pairs(rowptr, dst, keys, n_owned) if self.share_gates else None
+            self.num_gate_rows = int(pairs[1].numel()) if pairs is not None else self.num_edges
             energy, grad, _ = self.engine.energy_and_gradient(local, self.species.index_select(0, ids), src, dst, None,
                                                               self.box.tolist(), n_owned, rowptr, plan, pairs=pairs)
             total = torch.zeros_like(self.pos)
