@@ -88,12 +88,17 @@ def decompose(pos: torch.Tensor, box: torch.Tensor, grid, rank: int, cutoff: flo
     shifts3 = torch.tensor([-1.0, 0.0, 1.0], dtype=torch.float64, device=dev)
     q = p64.unsqueeze(-1) + shifts3 * box_d.view(1, 3, 1)                       # [N, axis, image]
     inside = (q >= (lo_d - cutoff).view(1, 3, 1)) & (q < (hi_d + cutoff).view(1, 3, 1))
+    # only atoms with at least one image inside the extended brick on EVERY axis can contribute: expand the 27
+    # image combinations for those candidates alone (the replicated position table grows with the number of
+    # ranks, the candidates do not)
+    cand = torch.nonzero(inside.any(dim=2).all(dim=1)).flatten()
+    inside_c = inside.index_select(0, cand)
     codes = torch.arange(27, device=dev)
     sx, sy, sz = codes // 9, (codes // 3) % 3, codes % 3                        # image index per axis
-    valid = inside[:, 0, :][:, sx] & inside[:, 1, :][:, sy] & inside[:, 2, :][:, sz]   # [N, 27]
-    valid[:, 13] &= owner != rank                                               # zero shift: ghosts only
+    valid = inside_c[:, 0, :][:, sx] & inside_c[:, 1, :][:, sy] & inside_c[:, 2, :][:, sz]   # [M, 27]
+    valid[:, 13] &= owner.index_select(0, cand) != rank                         # zero shift: ghosts only
     pairs = torch.nonzero(valid.t())                                            # sorted by (image code, atom id)
-    code, ghost_ids = pairs[:, 0], pairs[:, 1].contiguous()
+    code, ghost_ids = pairs[:, 0], cand.index_select(0, pairs[:, 1]).contiguous()
     ghost_shift = torch.stack((code // 9 - 1, (code // 3) % 3 - 1, code % 3 - 1), 1).to(torch.float32)
     return LocalDomain(owned, ghost_ids, ghost_shift, lo, hi, owner, owner_row)
 
