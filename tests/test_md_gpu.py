@@ -219,3 +219,46 @@ def test_radial_pairs_are_exact_and_do_not_change_forces():
     fa, fb = a.compute_forces(), b.compute_forces()
     assert float((fa - fb).abs().max()) < 5e-6 * float(fb.abs().max())
     assert abs(float(a.energy) - float(b.energy)) < 1e-6 * abs(float(b.energy))
+
+
+@pytest.mark.parametrize("p", [5, 6])
+def test_edge_geometry_kernel_matches_the_reference_radial_embedding(p):
+    """The fused geometry kernel's radial basis and its length derivative against vectors computed by the
+    reference's own `mace_radial_embedding` (tests/golden/radial_bessel8_rmax4p5.npz)."""
+    import os
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "radial_bessel8_rmax4p5.npz"))
+    keep = g["r"] < 4.5
+    r = torch.tensor(g["r"][keep], dtype=torch.float64)
+    e = r.numel()
+    torch.manual_seed(0)
+    unit = torch.nn.functional.normalize(torch.randn(e, 3, dtype=torch.float64), dim=-1)
+    pos = torch.zeros(2 * e, 3, dtype=torch.float64)
+    pos[0::2] = torch.rand(e, 3, dtype=torch.float64) * 3.0 + 5.0
+    pos[1::2] = pos[0::2] + unit * r[:, None]
+    dev = "cuda"
+    posd = pos.float().to(dev)
+    src = torch.arange(1, 2 * e, 2, device=dev)          # one edge per pair of points, length r
+    dst = torch.arange(0, 2 * e, 2, device=dev)
+    sh = torch.empty(e, 9, device=dev)
+    rb = torch.empty(e, 8, device=dev)
+    un = torch.empty(e, 3, device=dev)
+    ln = torch.empty(e, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.ictc_edge_geometry_forward(posd.data_ptr(), src.data_ptr(), dst.data_ptr(), None, None, 4.5, 8, p, e,
+                                              sh.data_ptr(), rb.data_ptr(), un.data_ptr(), ln.data_ptr(), st), "geom")
+    # the fp32 positions give a slightly different length: compare at the length the kernel saw
+    want = torch.tensor(g[f"emb_p{p}"][keep])
+    slope = torch.tensor(g[f"grad_p{p}"][keep])
+    assert float((ln.double().cpu() - r).abs().max()) < 5e-6
+    err = float((rb.double().cpu() - want).abs().max() / want.abs().max())
+    assert err < 1e-5, err
+    w = torch.tensor(g["w"], dtype=torch.float32, device=dev)
+    drb = w.unsqueeze(0).expand(e, -1).contiguous()
+    dsh = torch.zeros(e, 9, device=dev)
+    dvec = torch.empty(e, 3, device=dev)
+    _lib.check(lib.ictc_edge_geometry_backward(un.data_ptr(), ln.data_ptr(), 4.5, 8, p, e, dsh.data_ptr(), drb.data_ptr(),
+                                               dvec.data_ptr(), st), "geom bwd")
+    dr = (dvec * un).sum(-1).double().cpu()
+    assert float((dr - slope).abs().max() / slope.abs().max()) < 1e-5

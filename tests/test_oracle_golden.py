@@ -139,3 +139,17 @@ def test_symmetric_contraction_equivariant_scalar_output():
     b = O.symmetric_contraction(feats(dirs @ q.T), species, weights, 0)
     assert a.shape == (5, c)
     assert torch.allclose(a, b, atol=1e-10, rtol=1e-10)
+
+
+@pytest.mark.parametrize("p", [5, 6])
+def test_radial_embedding_matches_the_reference_function(golden_dir, p):
+    """Bessel basis x polynomial cutoff of the model oracle against vectors computed by the reference's own
+    `mace_radial_embedding` (tests/golden/make_golden_radial.py), values and derivative."""
+    from oracle.model_oracle import radial_embedding
+    g = np.load(os.path.join(golden_dir, "radial_bessel8_rmax4p5.npz"))
+    r = torch.tensor(g["r"], dtype=torch.float64, requires_grad=True)
+    emb = radial_embedding(r, float(g["r_max"]), 8, p)
+    assert torch.allclose(emb, torch.tensor(g[f"emb_p{p}"]), rtol=1e-12, atol=1e-13)
+    (grad,) = torch.autograd.grad((emb * torch.tensor(g["w"])).sum(), r)
+    assert torch.allclose(grad, torch.tensor(g[f"grad_p{p}"]), rtol=1e-11, atol=1e-12)
+    assert float(emb[-2:].abs().max()) == 0.0          # beyond the cutoff
