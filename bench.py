@@ -305,9 +305,25 @@ def main_md(args, rank, world, local):
         sampler.start()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    md.run(args.steps, check_every=args.steps, on_step=sampler.tick)   # one capacity check (a host read-back) at the end
-    stop.record()
+    for attempt in range(3):
+        start.record()
+        if md.graph is not None:
+            # the replays are queued at once; the host then polls for completion and reads the clocks meanwhile
+            for _ in range(args.steps):
+                md.step()
+            stop.record()
+            while not stop.query():
+                sampler.tick()
+                time.sleep(0.02)
+            if not md.check_overflow():
+                break
+            md.graph, md._static = None, None          # the edge list outgrew the recorded buffers: record again
+            md.compute_forces()
+            graph_cap = md.enable_graph(margin=1.10 + 0.1 * (attempt + 1))
+        else:
+            md.run(args.steps, on_step=sampler.tick)
+            stop.record()
+            break
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = start.elapsed_time(stop) / args.steps
