@@ -56,10 +56,6 @@ __device__ __forceinline__ void give_up(Barriers* b, int* status, int code) {
   b->failed = 1;
   if (status) atomicExch(status, code);
 }
-__device__ __forceinline__ float dsilu_s(float v) {
-  const float s = 1.f / (1.f + expf(-v));
-  return kSiluScale * s * (1.f + v * (1.f - s));
-}
 __device__ __forceinline__ void stg256(float* p, const float* v) {
   asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]),
                "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])

@@ -88,7 +88,20 @@ __device__ __forceinline__ float to_tf32(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return __uint_as_float(r);
 }
-__device__ __forceinline__ float silu_s(float v) { return v / (1.f + expf(-v)) * kSiluScale; }
+// Logistic function from the hardware exp2 and reciprocal approximations (each within ~2 units in the last place;
+// the exponent product adds |v| * 6e-8): relative error below 1e-6 where the function is not saturated, which is
+// inside the fp32 noise of the surrounding three-term TF32 products and a fraction of the cost of expf and a division.
+__device__ __forceinline__ float sigmoid_fast(float v) {
+  float t, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(v * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + t));
+  return r;
+}
+__device__ __forceinline__ float silu_s(float v) { return v * sigmoid_fast(v) * kSiluScale; }
+__device__ __forceinline__ float dsilu_s(float v) {
+  const float s = sigmoid_fast(v);
+  return kSiluScale * s * fmaf(v, 1.f - s, 1.f);
+}
 
 __device__ __forceinline__ void umma_tf32_ts(unsigned d_tmem, unsigned a_tmem, uint64_t b_desc, unsigned accumulate) {
   asm volatile(
