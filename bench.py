@@ -229,11 +229,14 @@ def main_md(args, rank, world, local):
     global MD_BRICK
     if args.md_brick:
         MD_BRICK = tuple(int(v) for v in args.md_brick.lower().split("x"))
-    dims = md_lattice_dims(world)
+    if args.scaling == "strong":          # one fixed system (default: the reference's 262,144-atom strong series)
+        dims = tuple(int(v) for v in args.strong_lattice.lower().split("x"))
+    else:
+        dims = md_lattice_dims(world)
     atoms_total = dims[0] * dims[1] * dims[2]
     workload = {"workload": f"md: NVE velocity-Verlet, C{CHANNELS}/lmax2/2 interactions/corr3 random-init, jittered "
                             f"H/C/O lattice {dims[0]}x{dims[1]}x{dims[2]} = {atoms_total} atoms "
-                            f"({MD_BRICK[0] * MD_BRICK[1] * MD_BRICK[2]} per GPU), cutoff {MD_CUTOFF} A, dt {MD_DT} fs, "
+                            f"({atoms_total // world} per GPU), cutoff {MD_CUTOFF} A, dt {MD_DT} fs, "
                             f"{MD_T} K, neighbours rebuilt every step",
                 "l2": "edge tensors (gates 12 GB per layer) are larger than L2", "atoms_per_gpu": atoms_total // world}
     if args.impl == "reference":
@@ -243,7 +246,8 @@ def main_md(args, rank, world, local):
         res = run_cpu_md(steps, warmup, args.cpu_md_side)
         line = {"impl": "reference", "metric": "MD atom-steps/s", "value": res["value"], "unit": "atom-steps/s",
                 "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": res["ms_per_step"],
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic",
                 "config": workload, "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
                 "e2e": {"value": res["value"], "unit": "atom-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -385,7 +389,7 @@ def main_md(args, rank, world, local):
         achieved = bwd_b / (adj_ms * 1e-3) / 1e9 if adj_ms else None
         line = {"metric": "MD atom-steps/s", "value": atoms_total / (ms * 1e-3), "unit": "atom-steps/s",
                 "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": dict(workload, edges_total=total_edges, edges_per_atom=total_edges / atoms_total,
                                step_replayed_as_cuda_graph=graph_cap is not None, edge_capacity=graph_cap,
                                kernels_ms_from="3 eager steps before the timed region"),
@@ -418,6 +422,9 @@ def main():
     ap.add_argument("--workload", default="md", choices=["md", "fused_message"])
     ap.add_argument("--cpu-md-side", type=int, default=12)
     ap.add_argument("--no-graph", action="store_true", help="do not record the single-GPU MD step as a CUDA graph")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="md workload: weak = 131,072 atoms per GPU (default), strong = one fixed system")
+    ap.add_argument("--strong-lattice", default="64x64x64", help="lattice sites of the strong-scaling system")
     ap.add_argument("--md-brick", default=None, help="lattice sites per GPU as XxYxZ (profiling of small cases)")
     ap.add_argument("--atoms", type=int, default=NUM_ATOMS)
     ap.add_argument("--cpu-sample-atoms", type=int, default=2048)
