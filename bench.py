@@ -412,6 +412,114 @@ def main_md(args, rank, world, local):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------ training step
+def main_train(args, rank, world, local):
+    """BASELINE configuration 4: energy-and-force training step (forces with create_graph, force loss whose
+    gradient needs the mixed second derivatives, AdamW) of the C64 model on a 32^3-site jittered lattice per GPU
+    (independent replicas: no collective)."""
+    side = args.train_side
+    n_atoms = side ** 3
+    workload = {"workload": f"train: energy+force loss step (mixed second derivatives, AdamW), C{CHANNELS}/lmax2/2 "
+                            f"interactions/corr3 random-init, jittered H/C/O lattice {side}^3 = {n_atoms} atoms per GPU, "
+                            f"cutoff {MD_CUTOFF} A, neighbour list built once (as in the reference's protocol)",
+                "l2": "edge tensors (gates 3 GB per layer) are larger than L2", "atoms_per_gpu": n_atoms}
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU port times the MD step only; use --workload md"}))
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from ictc_o3 import _lib
+    from mace_ictc import synthetic as S
+    from mace_ictc.hp import configure_model, create_model, energy_and_forces
+    from mace_ictc.md import neighbor_list
+    pos, box, species = S.jittered_lattice(side, side, side, MD_SPACING, MD_SIGMA, rank)
+    z = np.array([1, 6, 8])[species]
+    torch.manual_seed(0)
+    model = create_model(channels=CHANNELS, lmax=2, num_interactions=2, correlation=3, cutoff=MD_CUTOFF,
+                         atomic_numbers=(1, 6, 8), avg_num_neighbors=32.0, device=dev)
+    configure_model(model, policy="generated")
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4)
+    p = torch.as_tensor(pos, dtype=torch.float32, device=dev)
+    src, dst, shifts, _ = neighbor_list(p, n_atoms, [0, 0, 0], list(box), list(box), (1, 1, 1), MD_CUTOFF)
+    zt = torch.as_tensor(z, device=dev)
+    batch = torch.zeros(n_atoms, dtype=torch.long, device=dev)
+    cell = torch.as_tensor(np.diag(box), dtype=torch.float32, device=dev).unsqueeze(0)
+    target = torch.randn(n_atoms, 3, device=dev) * 0.05
+    host_pos = torch.empty(n_atoms, 3, pin_memory=True).copy_(p)
+    host_target = torch.empty(n_atoms, 3, pin_memory=True).copy_(target)
+    host_loss = torch.empty(1, pin_memory=True)
+
+    def step(from_host=False):
+        if from_host:
+            p.copy_(host_pos, non_blocking=True)
+            target.copy_(host_target, non_blocking=True)
+        opt.zero_grad(set_to_none=True)
+        res = energy_and_forces(model, p, zt, batch, src, dst, shifts, cell, training=True)
+        loss = (res["energy"] / n_atoms).square().mean() + (res["forces"] - target).square().mean()
+        loss.backward()
+        opt.step()
+        if from_host:
+            host_loss.copy_(loss.detach().reshape(1), non_blocking=True)
+            torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    calls0 = _lib.CALLS
+    step()
+    torch.cuda.synchronize()
+    calls_per_step = _lib.CALLS - calls0
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+        sampler.tick()
+    stop.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = start.elapsed_time(stop) / args.steps
+    e2e_steps = max(3, min(args.steps, 10))
+    barrier()
+    start.record()
+    for _ in range(e2e_steps):
+        step(True)
+    stop.record()
+    barrier()
+    e2e_ms = start.elapsed_time(stop) / e2e_steps
+    t = torch.tensor([ms, e2e_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    status = _lib.kernel_status()
+    if rank == 0:
+        total = n_atoms * world
+        print(json.dumps({
+            "metric": "training atom-steps/s", "value": total / (ms * 1e-3), "unit": "atom-steps/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict(workload, edges_per_gpu=int(src.numel()), parallelism="independent replicas"),
+            "gpu_launches": calls_per_step * args.steps, "kernel_status": status, "clocks": clocks,
+            "peak_memory_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
+            "e2e": {"value": total / (e2e_ms * 1e-3), "unit": "atom-steps/s", "h2d_bytes_per_step": 24 * n_atoms,
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms, "steps": e2e_steps}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------------------------ GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -419,7 +527,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="md", choices=["md", "fused_message"])
+    ap.add_argument("--workload", default="md", choices=["md", "fused_message", "train"])
+    ap.add_argument("--train-side", type=int, default=32, help="train workload: lattice sites per edge (atoms = side^3)")
     ap.add_argument("--cpu-md-side", type=int, default=12)
     ap.add_argument("--no-graph", action="store_true", help="do not record the single-GPU MD step as a CUDA graph")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
@@ -436,6 +545,8 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload == "md":
         return main_md(args, rank, world, local)
+    if args.workload == "train":
+        return main_train(args, rank, world, local)
     workload = {"workload": f"fused_message: TP+scatter forward+adjoint, fp32, C{CHANNELS}, lmax {LMAX}, "
                             f"{args.atoms} atoms/GPU uniform density {DENSITY}, cutoff {CUTOFF}",
                 "l2": "inputs larger than L2 (gates alone are 7 GB)", "atoms_per_gpu": args.atoms}

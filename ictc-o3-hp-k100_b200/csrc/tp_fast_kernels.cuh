@@ -274,13 +274,25 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_fast_kernel(TpArgs
     if (NEEDH) {
       V dshv[S::NH];
       F::dharm(x, v, ge, dshv);
-      float mine = 0.f;
+      if constexpr (S::NP <= 4) {
+        // few paths: the reduction is a large share of the per-edge work, use the 12-shuffle recursive halving
+        float part[S::NH];
 #pragma unroll
-      for (int j = 0; j < S::NH; ++j) {
-        const float tot = warp_sum(dshv[j].hsum());
-        if (lane == j) mine = tot;
+        for (int j = 0; j < S::NH; ++j) part[j] = dshv[j].hsum();
+        int which;
+        bool holder;
+        const float tot = warp_reduce_scatter<S::NH>(part, lane, which, holder);
+        if (holder) a.dsh[e * S::NH + which] = tot;
+      } else {
+        // many paths: the kernel is at its register limit, the plain butterfly keeps fewer values live
+        float mine_sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < S::NH; ++j) {
+          const float tot = warp_sum(dshv[j].hsum());
+          if (lane == j) mine_sum = tot;
+        }
+        if (lane < S::NH) a.dsh[e * S::NH + lane] = mine_sum;
       }
-      if (lane < S::NH) a.dsh[e * S::NH + lane] = mine;
     }
   }
   if (NEEDX) {
