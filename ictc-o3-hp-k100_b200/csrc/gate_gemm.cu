@@ -41,6 +41,7 @@ struct Args {
   const int64_t* pair_a;  // backward, optional
   const int64_t* pair_b;
   int64_t rows;
+  const int64_t* limit;   // optional device scalar: only min(rows, *limit) rows are processed (recorded graphs)
   int nout;
   int act;                // forward: apply the scaled SiLU to the input
   int* status;
@@ -85,7 +86,8 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
   Barriers* bar = reinterpret_cast<Barriers*>(stage + 2 * kRows * kStagePitch);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = a.nout / kChunk;
-  const int64_t tiles = (a.rows + kRows - 1) / kRows;
+  const int64_t nrows = a.limit ? (ldg(a.limit) < a.rows ? ldg(a.limit) : a.rows) : a.rows;
+  const int64_t tiles = (nrows + kRows - 1) / kRows;
   const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (threadIdx.x == 0) {
@@ -207,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
         for (int i = 0; i < 16; ++i) {
           const int r = 2 * i + (lane >> 4);
           const float4 v = *reinterpret_cast<const float4*>(warp_rows + r * kStagePitch + (lane & 15) * 16);
-          if (row0 + r < a.rows) __stcs(reinterpret_cast<float4*>(base + off), v);
+          if (row0 + r < nrows) __stcs(reinterpret_cast<float4*>(base + off), v);
           if (mm == 1) {
             off += 2 * a.out_ld;
           } else {
@@ -227,7 +229,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
       const int ab = int(t & 1);
       const int64_t g = (blockIdx.x + t * gridDim.x) * kRows + row;
       float x[32];
-      if (g < a.rows) {
+      if (g < nrows) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) ldg256(a.in + row_offset(g, a.in_mm, a.in_ld) + half * 32 + j * 8, x + j * 8);
       } else {
@@ -267,7 +269,8 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
   Barriers* bar = reinterpret_cast<Barriers*>(w_buf + kWStages * kWStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = a.nout / kChunk;
-  const int64_t tiles = (a.rows + kRows - 1) / kRows;
+  const int64_t nrows = a.limit ? (ldg(a.limit) < a.rows ? ldg(a.limit) : a.rows) : a.rows;
+  const int64_t tiles = (nrows + kRows - 1) / kRows;
   const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (threadIdx.x == 0) {
@@ -350,7 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
       tmem_ld32(taddr + 32, v1);
       tc_fence_before();
       mbar_arrive(saddr(&bar->d_empty[d]));
-      if (grow < a.rows) {
+      if (grow < nrows) {
         float4* o = reinterpret_cast<float4*>(a.out + row_offset(grow, a.out_mm, a.out_ld));
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -366,8 +369,8 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
     int64_t it = 0;
     for (int64_t t = 0; t < my_tiles; ++t) {
       const int64_t g = (blockIdx.x + t * gridDim.x) * kRows + row;
-      const int64_t ra = g < a.rows ? (a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g) : -1;
-      const int64_t rb = (g < a.rows && a.pair_b) ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
+      const int64_t ra = g < nrows ? (a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g) : -1;
+      const int64_t rb = (g < nrows && a.pair_b) ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
       const float* pa = a.in + row_offset(ra >= 0 ? ra : 0, a.in_mm, a.in_ld) + half * 32;
       const float* pb = a.in + row_offset(rb >= 0 ? rb : 0, a.in_mm, a.in_ld) + half * 32;
       const int64_t cstep = int64_t(a.in_cs) * kChunk;
@@ -457,7 +460,7 @@ int ictc_gate_pack_weights(int num_out, const float* w3, int transpose, float* p
 }
 
 int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const float* w_packed, float* gates,
-                           int apply_silu, void* stream) {
+                           int apply_silu, const int64_t* row_limit, void* stream) {
   if (int rc = gg::check_common(num_rows, num_out)) return rc;
   if (num_rows == 0) return ICTC_OK;
   if (!z3 || !w_packed || !gates) { set_error("gate gemm forward: NULL buffer"); return ICTC_ERR_BAD_ARG; }
@@ -469,7 +472,7 @@ int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kFwdSmem);
   if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   gg::Args a{};
-  a.in = z3; a.w = w_packed; a.out = gates; a.rows = num_rows; a.nout = num_out; a.act = apply_silu ? 1 : 0;
+  a.in = z3; a.w = w_packed; a.out = gates; a.rows = num_rows; a.limit = row_limit; a.nout = num_out; a.act = apply_silu ? 1 : 0;
   a.in_mm = a.out_mm = a.in_cs = a.out_cs = 1; a.in_ld = gg::kK; a.out_ld = num_out;
   a.status = kernel_status_word();
   gg::gate_gemm_forward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kFwdSmem, (cudaStream_t)stream>>>(a);
@@ -477,7 +480,8 @@ int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const
 }
 
 int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, const int64_t* pair_a,
-                            const int64_t* pair_b, const float* w_packed_t, float* da3, void* stream) {
+                            const int64_t* pair_b, const float* w_packed_t, float* da3, const int64_t* row_limit,
+                            void* stream) {
   if (int rc = gg::check_common(num_rows, num_out)) return rc;
   if (num_rows == 0) return ICTC_OK;
   if (!dgates || !w_packed_t || !da3) { set_error("gate gemm backward: NULL buffer"); return ICTC_ERR_BAD_ARG; }
@@ -489,7 +493,7 @@ int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, 
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kBwdSmem);
   if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   gg::Args a{};
-  a.in = dgates; a.w = w_packed_t; a.out = da3; a.pair_a = pair_a; a.pair_b = pair_b; a.rows = num_rows; a.nout = num_out;
+  a.in = dgates; a.w = w_packed_t; a.out = da3; a.pair_a = pair_a; a.pair_b = pair_b; a.rows = num_rows; a.limit = row_limit; a.nout = num_out;
   a.in_mm = a.out_mm = a.in_cs = a.out_cs = 1; a.in_ld = num_out; a.out_ld = gg::kK;
   a.status = kernel_status_word();
   gg::gate_gemm_backward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kBwdSmem, (cudaStream_t)stream>>>(a);

@@ -41,6 +41,7 @@ struct Args {
   float* drb;          // backward output [E, nb]
   const int64_t* rows; // optional row index: forward reads rb[rows[r]], backward writes / adds to drb[rows[r]]
   int accumulate;      // backward: drb[...] += instead of =
+  const int64_t* limit; // optional device scalar: only min(E, *limit) rows are processed (recorded graphs)
   int64_t E;
   int nb;
   int* status;
@@ -134,7 +135,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_forward_kernel(Args a) 
   float* w0s = reinterpret_cast<float*>(chain_smem + 2 * kWStageBytes);
   Barriers* bar = reinterpret_cast<Barriers*>(chain_smem + kBarOffset);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t tiles = (a.E + kRows - 1) / kRows;
+  const int64_t nrows = a.limit ? (ldg(a.limit) < a.E ? ldg(a.limit) : a.E) : a.E;
+  const int64_t tiles = (nrows + kRows - 1) / kRows;
   const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   const unsigned tmem = setup(a, chain_smem, bar, w0s);
 
@@ -148,7 +150,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_forward_kernel(Args a) 
     unsigned phase = 0;
     for (int64_t i = s; i < my_tiles; i += 2) {
       const int64_t g = (blockIdx.x + i * gridDim.x) * kRows + row;
-      const bool valid = g < a.E;
+      const bool valid = g < nrows;
       // ---- layer 0 in fp32: z1[n] = sum_k rb[k] W0[n][k] for this thread's 32 units
       float rb[8];
 #pragma unroll
@@ -206,7 +208,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_backward_kernel(Args a)
   float* xchg = w0s + 64 * 8;                                         // [128][8] partial drb of the upper half
   Barriers* bar = reinterpret_cast<Barriers*>(chain_smem + kBarOffset);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t tiles = (a.E + kRows - 1) / kRows;
+  const int64_t nrows = a.limit ? (ldg(a.limit) < a.E ? ldg(a.limit) : a.E) : a.E;
+  const int64_t tiles = (nrows + kRows - 1) / kRows;
   const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   const unsigned tmem = setup(a, chain_smem, bar, w0s);
 
@@ -223,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_backward_kernel(Args a)
     unsigned phase = 0, xphase = 0;
     for (int64_t i = s; i < my_tiles; i += 2) {
       const int64_t g = (blockIdx.x + i * gridDim.x) * kRows + row;
-      const bool valid = g < a.E;
+      const bool valid = g < nrows;
       float x[32], z[32];
       bool ok = true;
 #pragma unroll 1
@@ -317,7 +320,7 @@ extern "C" {
 
 int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, const int64_t* rb_rows, const float* w0,
                            const float* w1_packed, const float* w2_packed, float* z1, float* z2, float* z3,
-                           void* stream) {
+                           const int64_t* row_limit, void* stream) {
   if (num_edges < 0 || num_basis < 1 || num_basis > 8) {
     set_error("mlp chain: needs 1..8 basis functions (got %d)", num_basis);
     return ICTC_ERR_BAD_SPEC;
@@ -333,7 +336,7 @@ int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, co
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, chain::kSmem);
   if (attr != cudaSuccess) { set_error("mlp chain smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   chain::Args a{};
-  a.in = rb; a.rows = rb_rows; a.w0 = w0; a.wa = w1_packed; a.wb = w2_packed; a.z1 = z1; a.z2 = z2; a.z3 = z3; a.E = num_edges; a.nb = num_basis;
+  a.in = rb; a.rows = rb_rows; a.limit = row_limit; a.w0 = w0; a.wa = w1_packed; a.wb = w2_packed; a.z1 = z1; a.z2 = z2; a.z3 = z3; a.E = num_edges; a.nb = num_basis;
   a.status = kernel_status_word();
   chain::mlp_chain_forward_kernel<<<chain::grid_size(num_edges), chain::kThreads, chain::kSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("mlp_chain_forward");
@@ -341,7 +344,7 @@ int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, co
 
 int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0, const float* w1t_packed,
                             const float* w2t_packed, const float* z1, const float* z2, const float* z3, float* drb,
-                            const int64_t* drb_rows, int accumulate, void* stream) {
+                            const int64_t* drb_rows, int accumulate, const int64_t* row_limit, void* stream) {
   if (num_edges < 0 || num_basis < 1 || num_basis > 8) {
     set_error("mlp chain: needs 1..8 basis functions (got %d)", num_basis);
     return ICTC_ERR_BAD_SPEC;
@@ -358,7 +361,7 @@ int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, 
   if (attr != cudaSuccess) { set_error("mlp chain smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   chain::Args a{};
   a.in = da3; a.w0 = w0; a.wa = w2t_packed; a.wb = w1t_packed; a.z1 = const_cast<float*>(z1); a.z2 = const_cast<float*>(z2);
-  a.z3 = const_cast<float*>(z3); a.drb = drb; a.rows = drb_rows; a.accumulate = accumulate ? 1 : 0; a.E = num_edges; a.nb = num_basis;
+  a.z3 = const_cast<float*>(z3); a.drb = drb; a.rows = drb_rows; a.limit = row_limit; a.accumulate = accumulate ? 1 : 0; a.E = num_edges; a.nb = num_basis;
   a.status = kernel_status_word();
   chain::mlp_chain_backward_kernel<<<chain::grid_size(num_edges), chain::kThreads, chain::kSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("mlp_chain_backward");

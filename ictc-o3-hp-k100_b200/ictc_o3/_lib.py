@@ -33,10 +33,10 @@ SIGNATURES = {
     "ictc_radial_mlp_hidden_forward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_radial_mlp_hidden_backward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_gate_pack_weights": (_I, [_I, _P, _I, _P, _P]),
-    "ictc_gate_gemm_forward": (_I, [_L, _I, _P, _P, _P, _I, _P]),
-    "ictc_gate_gemm_backward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P]),
-    "ictc_mlp_chain_forward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "ictc_mlp_chain_backward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P]),
+    "ictc_gate_gemm_forward": (_I, [_L, _I, _P, _P, _P, _I, _P, _P]),
+    "ictc_gate_gemm_backward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "ictc_mlp_chain_forward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "ictc_mlp_chain_backward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P]),
     "ictc_channel_linear_tc": (_I, [_L, _I, _I, _P, _I, _L, _P, _P, _I, _L, _P]),
     "ictc_csr_scratch_bytes": (_L, [_L, _L]),
     "ictc_csr_build": (_I, [_P, _L, _L, _P, _P, _P, _P, _P]),

@@ -178,9 +178,10 @@ class ForceEngine:
     def _chain_ok(self, L):
         return self._fused_mlp_ok(L) and "w3_umma" in L and self.mlp_chain
 
-    def _mlp(self, rb, L, rows=None):
+    def _mlp(self, rb, L, rows=None, limit=None):
         """Radial MLP: returns gates and the pre-activations needed by the reverse sweep.  ``rows`` (tensor-memory
-        chain kernels only) makes row r of the MLP read rb[rows[r]]."""
+        chain kernels only) makes row r of the MLP read rb[rows[r]]; ``limit`` is a device scalar with the number
+        of rows that are really in use (fixed-capacity buffers of a recorded step)."""
         if self._fused_mlp_ok(L):
             e, fc = (rb.shape[0] if rows is None else rows.numel()), L["fc"]
             nout = fc[3].shape[0]
@@ -193,7 +194,7 @@ class ForceEngine:
                                                                fc[0].data_ptr(),
                                                                L["hid_umma"][0].data_ptr(), L["hid_umma"][1].data_ptr(),
                                                                _lib.ptr(pre[0]), _lib.ptr(pre[1]), _lib.ptr(pre[2]),
-                                                               self._st()), "mlp_chain_forward")
+                                                               _lib.ptr(limit), self._st()), "mlp_chain_forward")
                 else:
                     _lib.check(self.lib.ictc_radial_mlp_hidden_forward(e, rb.shape[1], _lib.ptr(rb), fc[0].data_ptr(),
                                                                        fc[1].data_ptr(), fc[2].data_ptr(),
@@ -203,7 +204,8 @@ class ForceEngine:
                 self._done(f"radial_mlp_hidden_forward_{nout}", t0)
                 t0 = self._mark()
                 _lib.check(self.lib.ictc_gate_gemm_forward(e, nout, _lib.ptr(pre[2]), L["w3_umma"].data_ptr(),
-                                                           _lib.ptr(gates), 1, self._st()), "gate_gemm_forward")
+                                                           _lib.ptr(gates), 1, _lib.ptr(limit), self._st()),
+                           "gate_gemm_forward")
                 self._done(f"gate_gemm_forward_{nout}", t0)
                 return gates, pre
             _lib.check(self.lib.ictc_radial_mlp_forward(e, rb.shape[1], nout, _lib.ptr(rb), fc[0].data_ptr(),
@@ -221,7 +223,7 @@ class ForceEngine:
             else:
                 return z, pre
 
-    def _mlp_bwd(self, dgates, pre, L, pairs=None, out=None, accumulate=False):
+    def _mlp_bwd(self, dgates, pre, L, pairs=None, out=None, accumulate=False, limit=None):
         """Input gradient of the radial MLP.  With ``out`` [E, num_basis] (chain kernels, paired rows) the result of
         pair u is written or added to out[rep_edge[u]] and ``out`` is returned."""
         if pairs is not None and not self._fused_mlp_ok(L):
@@ -239,7 +241,7 @@ class ForceEngine:
                 da3 = self._rows(e, 64)
                 _lib.check(self.lib.ictc_gate_gemm_backward(e, dgates.shape[1], _lib.ptr(dgates), _lib.ptr(pa),
                                                             _lib.ptr(pb), L["w3t_umma"].data_ptr(), _lib.ptr(da3),
-                                                            self._st()), "gate_gemm_backward")
+                                                            _lib.ptr(limit), self._st()), "gate_gemm_backward")
                 self._done(f"gate_gemm_backward_{dgates.shape[1]}", t0)
                 t0 = self._mark()
                 if self.mlp_chain:
@@ -248,7 +250,8 @@ class ForceEngine:
                                                                 L["hid_t_umma"][1].data_ptr(), _lib.ptr(pre[0]),
                                                                 _lib.ptr(pre[1]), _lib.ptr(pre[2]), _lib.ptr(drb),
                                                                 _lib.ptr(pa) if out is not None else None,
-                                                                int(accumulate), self._st()), "mlp_chain_backward")
+                                                                int(accumulate), _lib.ptr(limit), self._st()),
+                               "mlp_chain_backward")
                 else:
                     _lib.check(self.lib.ictc_radial_mlp_hidden_backward(e, nb, _lib.ptr(da3), ft[0].data_ptr(),
                                                                         ft[1].data_ptr(), ft[2].data_ptr(),
@@ -325,7 +328,8 @@ class ForceEngine:
         receivers < n_owned, dst_rowptr [n_owned+1].  Returns (energy of owned atoms, dE/dpos [N_local,3],
         per-atom energies [n_owned]).  ``n_rows`` < N_local marks trailing rows of ``pos`` as padding: they may
         be named by inert edges (whose sender index is then outside the sender CSR) but carry no features.
-        ``pairs`` = (gate_row [E], rep_edge [U], other_edge [U]) evaluates the radial MLP once per edge pair."""
+        ``pairs`` = (gate_row [E], rep_edge [U], other_edge [U]) evaluates the radial MLP once per edge pair; an
+        optional fourth element is a device int64 scalar with the number of pair rows in use when U is a capacity."""
         self.refresh()
         m, c, lib, dev = self.model, self.c, self.lib, self.dev
         n_local, e = (pos.shape[0] if n_rows is None else int(n_rows)), int(src.numel())
@@ -347,6 +351,7 @@ class ForceEngine:
             grow = None if pairs is None else pairs[0]
             by_rows = pairs is not None and self._chain_ok(L0) and self._chain_ok(L1)
             rb_rows = pairs[1] if by_rows else None          # the MLP kernels gather / scatter the pair rows
+            live = pairs[3] if (by_rows and len(pairs) > 3) else None   # device count of pair rows in use
             rb_u = rb if (pairs is None or by_rows) else rb.index_select(0, pairs[1])
             sp_owned = species[:n_owned]
             s_count = self.emb.shape[0]
@@ -358,7 +363,7 @@ class ForceEngine:
                 self._lin(L0, ("up", 0), n_local, x0, 0, 1, c, u0, 0, 1, c)
             else:
                 u0 = torch.mm(x0, L0["up_t"][0])
-            g0, pre0 = self._mlp(rb_u, L0, rb_rows)
+            g0, pre0 = self._mlp(rb_u, L0, rb_rows, live)
             M0 = self._tp_forward(0, u0, sh, g0, src, dst_rowptr, n_owned, e, L0["tpw"], grow)   # [n, 9C]
             m0 = self._rows(n_owned, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
@@ -389,7 +394,7 @@ class ForceEngine:
                     continue
                 u1[:, off * c:(off + mm) * c] = torch.mm(h1_full[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L1["up_t"][l]).view(n_local, mm * c)
-            g1, pre1 = self._mlp(rb_u, L1, rb_rows)
+            g1, pre1 = self._mlp(rb_u, L1, rb_rows, live)
             M1 = self._tp_forward(1, u1, sh, g1, src, dst_rowptr, n_owned, e, L1["tpw"], grow)   # [n, 35C]
             m1 = self._rows(n_owned, 9 * c)
             in_off = 0
@@ -430,7 +435,7 @@ class ForceEngine:
                 out_off += cnt * mm * c
             du1, dsh1, dg1 = self._tp_adjoint(1, u1, sh, g1, dst, src_csr, v1, n_local, e, L1["tpw"], True, grow)
             drb = self._rows(e, nb, zero=True) if by_rows else None
-            drb = self._mlp_bwd(dg1, pre1, L1, pairs, drb, False)
+            drb = self._mlp_bwd(dg1, pre1, L1, pairs, drb, False, live)
             del dg1, g1, pre1
             dh1_full = self._rows(n_local, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
@@ -465,7 +470,7 @@ class ForceEngine:
                                                          L0["ml"][l]).view(n_owned, mm * c)
             _, dsh0, dg0 = self._tp_adjoint(0, u0, sh, g0, dst, src_csr, v0, n_local, e, L0["tpw"], False, grow)
             if by_rows:
-                self._mlp_bwd(dg0, pre0, L0, pairs, drb, True)
+                self._mlp_bwd(dg0, pre0, L0, pairs, drb, True, live)
             else:
                 drb += self._mlp_bwd(dg0, pre0, L0, pairs)
                 if pairs is not None:      # the pair's length gradient is carried by its representative edge

@@ -150,7 +150,7 @@ class StaticNeighborList:
                                            self.pscratch.data_ptr(), st), "ictc_neighbor_pairs")
 
     def pairs(self):
-        return self.gate_row, self.rep, self.other
+        return self.gate_row, self.rep, self.other, self.num_unique
 
 
 def maxwell_boltzmann(masses: np.ndarray, temperature: float, seed: int) -> np.ndarray:

@@ -265,12 +265,15 @@ int ictc_radial_mlp_hidden_backward(int64_t num_edges, int num_basis, const floa
  * ictc_gate_gemm_forward: gates[r, :] = act(z3[r, :]) @ W3^T, act = scaled SiLU when apply_silu != 0.
  * ictc_gate_gemm_backward: da3[r, :] = (dgates[pair_a[r], :] + dgates[pair_b[r], :]) @ W3; pair_a == NULL means
  *   row r itself, pair_b == NULL or pair_b[r] < 0 means no second row.
+ * row_limit (may be NULL): DEVICE scalar; only min(num_rows, *row_limit) rows are processed, so a recorded step whose
+ *   buffers have a fixed capacity does no work for the unused tail.
  * All buffers 32-byte aligned.  Bounded waits report through ictc_kernel_status (codes 21-25, 31-35). */
 int ictc_gate_pack_weights(int num_out, const float* w3, int transpose, float* packed, void* stream);
 int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const float* w_packed, float* gates,
-                           int apply_silu, void* stream);
+                           int apply_silu, const int64_t* row_limit, void* stream);
 int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, const int64_t* pair_a,
-                            const int64_t* pair_b, const float* w_packed_t, float* da3, void* stream);
+                            const int64_t* pair_b, const float* w_packed_t, float* da3, const int64_t* row_limit,
+                            void* stream);
 
 /* Per-degree channel linear map on the same tcgen05 kernels (reference: ictc_o3/operators.py:609-628
  * channel_linear; mace_ictc/models/mace/layers.py:21-87 linear_up / message_linear; products.py:817): rows are
@@ -294,13 +297,14 @@ int ictc_channel_linear_tc(int64_t num_rows, int k_chunks, int n_chunks, const f
  * backward: da3 [E, 64] (gradient of silu(z3)) and z1..z3 -> drb; row r is written (accumulate == 0) or added
  *   (accumulate != 0) to drb[drb_rows[r]] (drb_rows NULL: drb[r]); a row index that repeats (the inert padding
  *   rows of a fixed-capacity pair table) receives an unspecified one of its results.
+ * row_limit: as for ictc_gate_gemm_forward.
  * z*, da3 and the packed weights 32-byte aligned.  Bounded waits report codes 41-46. */
 int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, const int64_t* rb_rows, const float* w0,
                            const float* w1_packed, const float* w2_packed, float* z1, float* z2, float* z3,
-                           void* stream);
+                           const int64_t* row_limit, void* stream);
 int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0, const float* w1t_packed,
                             const float* w2t_packed, const float* z1, const float* z2, const float* z3, float* drb,
-                            const int64_t* drb_rows, int accumulate, void* stream);
+                            const int64_t* drb_rows, int accumulate, const int64_t* row_limit, void* stream);
 
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).

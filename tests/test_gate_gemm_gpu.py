@@ -31,7 +31,7 @@ def test_gate_gemm_forward(rows, nout, act):
     gates = torch.full((rows, nout), float("nan"), device="cuda")
     st = torch.cuda.current_stream().cuda_stream
     _lib.check(lib.ictc_gate_gemm_forward(rows, nout, z3.data_ptr(), _pack(lib, w3, 0).data_ptr(), gates.data_ptr(),
-                                          act, st), "fwd")
+                                          act, None, st), "fwd")
     assert _status(lib) == 0
     sample = torch.arange(0, rows, max(1, rows // 4000))
     h = z3[sample].double().cpu()
@@ -61,7 +61,7 @@ def test_gate_gemm_backward(rows, nout, paired):
         pa_p = pb_p = None
     st = torch.cuda.current_stream().cuda_stream
     _lib.check(lib.ictc_gate_gemm_backward(rows, nout, dg.data_ptr(), pa_p, pb_p, _pack(lib, w3, 1).data_ptr(),
-                                           da3.data_ptr(), st), "bwd")
+                                           da3.data_ptr(), None, st), "bwd")
     assert _status(lib) == 0
     sample = torch.arange(0, rows, max(1, rows // 4000))
     if paired:
@@ -103,7 +103,7 @@ def test_hidden_layers_plus_gate_gemm_equal_the_single_kernel_mlp():
     _lib.check(lib.ictc_radial_mlp_hidden_forward(edges, nb, rb.data_ptr(), *[w.data_ptr() for w in ws[:3]],
                                                   *[z.data_ptr() for z in zb], st), "hidden fwd")
     _lib.check(lib.ictc_gate_gemm_forward(edges, nout, zb[2].data_ptr(), _pack(lib, ws[3], 0).data_ptr(),
-                                          gates_b.data_ptr(), 1, st), "gate fwd")
+                                          gates_b.data_ptr(), 1, None, st), "gate fwd")
     for x, y in zip(za, zb):
         assert torch.equal(x, y)
     assert float((gates_a - gates_b).abs().max()) < 3e-6 * float(gates_a.abs().max())
@@ -115,12 +115,12 @@ def test_hidden_layers_plus_gate_gemm_equal_the_single_kernel_mlp():
     da3 = torch.empty(edges, 64, device="cuda")
     drb_b = torch.empty(edges, nb, device="cuda")
     _lib.check(lib.ictc_gate_gemm_backward(edges, nout, dg.data_ptr(), None, None, _pack(lib, ws[3], 1).data_ptr(),
-                                           da3.data_ptr(), st), "gate bwd")
+                                           da3.data_ptr(), None, st), "gate bwd")
     _lib.check(lib.ictc_radial_mlp_hidden_backward(edges, nb, da3.data_ptr(), *[w.data_ptr() for w in wt[:3]],
                                                    *[z.data_ptr() for z in zb], drb_b.data_ptr(), st), "hidden bwd")
     assert _status(lib) == 0
     assert float((drb_a - drb_b).abs().max()) < 5e-6 * float(drb_a.abs().max())
-    assert lib.ictc_gate_gemm_forward(10, 100, *([None] * 3), 1, None) == -1
+    assert lib.ictc_gate_gemm_forward(10, 100, *([None] * 3), 1, None, None) == -1
 
 
 @pytest.mark.parametrize("nodes,mm,cnt", [(777, 3, 4), (1000, 5, 4), (300, 1, 3), (513, 3, 1)])
@@ -173,7 +173,7 @@ def test_mlp_chain_hidden_layers(edges, nb):
     zs = [torch.full((edges, 64), float("nan"), device="cuda") for _ in range(3)]
     packed = [_pack(lib, ws[1], 0), _pack(lib, ws[2], 0), _pack(lib, ws[1], 1), _pack(lib, ws[2], 1)]
     _lib.check(lib.ictc_mlp_chain_forward(edges, nb, rb.data_ptr(), None, ws[0].data_ptr(), packed[0].data_ptr(),
-                                          packed[1].data_ptr(), *[z.data_ptr() for z in zs], st), "chain fwd")
+                                          packed[1].data_ptr(), *[z.data_ptr() for z in zs], None, st), "chain fwd")
     assert _status(lib) == 0
     x = rb.double().cpu().requires_grad_(True)
     h, ref = x, []
@@ -190,7 +190,7 @@ def test_mlp_chain_hidden_layers(edges, nb):
     da3d = da3.cuda()
     _lib.check(lib.ictc_mlp_chain_backward(edges, nb, da3d.data_ptr(), ws[0].data_ptr(), packed[2].data_ptr(),
                                            packed[3].data_ptr(), *[z.data_ptr() for z in zs], drb.data_ptr(),
-                                           None, 0, st), "chain bwd")
+                                           None, 0, None, st), "chain bwd")
     assert _status(lib) == 0
     assert torch.isfinite(drb).all()
     err = float((drb.double().cpu() - ref_d).abs().max() / ref_d.abs().max())
@@ -212,9 +212,9 @@ def test_mlp_chain_row_indices_gather_and_scatter():
     zb = [torch.empty(edges, 64, device="cuda") for _ in range(3)]
     sub = rb[rows].contiguous()
     _lib.check(lib.ictc_mlp_chain_forward(edges, nb, sub.data_ptr(), None, ws[0].data_ptr(), packed[0].data_ptr(),
-                                          packed[1].data_ptr(), *[z.data_ptr() for z in za], st), "fwd")
+                                          packed[1].data_ptr(), *[z.data_ptr() for z in za], None, st), "fwd")
     _lib.check(lib.ictc_mlp_chain_forward(edges, nb, rb.data_ptr(), rows.data_ptr(), ws[0].data_ptr(),
-                                          packed[0].data_ptr(), packed[1].data_ptr(), *[z.data_ptr() for z in zb], st),
+                                          packed[0].data_ptr(), packed[1].data_ptr(), *[z.data_ptr() for z in zb], None, st),
                "fwd rows")
     for x, y in zip(za, zb):
         assert torch.equal(x, y)
@@ -222,12 +222,40 @@ def test_mlp_chain_row_indices_gather_and_scatter():
     dense = torch.empty(edges, nb, device="cuda")
     _lib.check(lib.ictc_mlp_chain_backward(edges, nb, da3.data_ptr(), ws[0].data_ptr(), packed[2].data_ptr(),
                                            packed[3].data_ptr(), *[z.data_ptr() for z in za], dense.data_ptr(), None, 0,
-                                           st), "bwd")
+                                           None, st), "bwd")
     out = torch.ones(total, nb, device="cuda")
     _lib.check(lib.ictc_mlp_chain_backward(edges, nb, da3.data_ptr(), ws[0].data_ptr(), packed[2].data_ptr(),
                                            packed[3].data_ptr(), *[z.data_ptr() for z in za], out.data_ptr(),
-                                           rows.data_ptr(), 1, st), "bwd rows")
+                                           rows.data_ptr(), 1, None, st), "bwd rows")
     assert _status(lib) == 0
     expect = torch.ones(total, nb, device="cuda")
     expect[rows] += dense
     assert torch.equal(out, expect)
+
+
+def test_row_limit_on_the_device_bounds_the_work():
+    """A device-side row count smaller than the host row count leaves the tail of the outputs untouched."""
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    torch.manual_seed(9)
+    rows, live, nout = 1000, 333, 192
+    z3 = torch.randn(rows, 64).cuda()
+    w3 = (torch.randn(nout, 64) / 8).cuda().contiguous()
+    limit = torch.tensor([live], dtype=torch.int64, device="cuda")
+    gates = torch.full((rows, nout), float("nan"), device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    packed = _pack(lib, w3, 0)
+    _lib.check(lib.ictc_gate_gemm_forward(rows, nout, z3.data_ptr(), packed.data_ptr(), gates.data_ptr(), 0,
+                                          limit.data_ptr(), st), "fwd")
+    ref = z3[:live].double().cpu() @ w3.double().cpu().t()
+    assert float((gates[:live].double().cpu() - ref).abs().max() / ref.abs().max()) < 2e-6
+    assert bool(torch.isnan(gates[live:]).all())
+    da3 = torch.full((rows, 64), float("nan"), device="cuda")
+    dg = torch.randn(rows, nout).cuda()
+    packed_t = _pack(lib, w3, 1)
+    _lib.check(lib.ictc_gate_gemm_backward(rows, nout, dg.data_ptr(), None, None, packed_t.data_ptr(), da3.data_ptr(),
+                                           limit.data_ptr(), st), "bwd")
+    ref = dg[:live].double().cpu() @ w3.double().cpu()
+    assert float((da3[:live].double().cpu() - ref).abs().max() / ref.abs().max()) < 1e-5
+    assert bool(torch.isnan(da3[live:]).all())
+    assert _status(lib) == 0
