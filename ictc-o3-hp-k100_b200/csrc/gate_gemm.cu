@@ -67,6 +67,7 @@ struct Barriers {
   unsigned long long w_full[kWStages], w_empty[kWStages], a_full[4], a_empty[4], d_full[4], d_empty[4];
   unsigned tmem_base;
   int failed;
+  volatile long long progress;   // backward: chunks finished by the first producer warp (read by the prefetch warps)
 };
 
 __device__ __forceinline__ void give_up(Barriers* b, int* status, int code) {
@@ -287,6 +288,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
       mbar_init(saddr(&bar->d_empty[i]), 128);
     }
     bar->failed = 0;
+    bar->progress = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -362,7 +364,57 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
         }
       }
     }
-  } else if (warp >= kProducerWarp0) {
+  } else if (warp < kProducerWarp0) {
+    // ---- warps 6-9: L2 prefetch of the rows a few chunks ahead of the producers, across tile boundaries
+    // (thread = row).  They follow the producers through a progress counter and never wait when they are behind.
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    constexpr int kAhead = 2;
+    const int64_t cstep = int64_t(a.in_cs) * kChunk;
+    int64_t pf_tile = 0;
+    int pf_chunk = 0;
+    const float* pa = nullptr;
+    const float* pb = nullptr;
+    auto enter_tile = [&]() {
+      pa = pb = nullptr;
+      if (pf_tile >= my_tiles) return;
+      const int64_t g = (blockIdx.x + pf_tile * gridDim.x) * kRows + row;
+      if (g >= nrows) return;
+      const int64_t ra = a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g;
+      const int64_t rb = a.pair_b ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
+      pa = a.in + row_offset(ra, a.in_mm, a.in_ld);
+      if (rb >= 0) pb = a.in + row_offset(rb, a.in_mm, a.in_ld);
+    };
+    auto advance = [&]() {
+      if (pf_tile >= my_tiles) return;
+      if (pa) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pa + pf_chunk * cstep));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pa + pf_chunk * cstep + 32));
+      }
+      if (pb) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pb + pf_chunk * cstep));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pb + pf_chunk * cstep + 32));
+      }
+      if (++pf_chunk == chunks) {
+        pf_chunk = 0;
+        ++pf_tile;
+        enter_tile();
+      }
+    };
+    enter_tile();
+    for (int k = 0; k < kAhead; ++k) advance();
+    const int64_t total = my_tiles * chunks;
+    for (int64_t it = 0; it < total; ++it) {
+      advance();
+      const long long start = clock64();
+      bool ok = true;
+      while (bar->progress <= it && !bar->failed) {
+        if (clock64() - start > kWaitCycles) { ok = false; break; }
+        __nanosleep(64);
+      }
+      if (!ok || bar->failed) break;
+    }
+  } else {
     // ---- A producers: thread = (row, half of a 64-column chunk); (dG[a] + dG[b]) -> split -> TMEM ring
     const int q = warp & 3, half = (warp - kProducerWarp0) >> 2;
     const int row = q * 32 + lane;
@@ -402,6 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
         store_split_tmem(t_big, t_big + kK, x);
         tc_fence_before();
         mbar_arrive(saddr(&bar->a_full[sa]));
+        if (warp == kProducerWarp0 && lane == 0) bar->progress = it + 1;
       }
       if (!ok) break;
     }
