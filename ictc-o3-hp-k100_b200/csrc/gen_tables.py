@@ -127,6 +127,37 @@ def emit_tp(lines):
             seen.add(j)
         lines.append(f"#define ICTC_TP_{n}_BYJT(F,A) \\\n  " + " \\\n  ".join(
             " ".join(ent[a:a + 5]) for a in range(0, len(ent), 5)))
+        # ---- path-major program of the fused adjoint: per path p the cotangent slots of p are loaded (VL), every
+        # (i,p) group contracts geometry with them (ZF/ZA, then Q: dx[i] and the gate gradient of p), the slots are
+        # gated (VG) and the literal couplings of p give the harmonic gradient (DS: t = position in CLIST).  Only
+        # the slots of a few paths are live at a time (loads run two paths ahead of their use).  AP_TAB: geometry rows in
+        # this program's order.
+        ap = sorted(ik, key=lambda t: (t[2], t[0], t[1]))
+        btab("AP", ap)
+        pos_t = {(i, j, k, p_): t for t, (i, j, k, p_, c) in enumerate(byj)}
+        ent = []
+        ahead = 99                         # cotangent slots are requested this many paths before their use
+        slots_of = [[k for k, pp in enumerate(op) if pp == q_] for q_ in range(plan.num_paths)]
+        for q_ in range(min(ahead, plan.num_paths)):
+            ent += [f"VL({k})" for k in slots_of[q_]]
+        for p_ in range(plan.num_paths):
+            slots = slots_of[p_]
+            ent.append(f"PB({p_})")
+            if p_ + ahead < plan.num_paths:
+                ent += [f"VL({k})" for k in slots_of[p_ + ahead]]
+            rows = [(e, t) for e, t in enumerate(ap) if t[2] == p_]
+            for n_, (e, (i, k, _pp)) in enumerate(rows):
+                first = n_ == 0 or rows[n_ - 1][1][0] != i
+                last = n_ + 1 == len(rows) or rows[n_ + 1][1][0] != i
+                ent.append(f"{'ZF' if first else 'ZA'}({e},{k})")
+                if last:
+                    ent.append(f"Q({i},{p_})")
+            ent += [f"VG({k},{p_})" for k in slots]
+            for (i, j, k, pp, c) in sorted((e_ for e_ in plan.nnz if e_[3] == p_), key=lambda e_: (e_[1], e_[2], e_[0])):
+                ent.append(f"DS({pos_t[(i, j, k, pp)]},{i},{j},{k})")
+            ent.append(f"PE({p_})")
+        lines.append(f"#define ICTC_TP_{n}_ADJP(PB,VL,ZF,ZA,Q,VG,DS,PE) \\\n  " + " \\\n  ".join(
+            " ".join(ent[a:a + 6]) for a in range(0, len(ent), 6)))
         used_i = sorted({e[0] for e in plan.nnz})
         used_j = sorted({e[1] for e in plan.nnz})
         lines.append(f"#define ICTC_TP_{n}_XUSED(X) " + " ".join(f"X({i})" for i in used_i))

@@ -65,12 +65,20 @@ template <> __device__ __forceinline__ Vec<2> lds_vec<2>(const unsigned char* p)
 // are mostly L2 hits and are loaded straight into registers, which keeps shared-memory traffic low.
 constexpr bool kStageRows = false;
 
-// Resident blocks per SM the forward kernel is compiled for (caps its registers at 65536 / (128 * blocks);
-// the adjoint kernels would spill at that limit and keep the compiler's choice).
-#ifndef ICTC_TMA_MIN_BLOCKS
-#define ICTC_TMA_MIN_BLOCKS 3
+#ifndef ICTC_TMA_WARPS
+#define ICTC_TMA_WARPS 1
 #endif
-constexpr int kTmaMinBlocks = ICTC_TMA_MIN_BLOCKS;
+#ifndef ICTC_TMA_MIN_WARPS
+#define ICTC_TMA_MIN_WARPS 12
+#endif
+// Warps (= owner rows) per block and the resident warps per SM the kernels are compiled for (12 warps of 32 lanes cap
+// the registers at 168 per thread).  One warp per block: a block ends with its row, no warp waits for a longer row.
+constexpr int kTmaWarps = ICTC_TMA_WARPS;
+constexpr int kTmaMinBlocks = ICTC_TMA_MIN_WARPS / ICTC_TMA_WARPS;
+#ifndef ICTC_TMA_MIN_WARPS_ADJ
+#define ICTC_TMA_MIN_WARPS_ADJ 12
+#endif
+constexpr int kTmaMinBlocksAdj = ICTC_TMA_MIN_WARPS_ADJ / ICTC_TMA_WARPS;
 
 template <class S, class F, int CPL, int STAGES, bool ADJ> struct TmaLayout {
   static constexpr int C = 32 * CPL;
@@ -82,18 +90,18 @@ template <class S, class F, int CPL, int STAGES, bool ADJ> struct TmaLayout {
   static constexpr unsigned BAR_OFF = STAGES * SLOT_BYTES;
   static constexpr unsigned GEO_OFF = BAR_OFF + ((STAGES * 8 + 15) / 16) * 16;
   static constexpr unsigned WARP_BYTES = ((GEO_OFF + GEO_BYTES + 127) / 128) * 128;
-  static constexpr unsigned BLOCK_BYTES = WARP_BYTES * kFastWarps;
+  static constexpr unsigned BLOCK_BYTES = WARP_BYTES * kTmaWarps;
 };
 
 // ------------------------------------------------------------------------------------------------
 template <class S, class F, int CPL, int STAGES>
-__global__ void __launch_bounds__(kFastWarps * 32, kTmaMinBlocks) tp_graph_forward_tma_kernel(TpArgs a) {
+__global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocks) tp_graph_forward_tma_kernel(TpArgs a) {
   using V = Vec<CPL>;
   using L = TmaLayout<S, F, CPL, STAGES, false>;
   constexpr int C = L::C;
   extern __shared__ __align__(128) unsigned char tma_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t n = int64_t(blockIdx.x) * kFastWarps + warp;
+  const int64_t n = int64_t(blockIdx.x) * kTmaWarps + warp;
   if (n >= a.N) return;
   unsigned char* mine = tma_smem + warp * L::WARP_BYTES;
   const unsigned bars = smem_addr(mine + L::BAR_OFF);
@@ -201,13 +209,13 @@ __global__ void __launch_bounds__(kFastWarps * 32, kTmaMinBlocks) tp_graph_forwa
 
 // ------------------------------------------------------------------------------------------------
 template <class S, class F, int CPL, int STAGES, bool GRAPH, bool NEEDX, bool NEEDH, bool NEEDG>
-__global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs a) {
+__global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_tma_kernel(TpArgs a) {
   using V = Vec<CPL>;
   using L = TmaLayout<S, F, CPL, STAGES, true>;
   constexpr int C = L::C;
   extern __shared__ __align__(128) unsigned char tma_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t owner = int64_t(blockIdx.x) * kFastWarps + warp;
+  const int64_t owner = int64_t(blockIdx.x) * kTmaWarps + warp;
   if (owner >= (GRAPH ? a.N : a.E)) return;
   unsigned char* mine = tma_smem + warp * L::WARP_BYTES;
   const unsigned bars = smem_addr(mine + L::BAR_OFF);
@@ -220,7 +228,7 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs 
   __syncwarp();
   BTerm bt[L::R];
 #pragma unroll
-  for (int r = 0; r < L::R; ++r) bt[r] = (r * 32 + lane < F::NB) ? F::ab(r * 32 + lane) : BTerm{0, 0.f, 0, 0.f};
+  for (int r = 0; r < L::R; ++r) bt[r] = (r * 32 + lane < F::NB) ? F::ap(r * 32 + lane) : BTerm{0, 0.f, 0, 0.f};
   V x[S::NX], dx[S::NX];
   {
     const float* xp = a.x + owner * (S::NX * C) + lane * CPL;
@@ -266,12 +274,8 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs 
   for (int64_t it = begin; it < end; ++it, buf ^= 1) {
     const int64_t e = e_cur;
     const float sh_now = shv;
-    V ge[S::NP], v[S::NO], scale[S::NP];
-    if (!kStageRows) {
-      const float* vp = a.v + r_cur * (S::NO * C) + lane * CPL;
-#pragma unroll
-      for (int k = 0; k < S::NO; ++k) v[k] = V::load(vp + k * C);
-    }
+    static_assert(!kStageRows, "the path-major adjoint reads the cotangent row from global memory");
+    const float* vp = a.v + r_cur * (S::NO * C) + lane * CPL;     // this edge's cotangent row, read slot by slot
     int64_t e_pf2 = 0, d_pf2 = 0;
     if (it + 1 < end) {
       e_cur = edge_at(it + 1);
@@ -283,43 +287,29 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs 
       d_pf2 = row_of(e_pf2);
     }
     V* sb = geo + buf * L::NBP;
-    if (NEEDX || NEEDG) build_geometry<F::NB, CPL, L::R>(bt, sh_now, lane, sb);
+    build_geometry<F::NB, CPL, L::R>(bt, sh_now, lane, sb);
     if (!mbar_wait(bars + slot * 8, parity)) {
       if (lane == 0 && a.status) atomicExch(a.status, 2);
       for (int s = 0; s < STAGES; ++s) mbar_wait(bars + s * 8, parity);
       return;
     }
     const unsigned char* base = mine + slot * L::SLOT_BYTES + lane * (CPL * 4);
-#pragma unroll
-    for (int p = 0; p < S::NP; ++p) ge[p] = lds_vec<CPL>(base + p * (C * 4));
-    if (kStageRows) {
-#pragma unroll
-      for (int k = 0; k < S::NO; ++k) v[k] = lds_vec<CPL>(base + L::GATE_BYTES + k * (C * 4));
-    }
     const bool scaled = a.mask || a.w;
-    if (scaled) {
-      const V mu = V::dup(a.mask ? ldg(a.mask + e) : 1.f);
+    const V mu = V::dup((scaled && a.mask) ? ldg(a.mask + e) : 1.f);
+    auto scale_of = [&](int p) -> V { return a.w ? vmul(mu, V::load(a.w + p * C + lane * CPL)) : mu; };
+    auto gate = [&](int p) -> V {
+      const V g = lds_vec<CPL>(base + p * (C * 4));
+      return scaled ? vmul(g, scale_of(p)) : g;
+    };
+    float* dgp = a.dg + e * (S::NP * C) + lane * CPL;
+    auto store_dg = [&](int p, V val) { (scaled ? vmul(val, scale_of(p)) : val).store(dgp + p * C); };
+    __syncwarp();   // geometry visible to every lane
+    V dshv[S::NH];
 #pragma unroll
-      for (int p = 0; p < S::NP; ++p) {
-        scale[p] = a.w ? vmul(mu, V::load(a.w + p * C + lane * CPL)) : mu;
-        ge[p] = vmul(ge[p], scale[p]);
-      }
-    }
-    __syncwarp();
-    if (NEEDX || NEEDG) {
-      V dg[S::NP];
-#pragma unroll
-      for (int p = 0; p < S::NP; ++p) dg[p] = V::dup(0.f);
-      F::template adjoint_xg<NEEDX, NEEDG>(x, v, ge, sb, dx, dg);
-      if (NEEDG) {
-        float* dgp = a.dg + e * (S::NP * C) + lane * CPL;
-#pragma unroll
-        for (int p = 0; p < S::NP; ++p) (scaled ? vmul(dg[p], scale[p]) : dg[p]).store(dgp + p * C);
-      }
-    }
+    for (int j = 0; j < S::NH; ++j) dshv[j] = V::dup(0.f);
+    F::template adjoint_fused<NEEDX, NEEDH, NEEDG>(x, vp, gate, sb, dx, dshv, store_dg);
+    __syncwarp();   // every lane is done with the slot and the geometry buffer
     if (NEEDH) {
-      V dshv[S::NH];
-      F::dharm(x, v, ge, dshv);
       if constexpr (S::NP <= 4) {
         // few paths: the reduction is a large share of the per-edge work, use the 12-shuffle recursive halving
         float part[S::NH];
@@ -330,7 +320,6 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_tma_kernel(TpArgs 
         const float tot = warp_reduce_scatter<S::NH>(part, lane, which, holder);
         if (holder) a.dsh[e * S::NH + which] = tot;
       } else {
-        // many paths: the kernel is at its register limit, the plain butterfly keeps fewer values live
         float mine_sum = 0.f;
 #pragma unroll
         for (int j = 0; j < S::NH; ++j) {
@@ -374,8 +363,8 @@ template <class S, class F, int CPL> int launch_graph_forward_tma(const TpArgs& 
   auto kernel = tp_graph_forward_tma_kernel<S, F, CPL, kFwdStages>;
   static const int attr = set_smem(kernel, L::BLOCK_BYTES);
   if (attr != ICTC_OK) return attr;
-  const int64_t blocks = (a.N + kFastWarps - 1) / kFastWarps;
-  kernel<<<(unsigned)blocks, kFastWarps * 32, L::BLOCK_BYTES, st>>>(a);
+  const int64_t blocks = (a.N + kTmaWarps - 1) / kTmaWarps;
+  kernel<<<(unsigned)blocks, kTmaWarps * 32, L::BLOCK_BYTES, st>>>(a);
   return finish_launch("tp_graph_forward_tma");
 }
 
@@ -386,8 +375,8 @@ int launch_adjoint_tma_one(const TpArgs& a, cudaStream_t st) {
   static const int attr = set_smem(kernel, L::BLOCK_BYTES);
   if (attr != ICTC_OK) return attr;
   const int64_t owners = GRAPH ? a.N : a.E;
-  const int64_t blocks = (owners + kFastWarps - 1) / kFastWarps;
-  kernel<<<(unsigned)blocks, kFastWarps * 32, L::BLOCK_BYTES, st>>>(a);
+  const int64_t blocks = (owners + kTmaWarps - 1) / kTmaWarps;
+  kernel<<<(unsigned)blocks, kTmaWarps * 32, L::BLOCK_BYTES, st>>>(a);
   return finish_launch("tp_adjoint_tma");
 }
 
@@ -406,7 +395,7 @@ template <class S, class F, int CPL, bool GRAPH> int launch_adjoint_tma_g(const 
 }
 
 template <class S, int ID> int graph_forward_dispatch_tma(const TpArgs& a, cudaStream_t st) {
-  if (a.N > 0 && a.E > 0 && (a.C == 32 || a.C == 64) && (a.N + kFastWarps - 1) / kFastWarps <= 2147483647LL &&
+  if (a.N > 0 && a.E > 0 && (a.C == 32 || a.C == 64) && (a.N + kTmaWarps - 1) / kTmaWarps <= 2147483647LL &&
       aligned16(a.x) && aligned16(a.g) && aligned8(a.out) && (!a.w || aligned8(a.w))) {
     if (a.C == 64) return launch_graph_forward_tma<S, TpFast<ID, 2>, 2>(a, st);
     return launch_graph_forward_tma<S, TpFast<ID, 1>, 1>(a, st);
@@ -416,7 +405,7 @@ template <class S, int ID> int graph_forward_dispatch_tma(const TpArgs& a, cudaS
 
 template <class S, int ID> int adjoint_dispatch_tma(const TpArgs& a, bool graph, cudaStream_t st) {
   const int64_t owners = graph ? a.N : a.E;
-  if (owners > 0 && a.E > 0 && (a.C == 32 || a.C == 64) && (owners + kFastWarps - 1) / kFastWarps <= 2147483647LL &&
+  if (owners > 0 && a.E > 0 && (a.C == 32 || a.C == 64) && (owners + kTmaWarps - 1) / kTmaWarps <= 2147483647LL &&
       aligned16(a.g) && aligned16(a.v) && aligned8(a.x) && (!a.w || aligned8(a.w)) && (!a.dx || aligned8(a.dx)) &&
       (!a.dg || aligned8(a.dg))) {
     if (a.C == 64)
