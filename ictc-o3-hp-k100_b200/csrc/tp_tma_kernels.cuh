@@ -310,24 +310,14 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_t
     F::template adjoint_fused<NEEDX, NEEDH, NEEDG>(x, vp, gate, sb, dx, dshv, store_dg);
     __syncwarp();   // every lane is done with the slot and the geometry buffer
     if (NEEDH) {
-      if constexpr (S::NP <= 4) {
-        // few paths: the reduction is a large share of the per-edge work, use the 12-shuffle recursive halving
-        float part[S::NH];
+      // 12-shuffle recursive halving instead of nine 5-step butterflies
+      float part[S::NH];
 #pragma unroll
-        for (int j = 0; j < S::NH; ++j) part[j] = dshv[j].hsum();
-        int which;
-        bool holder;
-        const float tot = warp_reduce_scatter<S::NH>(part, lane, which, holder);
-        if (holder) a.dsh[e * S::NH + which] = tot;
-      } else {
-        float mine_sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < S::NH; ++j) {
-          const float tot = warp_sum(dshv[j].hsum());
-          if (lane == j) mine_sum = tot;
-        }
-        if (lane < S::NH) a.dsh[e * S::NH + lane] = mine_sum;
-      }
+      for (int j = 0; j < S::NH; ++j) part[j] = dshv[j].hsum();
+      int which;
+      bool holder;
+      const float tot = warp_reduce_scatter<S::NH>(part, lane, which, holder);
+      if (holder) a.dsh[e * S::NH + which] = tot;
     }
     if (it + STAGES < end) issue(slot, e_pf, d_pf);
     e_pf = e_pf2;
