@@ -399,9 +399,9 @@ def main_md(args, rank, world, local):
                              "achieved": achieved, "peak": peak, "unit": "GB/s",
                              "frac": achieved / peak if achieved else None, "peak_source": peak_src,
                              "algorithmic_bytes_per_launch": bwd_b,
-                             # DRAM bytes per launch: 6,246 B per edge measured by ncu on the 32,768-atom case
+                             # DRAM bytes per launch: 5,995 B per edge measured by ncu on the 32,768-atom case
                              # (dram__bytes_read.sum + dram__bytes_write.sum), scaled by this launch's edge count
-                             "traffic": 6246.0 * edges, "traffic_source": "ncu on 32768 atoms, scaled by edges"},
+                             "traffic": 5995.0 * edges, "traffic_source": "ncu on 32768 atoms, scaled by edges"},
                 "e2e": ({"value": atoms_total / (e2e[0] * 1e-3), "unit": "atom-steps/s", "h2d_bytes_per_step": e2e[1],
                          "d2h_bytes_per_step": e2e[2], "ms_per_step": e2e[0], "steps": e2e[3]} if e2e else None)}
         if world == 1 and not args.no_cpu_baseline:
