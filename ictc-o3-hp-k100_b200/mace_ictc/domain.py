@@ -147,6 +147,39 @@ class ExchangePlan:
         out.index_copy_(0, self.recv_perm, recv)
         return out
 
+    def forward_async(self, owned_rows: torch.Tensor):
+        """Starts ``forward`` and returns a callable that waits for it and gives the ghost rows; kernels launched in
+        between run while the rows travel (NCCL works on its own stream)."""
+        if self.world == 1:
+            out = self.forward(owned_rows)
+            return lambda: out
+        send = owned_rows.index_select(0, self.send_rows).contiguous()
+        recv = owned_rows.new_empty(sum(self.recv_split), owned_rows.shape[1])
+        work = dist.all_to_all_single(recv, send, self.recv_split, self.send_split, group=self.group, async_op=True)
+
+        def finish():
+            work.wait()
+            out = torch.empty_like(recv)
+            out.index_copy_(0, self.recv_perm, recv)
+            return out
+        return finish
+
+    def adjoint_async(self, ghost_grad: torch.Tensor):
+        """Starts ``adjoint`` and returns a callable that waits for it and gives the owners' cotangent rows."""
+        if self.world == 1:
+            out = self.adjoint(ghost_grad)
+            return lambda: out
+        send = ghost_grad.index_select(0, self.recv_perm).contiguous()
+        recv = ghost_grad.new_empty(sum(self.send_split), ghost_grad.shape[1])
+        work = dist.all_to_all_single(recv, send, self.send_split, self.recv_split, group=self.group, async_op=True)
+
+        def finish():
+            work.wait()
+            out = ghost_grad.new_zeros(self.num_owned, ghost_grad.shape[1])
+            out.index_add_(0, self.send_rows, recv)
+            return out
+        return finish
+
     def adjoint(self, ghost_grad: torch.Tensor) -> torch.Tensor:
         """Cotangent of the ghost rows -> cotangent of the owners' rows (repeated images accumulate)."""
         send = ghost_grad.index_select(0, self.recv_perm).contiguous()

@@ -384,8 +384,10 @@ class ForceEngine:
                                                          L0["pl"][l]).view(n_owned, mm * c)
             h1[:, :c] += sc0
             e0 = torch.mv(h1[:, :c], self.ro0)
-            # ---- halo
-            h1_full = h1 if plan is None else torch.cat((h1, plan.forward(h1)), 0)
+            # ---- halo: the ghost rows travel while the layer-1 gates (which need only the radial basis) are computed
+            halo = None if plan is None else plan.forward_async(h1)
+            g1, pre1 = self._mlp(rb_u, L1, rb_rows, live)
+            h1_full = h1 if plan is None else torch.cat((h1, halo()), 0)
             # ---- layer 1
             u1 = self._rows(n_local, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
@@ -394,7 +396,6 @@ class ForceEngine:
                     continue
                 u1[:, off * c:(off + mm) * c] = torch.mm(h1_full[:, off * c:(off + mm) * c].reshape(-1, c),
                                                          L1["up_t"][l]).view(n_local, mm * c)
-            g1, pre1 = self._mlp(rb_u, L1, rb_rows, live)
             M1 = self._tp_forward(1, u1, sh, g1, src, dst_rowptr, n_owned, e, L1["tpw"], grow)   # [n, 35C]
             m1 = self._rows(n_owned, 9 * c)
             in_off = 0
@@ -434,9 +435,6 @@ class ForceEngine:
                     self._transpose(n_owned, cnt, mm, buf, 0, mm * cnt * c, v1, out_off, 35 * c, False)
                 out_off += cnt * mm * c
             du1, dsh1, dg1 = self._tp_adjoint(1, u1, sh, g1, dst, src_csr, v1, n_local, e, L1["tpw"], True, grow)
-            drb = self._rows(e, nb, zero=True) if by_rows else None
-            drb = self._mlp_bwd(dg1, pre1, L1, pairs, drb, False, live)
-            del dg1, g1, pre1
             dh1_full = self._rows(n_local, 9 * c)
             for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
                 if tc:
@@ -444,9 +442,14 @@ class ForceEngine:
                     continue
                 dh1_full[:, off * c:(off + mm) * c] = torch.mm(du1[:, off * c:(off + mm) * c].reshape(-1, c),
                                                                L1["up"][l]).view(n_local, mm * c)
+            # the ghost rows' cotangents travel back while the layer-1 MLP is differentiated
+            halo = None if plan is None else plan.adjoint_async(dh1_full[n_owned:].contiguous())
+            drb = self._rows(e, nb, zero=True) if by_rows else None
+            drb = self._mlp_bwd(dg1, pre1, L1, pairs, drb, False, live)
+            del dg1, g1, pre1
             dh1 = dh1_full[:n_owned]
             if plan is not None:
-                dh1 = dh1 + plan.adjoint(dh1_full[n_owned:].contiguous())
+                dh1 = dh1 + halo()
             else:
                 dh1 = dh1.clone()
             dsc1 = dh2
