@@ -153,7 +153,9 @@ def emit_tp(lines):
                 if last:
                     ent.append(f"Q({i},{p_})")
             ent += [f"VG({k},{p_})" for k in slots]
-            for (i, j, k, pp, c) in sorted((e_ for e_ in plan.nnz if e_[3] == p_), key=lambda e_: (e_[1], e_[2], e_[0])):
+            # couplings of the path ordered by (slot, input component): consecutive terms feed different harmonic
+            # accumulators, so their FMAs do not wait for one another
+            for (i, j, k, pp, c) in sorted((e_ for e_ in plan.nnz if e_[3] == p_), key=lambda e_: (e_[2], e_[0], e_[1])):
                 ent.append(f"DS({pos_t[(i, j, k, pp)]},{i},{j},{k})")
             ent.append(f"PE({p_})")
         lines.append(f"#define ICTC_TP_{n}_ADJP(PB,VL,ZF,ZA,Q,VG,DS,PE) \\\n  " + " \\\n  ".join(
