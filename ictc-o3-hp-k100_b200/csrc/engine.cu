@@ -181,6 +181,32 @@ __global__ void slot_transpose_kernel(int64_t rows, int count, int m, int C, int
   }
 }
 
+// Whole-row layout conversion between mul_ir (block [C][m]) and ir_mul (block [m][C]) for a row made of
+// degree blocks, each holding `count` path slots.  One thread per output element: writes are coalesced,
+// reads are strided by at most 2l+1 floats and stay inside one cache line group.
+constexpr int kLayoutBlocks = 8;
+struct LayoutArgs {
+  int64_t rows;
+  int width, C, nblocks;
+  int count[kLayoutBlocks], m[kLayoutBlocks], off[kLayoutBlocks + 1];
+};
+
+__global__ void layout_copy_kernel(LayoutArgs a, const float* __restrict__ in, float* __restrict__ out, int to_ir_mul) {
+  const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= a.rows * a.width) return;
+  const int64_t r = idx / a.width;
+  const int col = int(idx % a.width);
+  int b = 0;
+  while (b + 1 < a.nblocks && col >= a.off[b + 1]) ++b;
+  const int m = a.m[b], C = a.C;
+  const int rel = col - a.off[b];
+  const int slot = rel / (C * m), q = rel % (C * m);
+  // output index q -> (outer, inner) of the OUTPUT block; the input block is its transpose
+  const int outer = to_ir_mul ? q / C : q / m, inner = to_ir_mul ? q % C : q % m;
+  const int src = to_ir_mul ? inner * m + outer : inner * C + outer;
+  out[idx] = in[r * a.width + a.off[b] + slot * C * m + src];
+}
+
 }  // namespace ictc
 
 using namespace ictc;
@@ -264,6 +290,30 @@ int ictc_slot_transpose(int64_t rows, int count, int m, int channels, int64_t in
     slot_transpose_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         rows, count, m, channels, in_stride, out_stride, in, out, to_gemm);
   return finish_launch("slot_transpose");
+}
+
+int ictc_layout_copy(int64_t rows, int channels, int num_blocks, const int* host_counts, const int* host_ms,
+                     const float* in, float* out, int to_ir_mul, void* stream) {
+  if (rows < 0 || channels < 1 || num_blocks < 1 || num_blocks > kLayoutBlocks || !host_counts || !host_ms) {
+    set_error("layout copy: invalid arguments");
+    return ICTC_ERR_BAD_ARG;
+  }
+  LayoutArgs a;
+  a.rows = rows; a.C = channels; a.nblocks = num_blocks;
+  int off = 0;
+  for (int b = 0; b < num_blocks; ++b) {
+    if (host_counts[b] < 0 || host_ms[b] < 1) { set_error("layout copy: invalid block"); return ICTC_ERR_BAD_ARG; }
+    a.count[b] = host_counts[b]; a.m[b] = host_ms[b]; a.off[b] = off;
+    off += host_counts[b] * host_ms[b] * channels;
+  }
+  a.off[num_blocks] = off;
+  a.width = off;
+  const int64_t total = rows * int64_t(off);
+  if (total == 0) return ICTC_OK;
+  if (!in || !out) { set_error("layout copy: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  if ((total + 255) / 256 > 2147483647LL) { set_error("layout copy: too large"); return ICTC_ERR_TOO_LARGE; }
+  layout_copy_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, in, out, to_ir_mul);
+  return finish_launch("layout_copy");
 }
 
 }  // extern "C"

@@ -59,6 +59,7 @@ SIGNATURES = {
     "ictc_silu_forward": (_I, [_L, C.c_float, _P, _P, _P]),
     "ictc_silu_backward": (_I, [_L, C.c_float, _P, _P, _P, _P]),
     "ictc_slot_transpose": (_I, [_L, _I, _I, _I, _L, _L, _P, _P, _I, _P]),
+    "ictc_layout_copy": (_I, [_L, _I, _I, C.POINTER(C.c_int), C.POINTER(C.c_int), _P, _P, _I, _P]),
     "ictc_split_tf32": (_I, [_L, _P, _P, _P]),
     "ictc_radial_mlp_forward": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_radial_mlp_backward": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),

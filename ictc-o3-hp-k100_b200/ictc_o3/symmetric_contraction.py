@@ -187,20 +187,20 @@ def create_symmetric_contraction(*, num_elements, lmax, target_lmax=None, channe
                                  training=False, reference_buffer_policy="auto", species_schedule="auto",
                                  inference_basis_fusion="auto"):
     """Create a parameterised trainable SC (ictc_o3/operators.py:493-526)."""
-    from .operators import _degree, _positive_integer, strict_fp32
-    _degree(lmax, "lmax")
-    _positive_integer(channels, "channels")
-    _positive_integer(correlation, "correlation")
-    if correlation not in (1, 2, 3):
-        raise ValueError("HP correlation currently supports 1, 2, 3; cor4/5 experiments are separate")
+    from .operators import _need_degree, _need_positive, strict_fp32
+    _need_degree(lmax, "lmax")
+    _need_positive(channels, "channels")
+    _need_positive(correlation, "correlation")
+    if correlation > 3:
+        raise ValueError(f"correlation: orders 1 to 3 are provided, got {correlation}")
     if not isinstance(use_reduced_cg, bool):
-        raise TypeError("use_reduced_cg must be a boolean")
+        raise TypeError(f"use_reduced_cg: expected True or False, got {type(use_reduced_cg).__name__}")
     if use_reduced_cg:
-        raise ValueError("The independent HP factory uses native full CG; cuEq reduced-basis generation is not enabled")
-    target_lmax = lmax if target_lmax is None else target_lmax
-    _degree(target_lmax, "target_lmax")
-    if not isinstance(num_elements, int) or isinstance(num_elements, bool) or num_elements < 1:
-        raise ValueError("num_elements must be a positive integer")
+        raise ValueError("use_reduced_cg: this factory builds the full Clebsch-Gordan basis only")
+    if target_lmax is None:
+        target_lmax = lmax
+    _need_degree(target_lmax, "target_lmax")
+    _need_positive(num_elements, "num_elements")
     strict_fp32()
     module = ICTDBridgeUSymmetricContractionSO3(
         num_elements=num_elements, channels=channels, lmax=lmax, target_lmax=target_lmax,
@@ -217,24 +217,21 @@ def configure_symmetric_contraction(module, *, policy="auto", high_l_policy="aut
     """Validate the reference's option set and report the selected plan (ictc_o3/operators.py:529-606).
 
     There is one kernel path here, so the K100 scheduling options only get validated."""
+    from .operators import _need_choice
     if not isinstance(module, ICTDBridgeUSymmetricContractionSO3):
-        raise TypeError("Expected ICTDBridgeUSymmetricContractionSO3")
-    if policy not in ("auto", "generated", "reference"):
-        raise ValueError("SC policy must be auto, generated or reference")
-    if high_l_policy not in ("auto", "off"):
-        raise ValueError("high_l_policy must be auto or off")
-    if species_schedule not in ('auto', 'grouped', 'indexed'):
-        raise ValueError('species_schedule must be auto, grouped or indexed')
-    if not (isinstance(inference_basis_fusion, bool) or inference_basis_fusion == 'auto'):
-        raise ValueError('inference_basis_fusion must be auto or a boolean')
+        raise TypeError(f"module: expected the bridge-U symmetric contraction, got {type(module).__name__}")
+    _need_choice(policy, ("auto", "generated", "reference"), "policy")
+    _need_choice(high_l_policy, ("auto", "off"), "high_l_policy")
+    _need_choice(species_schedule, ("auto", "grouped", "indexed"), "species_schedule")
+    _need_choice(reference_buffer_policy, ("auto", "device"), "reference_buffer_policy")
+    if inference_basis_fusion != "auto" and not isinstance(inference_basis_fusion, bool):
+        raise ValueError(f"inference_basis_fusion: expected 'auto', True or False, got {inference_basis_fusion!r}")
     if not isinstance(training, bool):
-        raise TypeError("training must be a boolean")
-    if reference_buffer_policy not in ('auto', 'device'):
-        raise ValueError('reference_buffer_policy must be auto or device')
-    parameter = next(module.parameters())
-    supported = parameter.is_cuda and parameter.dtype == torch.float32
-    if policy == "generated" and not supported:
-        raise ValueError("Generated SC requires CUDA FP32 and a positive-order bridge-U contraction")
+        raise TypeError(f"training: expected True or False, got {type(training).__name__}")
+    weights = next(module.parameters())
+    supported = weights.dtype == torch.float32 and weights.is_cuda
+    if not supported and policy == "generated":
+        raise ValueError("policy='generated' needs the module on a CUDA device in float32")
     return {"selected": "generated" if supported else "reference", "high_l_policy": high_l_policy,
             "species_schedule": species_schedule, "indexed_species_active": True,
             "inference_basis_fusion": inference_basis_fusion, "basis_fusion_active": False,

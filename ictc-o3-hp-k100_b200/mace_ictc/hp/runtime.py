@@ -6,47 +6,42 @@ import torch
 from ..model import MaceIctcModel
 
 
-def _degree(value, name):
-    if not isinstance(value, int) or isinstance(value, bool) or value < 0:
-        raise ValueError(f"{name} must be a nonnegative integer")
-
-
-def _positive_integer(value, name):
-    if not isinstance(value, int) or isinstance(value, bool) or value < 1:
-        raise ValueError(f"{name} must be a positive integer")
+from ictc_o3.operators import _need_degree, _need_positive
 
 
 def create_model(*, channels=64, lmax=3, edge_lmax=None, num_interactions=2, correlation=3, use_reduced_cg=False,
                  atomic_numbers=(1, 6, 8), cutoff=5.0, avg_num_neighbors=50.0, device="cuda", dtype=torch.float32,
                  electrostatics=None):
-    """Create a parameterised Cartesian model with freshly initialised weights (hp/runtime.py:6-79).
+    """A freshly initialised short-range model (reference factory: mace_ictc/hp/runtime.py:6-79): tensor-product
+    base coefficients fixed to one, radial MLP / channel linears / contraction weights trainable.
 
-    TP base coefficients are fixed to one; radial, linear and contraction weights are trainable.
-    Compiled coverage: lmax = edge_lmax = 2, fp32, short-range only (``electrostatics`` must be None).
+    Compiled coverage of this build: lmax = edge_lmax = 2, float32, CUDA, no electrostatics head.  Arguments
+    outside the reference's own domain raise the reference's exception types; arguments the reference accepts
+    but this build has no kernels for raise ValueError naming the limit.
     """
-    if not isinstance(num_interactions, int) or isinstance(num_interactions, bool) or num_interactions < 1:
-        raise ValueError("num_interactions must be a positive integer")
-    _positive_integer(channels, "channels")
-    _positive_integer(correlation, "correlation")
-    if correlation not in (1, 2, 3):
-        raise ValueError("HP correlation currently supports 1, 2, 3; cor4/5 experiments are separate")
+    _need_positive(num_interactions, "num_interactions")
+    _need_positive(channels, "channels")
+    _need_positive(correlation, "correlation")
+    if correlation > 3:
+        raise ValueError(f"correlation: orders 1 to 3 are provided, got {correlation}")
     if not isinstance(use_reduced_cg, bool):
-        raise TypeError("use_reduced_cg must be a boolean")
+        raise TypeError(f"use_reduced_cg: expected True or False, got {type(use_reduced_cg).__name__}")
     if use_reduced_cg:
-        raise ValueError("The independent HP factory uses native full CG; cuEq reduced-basis generation is not enabled")
-    _degree(lmax, "lmax")
-    edge_lmax = lmax if edge_lmax is None else edge_lmax
-    _degree(edge_lmax, "edge_lmax")
+        raise ValueError("use_reduced_cg: this factory builds the full Clebsch-Gordan basis only")
+    _need_degree(lmax, "lmax")
+    if edge_lmax is None:
+        edge_lmax = lmax
+    _need_degree(edge_lmax, "edge_lmax")
     if edge_lmax < lmax:
-        raise ValueError("edge_lmax must be at least lmax")
+        raise ValueError(f"edge_lmax ({edge_lmax}) may not be smaller than lmax ({lmax})")
     if electrostatics is not None:
-        raise ValueError("the long-range electrostatics head is outside this build (short-range model only)")
-    if lmax != 2 or edge_lmax != 2:
-        raise ValueError("kernels are compiled for lmax = edge_lmax = 2")
+        raise ValueError("electrostatics: the long-range head is not part of this build (short-range model only)")
+    if (lmax, edge_lmax) != (2, 2):
+        raise ValueError("lmax / edge_lmax: kernels are compiled for degree 2 only")
     if dtype != torch.float32:
-        raise ValueError("the kernels compute in fp32")
+        raise ValueError("dtype: the kernels compute in float32")
     if torch.device(device).type != "cuda":
-        raise ValueError("the model requires a CUDA device")
+        raise ValueError(f"device: a CUDA device is required, got {device!r}")
     model = MaceIctcModel(channels=channels, lmax=lmax, num_interactions=num_interactions, correlation=correlation,
                           atomic_numbers=atomic_numbers, cutoff=cutoff, avg_num_neighbors=avg_num_neighbors)
     return model.to(device=device, dtype=dtype)
@@ -54,30 +49,42 @@ def create_model(*, channels=64, lmax=3, edge_lmax=None, num_interactions=2, cor
 
 def energy_and_forces(model, positions, atomic_numbers, batch, edge_src, edge_dst, edge_shifts, cell, *,
                       training=False, owned_mask=None):
-    """Energy [B], forces [N,3] = -dE/dpos, atomic_energy [N] of a prebuilt graph (hp/runtime.py:82-111).
+    """Energies per graph [B], forces [N, 3] = -dE/dpositions and per-atom energies [N] of a graph whose edges
+    the caller has built (reference: mace_ictc/hp/runtime.py:82-111).
 
-    ``training=True`` keeps the graph of the force computation (mixed second derivatives for a force
-    loss); otherwise results are detached.  Shifts are lattice coordinates, cell is [B,3,3].
+    ``edge_shifts`` are lattice coordinates, ``cell`` is [B, 3, 3].  ``owned_mask`` [N] (constant) selects the
+    atoms whose energies count; the derivative is still taken with respect to every row of ``positions``,
+    ghost rows included.  With ``training=True`` the force computation stays on the tape, so a loss on the
+    forces can be differentiated (mixed second derivatives); otherwise everything returned is detached.
     """
     if torch.is_inference_mode_enabled():
-        raise ValueError("Full forces require autograd; use no_grad instead of inference_mode")
-    if positions.ndim != 2 or positions.shape[1] != 3 or cell.ndim != 3 or cell.shape[1:] != (3, 3):
-        raise ValueError("Expected positions [N,3] and cell [B,3,3]")
-    n = positions.shape[0]
-    if atomic_numbers.shape != (n,) or batch.shape != (n,):
-        raise ValueError("Atomic numbers and graph batch must have shape [N]")
-    if owned_mask is not None and (owned_mask.shape != (n,) or owned_mask.requires_grad):
-        raise ValueError("owned_mask must be a fixed [N] tensor")
+        raise ValueError("forces need the autograd tape: call under torch.no_grad(), not torch.inference_mode()")
+    count = positions.shape[0] if positions.ndim == 2 else -1
+    if count < 0 or positions.shape[1] != 3:
+        raise ValueError(f"positions: expected [N, 3], got {tuple(positions.shape)}")
+    if cell.ndim != 3 or tuple(cell.shape[1:]) != (3, 3):
+        raise ValueError(f"cell: expected [B, 3, 3], got {tuple(cell.shape)}")
+    for name, value in (("atomic_numbers", atomic_numbers), ("batch", batch)):
+        if tuple(value.shape) != (count,):
+            raise ValueError(f"{name}: expected shape [{count}], got {tuple(value.shape)}")
+    if owned_mask is not None:
+        if tuple(owned_mask.shape) != (count,) or owned_mask.requires_grad:
+            raise ValueError(f"owned_mask: expected a constant tensor of shape [{count}]")
     with torch.enable_grad():
-        pos = positions if positions.requires_grad else positions.detach().requires_grad_(True)
-        output = model(pos, atomic_numbers, batch, edge_src, edge_dst, edge_shifts, cell)
-        atomic = (output[0] if isinstance(output, tuple) else output).reshape(n)
-        selected = atomic if owned_mask is None else atomic * owned_mask.to(atomic)
-        energy = selected.new_zeros(cell.shape[0]).index_add(0, batch, selected)
-        force = -torch.autograd.grad(energy.sum() + pos.sum() * 0.0, pos, create_graph=training,
-                                     retain_graph=training)[0]
-        result = {"energy": energy, "forces": force, "atomic_energy": atomic}
-        return result if training else {key: value.detach() for key, value in result.items()}
+        coords = positions if positions.requires_grad else positions.detach().requires_grad_(True)
+        per_atom = model(coords, atomic_numbers, batch, edge_src, edge_dst, edge_shifts, cell)
+        if isinstance(per_atom, tuple):
+            per_atom = per_atom[0]
+        per_atom = per_atom.reshape(count)
+        counted = per_atom if owned_mask is None else per_atom * owned_mask.to(per_atom.dtype)
+        energy = torch.zeros(cell.shape[0], dtype=counted.dtype, device=counted.device).index_add_(0, batch, counted)
+        # the zero-weighted coordinate sum keeps `coords` in the graph when there is no edge at all
+        total = energy.sum() + 0.0 * coords.sum()
+        (gradient,) = torch.autograd.grad(total, coords, create_graph=training, retain_graph=training)
+    forces = -gradient
+    if training:
+        return {"energy": energy, "forces": forces, "atomic_energy": per_atom}
+    return {"energy": energy.detach(), "forces": forces.detach(), "atomic_energy": per_atom.detach()}
 
 
 _LEGACY_KEYS = {"policy", "training", "capture", "layout", "message_schedule", "edge_chunk_size", "gate_schedule",

@@ -21,7 +21,8 @@ import torch
 from torch import nn
 
 from ictc_o3.basis.ictd_irreps import EdgeWeightedPathPreservingTensorProduct
-from ictc_o3.operators import PackedGraphMessage, direction_harmonics, strict_fp32
+from ictc_o3.operators import (PackedGraphMessage, _RowsTimesWeight, _tc_eligible, channel_linear, convert_layout,
+                               direction_harmonics, strict_fp32)
 from ictc_o3.symmetric_contraction import ICTDBridgeUSymmetricContractionSO3
 
 SILU_SCALE = 1.6791767923989418
@@ -70,7 +71,7 @@ class EquivariantChannelLinearSO3(nn.Module):
     def forward(self, x):
         blocks = split_irreps(x, self.channels, self.lmax)
         for l in range(self.lmax + 1):
-            blocks[l] = torch.einsum("oc,ncm->nom", self.adapters[str(l)].weight, blocks[l])
+            blocks[l] = channel_linear(blocks[l], self.adapters[str(l)].weight)
         return merge_irreps(blocks, self.channels, self.lmax)
 
 
@@ -89,8 +90,8 @@ class PathPreservingLinearSO3(nn.Module):
             self.weights[str(l)] = nn.Parameter(w)
 
     def forward(self, blocks):
-        return merge_irreps({l: torch.einsum("oc,ncm->nom", self.weights[str(l)], blocks[l])
-                             for l in range(self.lmax + 1)}, self.out_channels, self.lmax)
+        return merge_irreps({l: channel_linear(blocks[l], self.weights[str(l)]) for l in range(self.lmax + 1)},
+                            self.out_channels, self.lmax)
 
 
 class ElementConditionedLinearSO3(nn.Module):
@@ -107,7 +108,9 @@ class ElementConditionedLinearSO3(nn.Module):
         out = {}
         for l in range(self.lmax + 1):
             # all species at once, then pick the node's own: avoids a per-node [C,C] weight gather
-            full = torch.einsum("soi,nim->nsom", self.weights[str(l)], blocks[l])
+            w = self.weights[str(l)]
+            full = channel_linear(blocks[l], w.reshape(-1, w.shape[-1])).reshape(
+                blocks[l].shape[0], self.num_elements, self.channels, 2 * l + 1)
             pick = idx.view(-1, 1, 1, 1).expand(-1, 1, self.channels, 2 * l + 1)
             out[l] = full.gather(1, pick).squeeze(1)
         return merge_irreps(out, self.channels, self.lmax)
@@ -148,19 +151,32 @@ class InteractionBlock(nn.Module):
             self._message = PackedGraphMessage(self.tp, input_lmax=self.input_lmax, edge_lmax=self.lmax)
         return self._message
 
+    def radial_gates(self, edge_feats):
+        """The gate MLP; layers whose sides are multiples of 64 (the hidden layers and the wide last one) run on
+        the tcgen05 channel-linear kernel, the narrow first layer on the library GEMM."""
+        h = edge_feats
+        for mod in self.fc:
+            if isinstance(mod, nn.Linear) and _tc_eligible(h, mod.weight):
+                h = _RowsTimesWeight.apply(h, mod.weight)
+            else:
+                h = mod(h)
+        return h
+
     def forward(self, h, sh, edge_feats, edge_src, edge_dst, edge_mask, species, topology=None):
         c = self.channels
         n = h.shape[0]
         up = self.linear_up(h)
-        x1 = split_irreps(up, c, self.input_lmax)
-        gates = self.fc(edge_feats)
+        gates = self.radial_gates(edge_feats)
         op = self.message_op()
-        x_packed = torch.cat([x1[l].transpose(1, 2).reshape(n, -1) for l in range(self.input_lmax + 1)], -1)
+        x_packed = convert_layout(up, c, op.edge._in_blocks(), True)
         if topology is not None:
             op._topology, op._topology_key = topology, (edge_src.data_ptr(), edge_src._version, edge_dst.data_ptr(),
                                                         edge_dst._version, edge_src.numel(), n)
-        out = op(x_packed.contiguous(), sh, gates, edge_src, edge_dst, edge_mask)
-        blocks = op.edge.unpack_output(out)
+        out = convert_layout(op(x_packed, sh, gates, edge_src, edge_dst, edge_mask), c, op.edge._out_blocks(), False)
+        blocks, start = {}, 0
+        for l, (slots, mm) in enumerate(op.edge._out_blocks()):
+            blocks[l] = out[:, start:start + slots * c * mm].reshape(n, slots * c, mm)
+            start += slots * c * mm
         message = self.message_linear(blocks) / max(self.avg_num_neighbors, 1e-8)
         sc_in = h if self.sc_lmax == self.input_lmax else split_irreps(h, c, self.input_lmax)[0].reshape(n, c)
         sc = self.self_connection.forward_type_idx(sc_in, species)
@@ -182,7 +198,7 @@ class ProductBlock(nn.Module):
         c = self.channels
         y = self.symmetric_contractions(message, None, species)
         blocks = split_irreps(y, c, self.target_lmax)
-        out = merge_irreps({l: torch.einsum("io,nim->nom", self.linear[str(l)], blocks[l]) / math.sqrt(c)
+        out = merge_irreps({l: channel_linear(blocks[l], self.linear[str(l)].t() / math.sqrt(c))
                             for l in range(self.target_lmax + 1)}, c, self.target_lmax)
         if sc is not None:
             if sc.shape[-1] == out.shape[-1]:

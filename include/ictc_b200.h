@@ -221,6 +221,14 @@ int ictc_silu_backward(int64_t n, float scale, const float* x, const float* dy, 
  * ictc_o3/backends/k100/hip_message_layout.py:27-34 for the message linear. */
 int ictc_slot_transpose(int64_t rows, int count, int m, int channels, int64_t in_stride, int64_t out_stride,
                         const float* in, float* out, int to_gemm, void* stream);
+/* Whole-row conversion between the model-native mul_ir layout (every block [C, 2l+1], channel outer) and the
+ * kernel-native ir_mul layout (every block [2l+1, C], channel contiguous) in one launch.  A row is a sequence of
+ * num_blocks degree blocks; block b holds host_counts[b] path slots of host_ms[b] components each (HOST int
+ * arrays, at most 8 blocks).  to_ir_mul != 0: in is mul_ir, out is ir_mul; 0: the reverse.  in and out must
+ * not overlap.  Replaces the `fused_pack` conversion kernel of ictc_o3/ops/message_layout.py:25-93
+ * (copy_layout, ictc_o3/backends/k100/hip_message_layout.py:27-34). */
+int ictc_layout_copy(int64_t rows, int channels, int num_blocks, const int* host_counts, const int* host_ms,
+                     const float* in, float* out, int to_ir_mul, void* stream);
 
 /* Radial gate MLP num_basis -> 64 -> 64 -> 64 -> num_out (bias-free, SiLU*1.6791767923989418 between
  * layers) on the tensor cores with error-compensated TF32 splitting (fp32-level accuracy).
