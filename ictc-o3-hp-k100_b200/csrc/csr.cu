@@ -89,7 +89,16 @@ __global__ void csr_fill_kernel(const int64_t* __restrict__ keys, int64_t E, int
   slots[pos] = e;
 }
 
-// One warp per row: order[row_begin + rank(edge id)] = edge id.
+// In-row ordering.  The slot hand-out above leaves the edge ids of a row in arrival order; they are put in
+// ascending order (a stable sort of the whole list) by one of two kernels:
+//   rows of at most kLongRow edges: one warp per row ranks every id against the row (quadratic, but the row is
+//     short and stays in L1);
+//   longer rows: one block per row sorts the ids in place with a bitonic network whose every compare-exchange
+//     keeps the minimum at the lower index, so positions beyond the row's end act as +infinity and are never
+//     touched; O(L log^2 L) instead of O(L^2), which bounds the run time of degenerate inputs (few rows, a
+//     million edges).
+constexpr int64_t kLongRow = 2048;
+
 __global__ void csr_rank_kernel(const int64_t* __restrict__ rowptr, int64_t N, const int64_t* __restrict__ slots,
                                 int64_t* order, const int32_t* flag) {
   if (*flag == 1) return;
@@ -97,11 +106,38 @@ __global__ void csr_rank_kernel(const int64_t* __restrict__ rowptr, int64_t N, c
   if (row >= N) return;
   const int lane = threadIdx.x & 31;
   const int64_t begin = rowptr[row], end = rowptr[row + 1];
+  if (end - begin > kLongRow) return;          // csr_sort_long_rows_kernel handles it
   for (int64_t a = begin + lane; a < end; a += 32) {
     const int64_t mine = slots[a];
     int64_t rank = 0;
     for (int64_t b = begin; b < end; ++b) rank += slots[b] < mine;
     order[begin + rank] = mine;
+  }
+}
+
+__global__ void csr_sort_long_rows_kernel(const int64_t* __restrict__ rowptr, int64_t N, int64_t* slots, int64_t* order,
+                                          const int32_t* flag) {
+  if (*flag == 1) return;
+  for (int64_t row = blockIdx.x; row < N; row += gridDim.x) {
+    const int64_t begin = rowptr[row], len = rowptr[row + 1] - begin;
+    if (len <= kLongRow) continue;             // uniform over the block
+    int64_t* v = slots + begin;
+    int64_t padded = 1;
+    while (padded < len) padded <<= 1;
+    for (int64_t k = 2; k <= padded; k <<= 1) {
+      for (int64_t j = k >> 1; j > 0; j >>= 1) {
+        for (int64_t i = threadIdx.x; i < padded; i += blockDim.x) {
+          const int64_t l = (j == (k >> 1)) ? (i ^ (k - 1)) : (i ^ j);     // first step of a stage mirrors the block
+          if (l > i && l < len) {
+            const int64_t a = v[i], b = v[l];
+            if (a > b) { v[i] = b; v[l] = a; }
+          }
+        }
+        __syncthreads();
+      }
+    }
+    for (int64_t i = threadIdx.x; i < len; i += blockDim.x) order[begin + i] = v[i];
+    __syncthreads();
   }
 }
 
@@ -224,7 +260,13 @@ int ictc_csr_build(const int64_t* keys, int64_t N, int64_t E, int64_t* rowptr, i
   if (E > 0) {
     if (N > 0) csr_cursor_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(rowptr, N, cursor);
     csr_fill_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(keys, E, N, cursor, slots, order, sorted_flag);
-    if (N > 0) csr_rank_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(rowptr, N, slots, order, sorted_flag);
+    if (N > 0) {
+      csr_rank_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(rowptr, N, slots, order, sorted_flag);
+      if (E > kLongRow) {      // a row longer than kLongRow can only exist when the list is
+        const unsigned blocks = (unsigned)(N < 1184 ? N : 1184);
+        csr_sort_long_rows_kernel<<<blocks, 512, 0, st>>>(rowptr, N, slots, order, sorted_flag);
+      }
+    }
   }
   return finish_launch("csr_build");
 }

@@ -66,7 +66,7 @@ constexpr int kAStagesBwd = 3;   // TMEM A ring of the backward kernel
 struct Barriers {
   unsigned long long w_full[kWStages], w_empty[kWStages], a_full[4], a_empty[4], d_full[4], d_empty[4];
   unsigned tmem_base;
-  int failed;
+  volatile int failed;   // polled inside wait loops by other warps: every read must go to shared memory
   volatile long long progress;   // backward: chunks finished by the first producer warp (read by the prefetch warps)
 };
 

@@ -50,7 +50,7 @@ struct Args {
 struct Barriers {
   unsigned long long a_ready[2], h_full[2], w_full, x_full[8], x_free[8];
   unsigned tmem_base;
-  int failed;
+  volatile int failed;   // polled inside wait loops by other warps: every read must go to shared memory
 };
 
 __device__ __forceinline__ void give_up(Barriers* b, int* status, int code) {

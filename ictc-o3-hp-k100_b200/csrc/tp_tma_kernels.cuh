@@ -172,8 +172,14 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocks) tp_graph_forwar
     build_geometry<F::NB, CPL, L::R>(bt, sh_now, lane, sb);
     if (!mbar_wait(bars + slot * 8, parity)) {
       if (lane == 0 && a.status) atomicExch(a.status, 1);
-      // outstanding copies of the other slots: bounded second wait, then leave
-      for (int s = 0; s < STAGES; ++s) mbar_wait(bars + s * 8, parity);
+      // drain the copies that are still in flight into this warp's shared memory before leaving: slots below
+      // `slot` were consumed and refilled in this round (their copy completes the NEXT phase), the others
+      // hold this round's copies; a slot is waited for only if an edge was really issued into it
+      for (int s = 0; s < STAGES; ++s) {
+        const bool refilled = s < slot;
+        const int64_t owner = it - slot + s + (refilled ? STAGES : 0);
+        if (owner < end) mbar_wait(bars + s * 8, refilled ? parity ^ 1u : parity);
+      }
       return;
     }
     const unsigned char* base = mine + slot * L::SLOT_BYTES + lane * (CPL * 4);
@@ -290,7 +296,11 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_t
     build_geometry<F::NB, CPL, L::R>(bt, sh_now, lane, sb);
     if (!mbar_wait(bars + slot * 8, parity)) {
       if (lane == 0 && a.status) atomicExch(a.status, 2);
-      for (int s = 0; s < STAGES; ++s) mbar_wait(bars + s * 8, parity);
+      for (int s = 0; s < STAGES; ++s) {     // drain, as in the forward kernel
+        const bool refilled = s < slot;
+        const int64_t owner = it - slot + s + (refilled ? STAGES : 0);
+        if (owner < end) mbar_wait(bars + s * 8, refilled ? parity ^ 1u : parity);
+      }
       return;
     }
     const unsigned char* base = mine + slot * L::SLOT_BYTES + lane * (CPL * 4);
