@@ -154,33 +154,6 @@ __global__ void silu_backward_kernel(int64_t n, float scale, const float* __rest
   dx[i] = dy[i] * scale * s * (1.f + v * (1.f - s));
 }
 
-// Row-block transposes between the TP output layout [rows][count][m][C] and the GEMM layout
-// [rows][m][count*C] of one degree (both directions are the same index map).
-// One thread moves VEC consecutive channels (128-bit accesses when VEC = 4).
-template <int VEC>
-__global__ void slot_transpose_kernel(int64_t rows, int count, int m, int C, int64_t in_stride, int64_t out_stride,
-                                      const float* __restrict__ in, float* out, int to_gemm) {
-  const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int cv = C / VEC;
-  const int64_t per_row = int64_t(count) * m * cv;
-  if (idx >= rows * per_row) return;
-  const int64_t r = idx / per_row;
-  const int rem = int(idx % per_row);
-  const int c = (rem % cv) * VEC;
-  const int a = (rem / cv) % (to_gemm ? count : m);     // inner of the two block indices of the OUTPUT
-  const int b = rem / (cv * (to_gemm ? count : m));     // outer one
-  // to_gemm: output [m][count][C], input [count][m][C];  otherwise the reverse
-  const int s = to_gemm ? a : b, mm = to_gemm ? b : a;
-  const int64_t in_off = to_gemm ? (int64_t(s) * m + mm) * C + c : (int64_t(mm) * count + s) * C + c;
-  const int64_t out_off = to_gemm ? (int64_t(mm) * count + s) * C + c : (int64_t(s) * m + mm) * C + c;
-  if (VEC == 4) {
-    *reinterpret_cast<float4*>(out + r * out_stride + out_off) =
-        *reinterpret_cast<const float4*>(in + r * in_stride + in_off);
-  } else {
-    out[r * out_stride + out_off] = in[r * in_stride + in_off];
-  }
-}
-
 // Whole-row layout conversion between mul_ir (block [C][m]) and ir_mul (block [m][C]) for a row made of
 // degree blocks, each holding `count` path slots.  One thread per output element: writes are coalesced,
 // reads are strided by at most 2l+1 floats and stay inside one cache line group.
@@ -272,24 +245,6 @@ int ictc_silu_backward(int64_t n, float scale, const float* x, const float* dy, 
   if (n == 0) return ICTC_OK;
   silu_backward_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(n, scale, x, dy, dx);
   return finish_launch("silu_backward");
-}
-
-int ictc_slot_transpose(int64_t rows, int count, int m, int channels, int64_t in_stride, int64_t out_stride,
-                        const float* in, float* out, int to_gemm, void* stream) {
-  if (rows < 0 || count < 1 || m < 1 || channels < 1) { set_error("slot transpose: invalid arguments"); return ICTC_ERR_BAD_ARG; }
-  const bool vec = channels % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 &&
-                   (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-  const int64_t total = rows * int64_t(count) * m * (vec ? channels / 4 : channels);
-  if (total == 0) return ICTC_OK;
-  if (!in || !out) { set_error("slot transpose: NULL buffer"); return ICTC_ERR_BAD_ARG; }
-  if ((total + 255) / 256 > 2147483647LL) { set_error("slot transpose: too large"); return ICTC_ERR_TOO_LARGE; }
-  if (vec)
-    slot_transpose_kernel<4><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        rows, count, m, channels, in_stride, out_stride, in, out, to_gemm);
-  else
-    slot_transpose_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        rows, count, m, channels, in_stride, out_stride, in, out, to_gemm);
-  return finish_launch("slot_transpose");
 }
 
 int ictc_layout_copy(int64_t rows, int channels, int num_blocks, const int* host_counts, const int* host_ms,

@@ -42,6 +42,11 @@ struct Args {
   const int64_t* pair_b;
   int64_t rows;
   const int64_t* limit;   // optional device scalar: only min(rows, *limit) rows are processed (recorded graphs)
+  // Row windows (plain matrices only).  With `begin` (device scalar) the launch covers the window
+  // [*begin, min(*begin + rows, *limit)) of a longer row list: local row g = 0.. stands for list entry *begin + g.
+  const int64_t* begin;
+  const int64_t* in_index;   // forward: local row g reads in[in_index[*begin + g]] (null: in[*begin + g])
+  const int64_t* out_index;  // backward: local row g is written to out[out_index[*begin + g]] (null: out[*begin + g])
   int nout;
   int act;                // forward: apply the scaled SiLU to the input
   int* status;
@@ -87,7 +92,9 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
   Barriers* bar = reinterpret_cast<Barriers*>(stage + 2 * kRows * kStagePitch);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = a.nout / kChunk;
-  const int64_t nrows = a.limit ? (ldg(a.limit) < a.rows ? ldg(a.limit) : a.rows) : a.rows;
+  const int64_t base = a.begin ? ldg(a.begin) : 0;
+  int64_t nrows = a.limit ? ldg(a.limit) - base : a.rows;
+  nrows = nrows < 0 ? 0 : (nrows < a.rows ? nrows : a.rows);
   const int64_t tiles = (nrows + kRows - 1) / kRows;
   const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
@@ -231,8 +238,9 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
       const int64_t g = (blockIdx.x + t * gridDim.x) * kRows + row;
       float x[32];
       if (g < nrows) {
+        const int64_t srow = a.in_index ? ldg(a.in_index + base + g) : base + g;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) ldg256(a.in + row_offset(g, a.in_mm, a.in_ld) + half * 32 + j * 8, x + j * 8);
+        for (int j = 0; j < 4; ++j) ldg256(a.in + row_offset(srow, a.in_mm, a.in_ld) + half * 32 + j * 8, x + j * 8);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) x[i] = 0.f;
@@ -270,7 +278,9 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
   Barriers* bar = reinterpret_cast<Barriers*>(w_buf + kWStages * kWStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = a.nout / kChunk;
-  const int64_t nrows = a.limit ? (ldg(a.limit) < a.rows ? ldg(a.limit) : a.rows) : a.rows;
+  const int64_t base = a.begin ? ldg(a.begin) : 0;
+  int64_t nrows = a.limit ? ldg(a.limit) - base : a.rows;
+  nrows = nrows < 0 ? 0 : (nrows < a.rows ? nrows : a.rows);
   const int64_t tiles = (nrows + kRows - 1) / kRows;
   const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
@@ -356,7 +366,8 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
       tc_fence_before();
       mbar_arrive(saddr(&bar->d_empty[d]));
       if (grow < nrows) {
-        float4* o = reinterpret_cast<float4*>(a.out + row_offset(grow, a.out_mm, a.out_ld));
+        const int64_t orow = a.out_index ? ldg(a.out_index + base + grow) : base + grow;
+        float4* o = reinterpret_cast<float4*>(a.out + row_offset(orow, a.out_mm, a.out_ld));
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           o[j] = make_float4(v0[4 * j], v0[4 * j + 1], v0[4 * j + 2], v0[4 * j + 3]);
@@ -551,6 +562,51 @@ int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, 
   a.status = kernel_status_word();
   gg::gate_gemm_backward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kBwdSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("gate_gemm_backward");
+}
+
+
+int ictc_gate_gemm_forward_rows(int64_t capacity, int num_out, const float* z3, const int64_t* row_index,
+                                const int64_t* row_begin, const int64_t* row_end, const float* w_packed, float* gates,
+                                int apply_silu, void* stream) {
+  if (int rc = gg::check_common(capacity, num_out)) return rc;
+  if (capacity == 0) return ICTC_OK;
+  if (!z3 || !w_packed || !gates || !row_begin || !row_end) { set_error("gate gemm forward rows: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  if ((reinterpret_cast<uintptr_t>(z3) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(gates)) & 31) {
+    set_error("gate gemm forward rows: buffers must be 32-byte aligned");
+    return ICTC_ERR_BAD_ARG;
+  }
+  static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_forward_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kFwdSmem);
+  if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
+  gg::Args a{};
+  a.in = z3; a.w = w_packed; a.out = gates; a.rows = capacity; a.limit = row_end; a.begin = row_begin; a.in_index = row_index;
+  a.nout = num_out; a.act = apply_silu ? 1 : 0;
+  a.in_mm = a.out_mm = a.in_cs = a.out_cs = 1; a.in_ld = gg::kK; a.out_ld = num_out;
+  a.status = kernel_status_word();
+  gg::gate_gemm_forward_kernel<<<gg::grid_size(capacity), gg::kThreads, gg::kFwdSmem, (cudaStream_t)stream>>>(a);
+  return finish_launch("gate_gemm_forward_rows");
+}
+
+int ictc_gate_gemm_backward_rows(int64_t capacity, int num_out, const float* dgates, const int64_t* row_begin,
+                                 const int64_t* row_end, const int64_t* out_index, const float* w_packed_t, float* da3,
+                                 void* stream) {
+  if (int rc = gg::check_common(capacity, num_out)) return rc;
+  if (capacity == 0) return ICTC_OK;
+  if (!dgates || !w_packed_t || !da3 || !row_begin || !row_end) { set_error("gate gemm backward rows: NULL buffer"); return ICTC_ERR_BAD_ARG; }
+  if ((reinterpret_cast<uintptr_t>(dgates) | reinterpret_cast<uintptr_t>(w_packed_t) | reinterpret_cast<uintptr_t>(da3)) & 31) {
+    set_error("gate gemm backward rows: buffers must be 32-byte aligned");
+    return ICTC_ERR_BAD_ARG;
+  }
+  static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_backward_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kBwdSmem);
+  if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
+  gg::Args a{};
+  a.in = dgates; a.w = w_packed_t; a.out = da3; a.rows = capacity; a.limit = row_end; a.begin = row_begin; a.out_index = out_index;
+  a.nout = num_out;
+  a.in_mm = a.out_mm = a.in_cs = a.out_cs = 1; a.in_ld = num_out; a.out_ld = gg::kK;
+  a.status = kernel_status_word();
+  gg::gate_gemm_backward_kernel<<<gg::grid_size(capacity), gg::kThreads, gg::kBwdSmem, (cudaStream_t)stream>>>(a);
+  return finish_launch("gate_gemm_backward_rows");
 }
 
 

@@ -40,6 +40,8 @@ struct Args {
   float* z3;
   float* drb;          // backward output [E, nb]
   const int64_t* rows; // optional row index: forward reads rb[rows[r]], backward writes / adds to drb[rows[r]]
+  const int64_t* in_a; // backward, optional: row r starts from in[in_a[r]] + in[in_b[r]] (in_b[r] < 0: first term only)
+  const int64_t* in_b;
   int accumulate;      // backward: drb[...] += instead of =
   const int64_t* limit; // optional device scalar: only min(E, *limit) rows are processed (recorded graphs)
   int64_t E;
@@ -242,8 +244,17 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_backward_kernel(Args a)
         }
         if (layer == 0) {
           if (valid) {
+            const int64_t ra = a.in_a ? ldg(a.in_a + g) : g;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) ldg256(a.in + g * kK + half * 32 + j * 8, x + j * 8);
+            for (int j = 0; j < 4; ++j) ldg256(a.in + ra * kK + half * 32 + j * 8, x + j * 8);
+            const int64_t rb = a.in_b ? ldg(a.in_b + g) : -1;
+            if (rb >= 0) {
+              float y[32];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) ldg256(a.in + rb * kK + half * 32 + j * 8, y + j * 8);
+#pragma unroll
+              for (int n = 0; n < 32; ++n) x[n] += y[n];
+            }
           } else {
 #pragma unroll
             for (int n = 0; n < 32; ++n) x[n] = 0.f;
@@ -345,6 +356,15 @@ int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, co
 int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0, const float* w1t_packed,
                             const float* w2t_packed, const float* z1, const float* z2, const float* z3, float* drb,
                             const int64_t* drb_rows, int accumulate, const int64_t* row_limit, void* stream) {
+  return ictc_mlp_chain_backward_paired(num_edges, num_basis, da3, nullptr, nullptr, w0, w1t_packed, w2t_packed, z1, z2,
+                                        z3, drb, drb_rows, accumulate, row_limit, stream);
+}
+
+int ictc_mlp_chain_backward_paired(int64_t num_edges, int num_basis, const float* da3, const int64_t* pair_a,
+                                   const int64_t* pair_b, const float* w0, const float* w1t_packed,
+                                   const float* w2t_packed, const float* z1, const float* z2, const float* z3,
+                                   float* drb, const int64_t* drb_rows, int accumulate, const int64_t* row_limit,
+                                   void* stream) {
   if (num_edges < 0 || num_basis < 1 || num_basis > 8) {
     set_error("mlp chain: needs 1..8 basis functions (got %d)", num_basis);
     return ICTC_ERR_BAD_SPEC;
@@ -361,7 +381,7 @@ int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, 
   if (attr != cudaSuccess) { set_error("mlp chain smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   chain::Args a{};
   a.in = da3; a.w0 = w0; a.wa = w2t_packed; a.wb = w1t_packed; a.z1 = const_cast<float*>(z1); a.z2 = const_cast<float*>(z2);
-  a.z3 = const_cast<float*>(z3); a.drb = drb; a.rows = drb_rows; a.limit = row_limit; a.accumulate = accumulate ? 1 : 0; a.E = num_edges; a.nb = num_basis;
+  a.z3 = const_cast<float*>(z3); a.drb = drb; a.in_a = pair_a; a.in_b = pair_b; a.rows = drb_rows; a.limit = row_limit; a.accumulate = accumulate ? 1 : 0; a.E = num_edges; a.nb = num_basis;
   a.status = kernel_status_word();
   chain::mlp_chain_backward_kernel<<<chain::grid_size(num_edges), chain::kThreads, chain::kSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("mlp_chain_backward");

@@ -184,4 +184,43 @@ int ictc_tp_graph_adjoint_shared(int spec, int channels, int64_t num_nodes, int6
   return o->adjoint(a, true, (cudaStream_t)stream);
 }
 
+int ictc_tp_graph_forward_chunk(int spec, int channels, int64_t num_rows, const float* x, const float* sh,
+                                const float* w, const float* g, const int64_t* gate_row, const int64_t* g_base,
+                                int64_t g_capacity, const int64_t* src, const int64_t* dst_rowptr,
+                                const int64_t* dst_order, const float* mask, float* out, void* stream) {
+  const TpOps* o = find_ops(spec);
+  if (!o) return ICTC_ERR_BAD_SPEC;
+  if (!check(channels > 0 && num_rows >= 0 && g_capacity >= 0, "sizes")) return ICTC_ERR_BAD_ARG;
+  if (num_rows == 0) return ICTC_OK;
+  if (!check(out && dst_rowptr && x && sh && g && src, "x, sh, g, src, dst_rowptr, out must not be NULL")) return ICTC_ERR_BAD_ARG;
+  if (!check(!g_base || g_capacity > 0, "g_capacity must be positive when g_base is given")) return ICTC_ERR_BAD_ARG;
+  TpArgs a{};
+  a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.out = out; a.nbr = src; a.rowptr = dst_rowptr;
+  a.grow = gate_row; a.order = dst_order; a.E = 1; a.N = num_rows; a.C = channels; a.status = kernel_status_word();
+  a.g_base = g_base; a.g_cap = g_capacity;
+  return o->graph_forward(a, (cudaStream_t)stream);
+}
+
+int ictc_tp_graph_adjoint_chunk(int spec, int channels, int64_t num_rows, const float* x, const float* sh,
+                                const float* w, const float* g, const int64_t* gate_row, int g_by_position,
+                                const int64_t* g_base, int64_t g_capacity, const int64_t* dst,
+                                const int64_t* src_rowptr, const int64_t* src_order, const float* mask, const float* v,
+                                float* dx, float* dsh, float* dg, const int64_t* dg_base, int64_t dg_capacity,
+                                void* stream) {
+  const TpOps* o = find_ops(spec);
+  if (!o) return ICTC_ERR_BAD_SPEC;
+  if (!check(channels > 0 && num_rows >= 0 && g_capacity >= 0 && dg_capacity >= 0, "sizes")) return ICTC_ERR_BAD_ARG;
+  if (num_rows == 0 || (!dx && !dsh && !dg)) return ICTC_OK;
+  if (!check(src_rowptr && x && sh && g && dst && v, "x, sh, g, dst, v, src_rowptr must not be NULL")) return ICTC_ERR_BAD_ARG;
+  if (!check(!g_base || g_capacity > 0, "g_capacity must be positive when g_base is given")) return ICTC_ERR_BAD_ARG;
+  if (!check(!(dg && dg_base) || dg_capacity > 0, "dg_capacity must be positive when dg_base is given")) return ICTC_ERR_BAD_ARG;
+  TpArgs a{};
+  a.x = x; a.sh = sh; a.w = w; a.g = g; a.mask = mask; a.v = v; a.dx = dx; a.dsh = dsh; a.dg = dg; a.nbr = dst;
+  a.grow = gate_row; a.rowptr = src_rowptr; a.order = src_order; a.E = 1; a.N = num_rows; a.C = channels;
+  a.status = kernel_status_word();
+  a.g_base = g_base; a.g_cap = g_capacity; a.g_by_pos = g_by_position ? 1 : 0;
+  a.dg_base = dg ? dg_base : nullptr; a.dg_cap = dg_capacity;
+  return o->adjoint(a, true, (cudaStream_t)stream);
+}
+
 }  // extern "C"

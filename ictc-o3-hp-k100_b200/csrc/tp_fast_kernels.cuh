@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_graph_forward_fast_kernel(
       s_next = ldg(a.nbr + e_next);
     }
     const float shv = lane < S::NH ? ldg(a.sh + e * S::NH + lane) : 0.f;
-    const float* gp = a.g + (a.grow ? ldg(a.grow + e) : e) * (S::NP * C) + lane * CPL;
+    const float* gp = a.g + gate_row_of(a, e, it) * (S::NP * C) + lane * CPL;
     const float* xp = a.x + s * (S::NX * C) + lane * CPL;
     V ge[S::NP], x[S::NX];
 #pragma unroll
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_fast_kernel(TpArgs
       d_next = GRAPH ? ldg(a.nbr + e_next) : e_next;
     }
     const float shv = lane < S::NH ? ldg(a.sh + e * S::NH + lane) : 0.f;
-    const float* gp = a.g + (a.grow ? ldg(a.grow + e) : e) * (S::NP * C) + lane * CPL;
+    const float* gp = a.g + gate_row_of(a, e, it) * (S::NP * C) + lane * CPL;
     const float* vp = a.v + d * (S::NO * C) + lane * CPL;
     V ge[S::NP], v[S::NO], scale[S::NP];
 #pragma unroll
@@ -292,9 +292,12 @@ __global__ void __launch_bounds__(kFastWarps * 32) tp_adjoint_fast_kernel(TpArgs
       for (int p = 0; p < S::NP; ++p) dg[p] = V::dup(0.f);
       F::template adjoint_xg<NEEDX, NEEDG>(x, v, ge, sb, dx, dg);
       if (NEEDG) {
-        float* dgp = a.dg + e * (S::NP * C) + lane * CPL;
+        const int64_t dgr = dg_row_of(a, e, it);
+        if (dgr >= 0) {
+          float* dgp = a.dg + dgr * (S::NP * C) + lane * CPL;
 #pragma unroll
-        for (int p = 0; p < S::NP; ++p) (scaled ? vmul(dg[p], scale[p]) : dg[p]).store(dgp + p * C);
+          for (int p = 0; p < S::NP; ++p) (scaled ? vmul(dg[p], scale[p]) : dg[p]).store(dgp + p * C);
+        }
       }
     }
     if (NEEDH) {

@@ -85,7 +85,30 @@ struct TpArgs {
   int64_t N, E;
   int C;
   int* status;          // device status word for kernels with bounded waits (may be null)
+  // Chunked evaluation (graph kernels; all optional).  A chunk is a range of owner rows whose gate rows, and for
+  // the adjoint gate-gradient rows, live in a buffer that covers only the chunk's edges.
+  const int64_t* g_base;   // device scalar subtracted from the gate row; rows are then clamped to [0, g_cap)
+  const int64_t* dg_base;  // device scalar: the gate gradient of the edge at CSR position q goes to row q - *dg_base
+                           // (rows outside [0, dg_cap) are not stored); null: row = edge id
+  int64_t g_cap, dg_cap;
+  int g_by_pos;            // gate row = CSR position of the edge instead of grow[e] / e
 };
+
+// Row of edge e, found at position `pos` of the owner's CSR walk, in the gate table.
+__device__ __forceinline__ int64_t gate_row_of(const TpArgs& a, int64_t e, int64_t pos) {
+  int64_t r = a.g_by_pos ? pos : (a.grow ? ldg(a.grow + e) : e);
+  if (a.g_base) {
+    r -= ldg(a.g_base);
+    r = r < 0 ? 0 : (r >= a.g_cap ? a.g_cap - 1 : r);
+  }
+  return r;
+}
+// Row of the edge's gate gradient; negative: outside the caller's buffer, do not store.
+__device__ __forceinline__ int64_t dg_row_of(const TpArgs& a, int64_t e, int64_t pos) {
+  if (!a.dg_base) return e;
+  const int64_t r = pos - ldg(a.dg_base);
+  return (r >= 0 && r < a.dg_cap) ? r : -1;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Edge-owned forward: one warp per (edge, 32-channel tile).
@@ -142,7 +165,7 @@ __global__ void __launch_bounds__(128) tp_graph_forward_kernel(TpArgs a) {
     for (int i = 0; i < S::NX; ++i) x[i] = ldg(a.x + (s * S::NX + i) * a.C + c);
 #pragma unroll
     for (int j = 0; j < S::NH; ++j) sh[j] = ldg(a.sh + e * S::NH + j);
-    const int64_t gr = a.grow ? ldg(a.grow + e) : e;
+    const int64_t gr = gate_row_of(a, e, it);
 #pragma unroll
     for (int p = 0; p < S::NP; ++p) ge[p] = ldg(a.g + (gr * S::NP + p) * a.C + c) * (wv[p] * mu);
     S::couple(x, sh, t);
@@ -192,7 +215,8 @@ __global__ void tp_adjoint_kernel(TpArgs a) {
     for (int q = 0; q < cnt; ++q) {
       const int64_t e = (GRAPH && a.order) ? ldg(a.order + base + q) : base + q;
       const int64_t vrow = GRAPH ? ldg(a.nbr + e) : e;
-      const int64_t gr = a.grow ? ldg(a.grow + e) : e;
+      const int64_t gr = gate_row_of(a, e, base + q);
+      const int64_t dgr = dg_row_of(a, e, base + q);
       const float mu = a.mask ? ldg(a.mask + e) : 1.f;
       float sh[S::NH], ge[S::NP], v[S::NO];
 #pragma unroll
@@ -208,9 +232,9 @@ __global__ void tp_adjoint_kernel(TpArgs a) {
         if (NEEDG) {
           float dg[S::NP];
           S::dgate(x, zq, dg);
-          if (on) {
+          if (on && dgr >= 0) {
 #pragma unroll
-            for (int p = 0; p < S::NP; ++p) a.dg[(e * S::NP + p) * a.C + c] = dg[p] * (wv[p] * mu);
+            for (int p = 0; p < S::NP; ++p) a.dg[(dgr * S::NP + p) * a.C + c] = dg[p] * (wv[p] * mu);
           }
         }
       }

@@ -120,12 +120,12 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocks) tp_graph_forwar
   for (int k = 0; k < S::NO; ++k) acc[k] = V::dup(0.f);
   const int64_t begin = ldg(a.rowptr + n), end = ldg(a.rowptr + n + 1);
   auto edge_at = [&](int64_t it) -> int64_t { return a.order ? ldg(a.order + it) : it; };
-  auto issue = [&](int slot, int64_t e, int64_t s) {
+  auto issue = [&](int slot, int64_t e, int64_t s, int64_t pos) {
     if (lane == 0) {
       const unsigned bar = bars + slot * 8;
       unsigned char* dst = mine + slot * L::SLOT_BYTES;
       mbar_expect_tx(bar, L::SLOT_BYTES);
-      const int64_t gr = a.grow ? ldg(a.grow + e) : e;
+      const int64_t gr = gate_row_of(a, e, pos);
       bulk_g2s(smem_addr(dst), a.g + gr * (S::NP * C), L::GATE_BYTES, bar);
       if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.x + s * (S::NX * C), L::ROW_BYTES, bar);
     }
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocks) tp_graph_forwar
   for (int k = 0; k < STAGES; ++k)
     if (begin + k < end) {
       const int64_t e = edge_at(begin + k);
-      issue(k, e, ldg(a.nbr + e));
+      issue(k, e, ldg(a.nbr + e), begin + k);
     }
   // (edge id, sender) of the edge that will be issued at the END of this iteration, started early
   int64_t e_pf = 0, s_pf = 0;
@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocks) tp_graph_forwar
     __syncwarp();   // geometry visible; every lane has read its slot data into registers
     F::forward(x, ge, sb, acc);
     // the slot's values were consumed by the arithmetic above: refill it for edge it + STAGES
-    if (it + STAGES < end) issue(slot, e_pf, s_pf);
+    if (it + STAGES < end) issue(slot, e_pf, s_pf, it + STAGES);
     e_pf = e_pf2;
     s_pf = s_pf2;
     if (++slot == STAGES) {
@@ -251,12 +251,12 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_t
   }
   auto edge_at = [&](int64_t it) -> int64_t { return (GRAPH && a.order) ? ldg(a.order + it) : it; };
   auto row_of = [&](int64_t e) -> int64_t { return GRAPH ? ldg(a.nbr + e) : e; };
-  auto issue = [&](int slot, int64_t e, int64_t d) {
+  auto issue = [&](int slot, int64_t e, int64_t d, int64_t pos) {
     if (lane == 0) {
       const unsigned bar = bars + slot * 8;
       unsigned char* dst = mine + slot * L::SLOT_BYTES;
       mbar_expect_tx(bar, L::SLOT_BYTES);
-      const int64_t gr = a.grow ? ldg(a.grow + e) : e;
+      const int64_t gr = gate_row_of(a, e, pos);
       bulk_g2s(smem_addr(dst), a.g + gr * (S::NP * C), L::GATE_BYTES, bar);
       if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.v + d * (S::NO * C), L::ROW_BYTES, bar);
     }
@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_t
   for (int k = 0; k < STAGES; ++k)
     if (begin + k < end) {
       const int64_t e = edge_at(begin + k);
-      issue(k, e, row_of(e));
+      issue(k, e, row_of(e), begin + k);
     }
   int64_t e_pf = 0, d_pf = 0;
   if (begin + STAGES < end) {
@@ -311,8 +311,11 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_t
       const V g = lds_vec<CPL>(base + p * (C * 4));
       return scaled ? vmul(g, scale_of(p)) : g;
     };
-    float* dgp = a.dg + e * (S::NP * C) + lane * CPL;
-    auto store_dg = [&](int p, V val) { (scaled ? vmul(val, scale_of(p)) : val).store(dgp + p * C); };
+    const int64_t dgr = NEEDG ? dg_row_of(a, e, it) : 0;
+    float* dgp = a.dg + (dgr < 0 ? 0 : dgr) * (S::NP * C) + lane * CPL;
+    auto store_dg = [&](int p, V val) {
+      if (dgr >= 0) (scaled ? vmul(val, scale_of(p)) : val).store(dgp + p * C);
+    };
     __syncwarp();   // geometry visible to every lane
     V dshv[S::NH];
 #pragma unroll
@@ -329,7 +332,7 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_t
       const float tot = warp_reduce_scatter<S::NH>(part, lane, which, holder);
       if (holder) a.dsh[e * S::NH + which] = tot;
     }
-    if (it + STAGES < end) issue(slot, e_pf, d_pf);
+    if (it + STAGES < end) issue(slot, e_pf, d_pf, it + STAGES);
     e_pf = e_pf2;
     d_pf = d_pf2;
     if (++slot == STAGES) {

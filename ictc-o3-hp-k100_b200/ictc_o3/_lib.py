@@ -29,9 +29,12 @@ SIGNATURES = {
     "ictc_tp_graph_adjoint": (_I, [_I, _I, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_tp_graph_forward_shared": (_I, [_I, _I, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_tp_graph_adjoint_shared": (_I, [_I, _I, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "ictc_radial_mlp_backward_paired": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "ictc_radial_mlp_hidden_forward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "ictc_radial_mlp_hidden_backward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "ictc_tp_graph_forward_chunk": (_I, [_I, _I, _L, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _P, _P, _P]),
+    "ictc_tp_graph_adjoint_chunk": (_I, [_I, _I, _L, _P, _P, _P, _P, _P, _I, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                         _L, _P]),
+    "ictc_gate_gemm_forward_rows": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _I, _P]),
+    "ictc_gate_gemm_backward_rows": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "ictc_mlp_chain_backward_paired": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P]),
     "ictc_gate_pack_weights": (_I, [_I, _P, _I, _P, _P]),
     "ictc_gate_gemm_forward": (_I, [_L, _I, _P, _P, _P, _I, _P, _P]),
     "ictc_gate_gemm_backward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P]),
@@ -58,11 +61,7 @@ SIGNATURES = {
     "ictc_position_gradient": (_I, [_L, _L, _P, _P, _P, _P, _P, _P]),
     "ictc_silu_forward": (_I, [_L, C.c_float, _P, _P, _P]),
     "ictc_silu_backward": (_I, [_L, C.c_float, _P, _P, _P, _P]),
-    "ictc_slot_transpose": (_I, [_L, _I, _I, _I, _L, _L, _P, _P, _I, _P]),
     "ictc_layout_copy": (_I, [_L, _I, _I, C.POINTER(C.c_int), C.POINTER(C.c_int), _P, _P, _I, _P]),
-    "ictc_split_tf32": (_I, [_L, _P, _P, _P]),
-    "ictc_radial_mlp_forward": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "ictc_radial_mlp_backward": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_harmonics_forward": (_I, [_I, _L, _P, _P, _P]),
     "ictc_harmonics_vjp": (_I, [_I, _L, _P, _P, _P, _P]),
     "ictc_harmonics_second": (_I, [_I, _L, _P, _P, _P, _P, _P, _P]),

@@ -6,8 +6,16 @@ Same arithmetic as ``MaceIctcModel.forward`` followed by ``autograd.grad(E, pos)
 what an MD step needs: frozen weights, gradient with respect to positions only.  Every adjoint below is
 the hand-written reverse of the line that produced the value; tests compare it with the autograd path.
 Node features live in ir_mul rows ([rows, 9C], degree blocks [2l+1, C]) from end to end, so channel
-linears are plain GEMMs over contiguous rows and no mul_ir <-> ir_mul conversion is made.
-Dense layers are fp32 library GEMMs (``torch.mm``).
+linears are GEMMs over contiguous rows and no mul_ir <-> ir_mul conversion is made.
+
+Gates are streamed (reference: ictc_o3/ops/streamed_gate_message.py:112-116, 193-221; chunk sizes
+mace_ictc/interfaces/lammps_hp.py:163-172).  The per-edge gate table [E, P*C] and its gradient are the largest
+tensors of the step, so the sweeps can run over chunks of owner rows (``chunk_rows``): the forward produces the
+gates of a chunk's edges from the 64-wide hidden state, consumes them and reuses the buffer; the reverse sweep
+recomputes the chunk's gates, lets the tensor-product adjoint write the chunk's gate gradients and contracts
+them back to the hidden width at once.  No tensor wider than 64 floats per edge outlives a chunk.  Without
+chunking the gate table of the (edge, reverse edge) pairs is kept for both sweeps and only the gate gradient is
+per edge.  Both modes run the same arithmetic per edge in the same order, so their results agree bit for bit.
 """
 from __future__ import annotations
 
@@ -19,32 +27,34 @@ import torch
 from ictc_o3 import _lib
 from ictc_o3.ops.topology import build_csr
 from ictc_o3.symmetric_contraction import _ScCall
-from . import domain as D
 from .model import SILU_SCALE, MaceIctcModel
 
-
-def _blocks(flat, c):
-    """Views of the three degree blocks of ir_mul rows [rows, 9C] as [rows, m, C]."""
-    rows = flat.shape[0]
-    return [flat[:, 0:c].reshape(rows, 1, c), flat[:, c:4 * c].reshape(rows, 3, c),
-            flat[:, 4 * c:9 * c].reshape(rows, 5, c)]
+_DEGREES = ((0, 1), (1, 3), (4, 5))        # (first component, number of components) of the degree blocks
 
 
 class ForceEngine:
-    def __init__(self, model: MaceIctcModel):
+    """``chunk_rows``: owner rows per chunk of the streamed gate evaluation (None: one pass over everything).
+    ``chunk_margin``: a chunk buffer holds ``chunk_rows x mean degree x chunk_margin`` edges; a chunk with more
+    edges than that raises ``overflow`` (device flag) and its surplus edges are dropped, never written out of
+    bounds."""
+
+    def __init__(self, model: MaceIctcModel, chunk_rows: int | None = None, chunk_margin: float = 1.3):
         if len(model.interactions) != 2:
             raise ValueError("the force engine covers the two-interaction model")
+        if model.channels != 64:
+            raise ValueError("the force engine runs on the 64-channel tensor-core kernels; other widths use the "
+                             "autograd route (MolecularDynamics(..., use_engine=False))")
         self.model = model
         self.c = model.channels
         self.dev = next(model.parameters()).device
         self.lib = _lib.load()
         self._versions = None
         self._spec = {0: _lib.tp_spec(0, 2, 2), 1: _lib.tp_spec(2, 2, 2)}
-        self.fused_mlp = True
-        self.gate_gemm = True    # last MLP layer on the tcgen05 tensor cores (False: single mma.sync kernel)
-        self.mlp_chain = True    # hidden MLP layers as a TMEM chain (False: mma.sync kernels)
-        self.tc_linear = True    # per-degree channel linears on the same kernels (False: library fp32 GEMM)
+        self.chunk_rows = None if chunk_rows is None else int(chunk_rows)
+        self.chunk_margin = float(chunk_margin)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=self.dev)   # sticky: a chunk buffer was too small
         self.profile = None      # list of (kernel name, start event, end event) when enabled by a benchmark
+        self._bounds = {}
         self.refresh()
 
     # ---------------------------------------------------------------- weights
@@ -57,63 +67,53 @@ class ForceEngine:
         with torch.no_grad():
             self.emb = m.node_embedding.weight.t().contiguous()                         # [S, C]
             self.layers = []
-            for k, (inter, prod) in enumerate(zip(m.interactions, m.products)):
+            for inter, prod in zip(m.interactions, m.products):
                 lin = inter.input_lmax
+                fc = [mod.weight.contiguous() for mod in inter.fc if isinstance(mod, torch.nn.Linear)]
+                if not (len(fc) == 4 and fc[0].shape[0] == 64 and fc[0].shape[1] <= 8 and tuple(fc[1].shape) == (64, 64)
+                        and tuple(fc[2].shape) == (64, 64) and fc[3].shape[1] == 64 and fc[3].shape[0] % 64 == 0):
+                    raise ValueError("the force engine needs the radial MLP num_basis (<= 8) -> 64 -> 64 -> 64 -> P*C")
                 L = {
-                    "up_t": [inter.linear_up.adapters[str(l)].weight.t().contiguous() for l in range(lin + 1)],
                     "up": [inter.linear_up.adapters[str(l)].weight.contiguous() for l in range(lin + 1)],
-                    "fc": [mod.weight.contiguous() for mod in inter.fc if isinstance(mod, torch.nn.Linear)],
-                    "fc_t": [mod.weight.t().contiguous() for mod in inter.fc if isinstance(mod, torch.nn.Linear)],
+                    "fc0": fc[0], "nout": fc[3].shape[0],
                     "ml": [(inter.message_linear.weights[str(l)] / max(inter.avg_num_neighbors, 1e-8)).contiguous()
                            for l in range(3)],
                     "counts": [inter.tp.path_counts_by_l[l] for l in range(3)],
                     "tpw": None if bool(torch.all(inter.tp.weight == 1)) else inter.tp.weight.contiguous(),
+                    "w3": self._pack(fc[3], 0), "w3t": self._pack(fc[3], 1),
+                    "hid": [self._pack(fc[1], 0), self._pack(fc[2], 0)],
+                    "hid_t": [self._pack(fc[1], 1), self._pack(fc[2], 1)],
                 }
-                L["ml_t"] = [w.t().contiguous() for w in L["ml"]]
-                L["w3_split"] = self._split(L["fc"][-1])
-                L["w3t_split"] = self._split(L["fc_t"][-1])
-                if self._fused_mlp_ok(L) and self.gate_gemm:
-                    L["w3_umma"] = self._pack_umma(L["fc"][-1], 0)
-                    L["w3t_umma"] = self._pack_umma(L["fc"][-1], 1)
-                    L["hid_umma"] = [self._pack_umma(L["fc"][1], 0), self._pack_umma(L["fc"][2], 0)]
-                    L["hid_t_umma"] = [self._pack_umma(L["fc"][1], 1), self._pack_umma(L["fc"][2], 1)]
                 wsc = inter.self_connection.weights["0"]                                 # [S, C(out), C(in)]
                 s = wsc.shape[0]
                 L["sc_fwd"] = wsc.permute(2, 0, 1).reshape(c, s * c).contiguous()          # x @ -> [n, S*C(out)]
                 L["sc_bwd"] = wsc.permute(1, 0, 2).reshape(c, s * c).contiguous()          # dout @ -> [n, S*C(in)]
                 L["bank"] = prod.symmetric_contractions.weight_bank()
                 L["target"] = prod.target_lmax
-                L["pl"] = [(prod.linear[str(l)] / math.sqrt(c)).contiguous() for l in range(prod.target_lmax + 1)]
-                L["pl_t"] = [w.t().contiguous() for w in L["pl"]]
-                if self.tc_linear and c == 64:
-                    # operand-layout copies for the tensor-core channel linears: key -> (packed, k_chunks, n_chunks)
-                    P = {}
-                    for l in range(lin + 1):
-                        P["up", l] = self._pack_lin(L["up"][l], L["up_t"][l])
-                        P["up_b", l] = self._pack_lin(L["up_t"][l], L["up"][l])
-                    for l in range(3):
-                        P["ml", l] = self._pack_lin(L["ml"][l], L["ml_t"][l])        # x @ ml_t
-                        P["ml_b", l] = self._pack_lin(L["ml_t"][l], L["ml"][l])      # x @ ml
-                    for l in range(prod.target_lmax + 1):
-                        P["pl", l] = self._pack_lin(L["pl_t"][l], L["pl"][l])        # x @ pl
-                        P["pl_b", l] = self._pack_lin(L["pl"][l], L["pl_t"][l])      # x @ pl_t
-                    L["packed"] = P
+                pl = [(prod.linear[str(l)] / math.sqrt(c)).contiguous() for l in range(prod.target_lmax + 1)]
+                L["pl0"], L["pl0_t"] = pl[0], pl[0].t().contiguous()
+                # operand-layout copies for the tensor-core channel linears: key -> (packed, k_chunks, n_chunks)
+                P = {}
+                for l in range(lin + 1):
+                    up = L["up"][l]
+                    P["up", l] = self._pack_lin(up, up.t().contiguous())                  # x @ up^T
+                    P["up_b", l] = self._pack_lin(up.t().contiguous(), up)                # x @ up
+                for l in range(3):
+                    ml = L["ml"][l]
+                    P["ml", l] = self._pack_lin(ml, ml.t().contiguous())                  # x @ ml^T
+                    P["ml_b", l] = self._pack_lin(ml.t().contiguous(), ml)                # x @ ml
+                for l in range(prod.target_lmax + 1):
+                    P["pl", l] = self._pack_lin(pl[l].t().contiguous(), pl[l])            # x @ pl
+                    P["pl_b", l] = self._pack_lin(pl[l], pl[l].t().contiguous())          # x @ pl^T
+                L["packed"] = P
                 self.layers.append(L)
             self.ro0 = m.layer_energy_readouts[0].readout.weight.reshape(-1).contiguous()  # [C]
             self.ro1_w1 = m.last_layer_energy_readout.linear_1.weight.contiguous()          # [16, C]
             self.ro1_w2 = m.last_layer_energy_readout.linear_2.weight.reshape(-1).contiguous()  # [16]
         self._versions = versions
 
-    def _split(self, w):
-        """{tf32(x), tf32(x - tf32(x))} pairs of a weight matrix for the tensor-core MLP kernels."""
-        out = torch.empty(*w.shape, 2, dtype=torch.float32, device=w.device)
-        with _lib.on_device(w.device):
-            _lib.check(self.lib.ictc_split_tf32(w.numel(), w.data_ptr(), out.data_ptr(), _lib.stream(w.device)),
-                       "split_tf32")
-        return out
-
-    def _pack_umma(self, w, transpose):
-        """Last-layer weights in the shared-memory operand layout of the tcgen05 gate GEMM kernels."""
+    def _pack(self, w, transpose):
+        """A [rows, 64] matrix in the shared-memory operand layout of the tcgen05 kernels."""
         out = torch.empty(2 * w.numel(), dtype=torch.float32, device=w.device)
         with _lib.on_device(w.device):
             _lib.check(self.lib.ictc_gate_pack_weights(w.shape[0], w.data_ptr(), transpose, out.data_ptr(),
@@ -124,10 +124,10 @@ class ForceEngine:
         """Operand copy for out = x @ w_in_major, where w_in_major is [K, N] and w_out_major its transpose."""
         k, n = w_in_major.shape
         if k == 64:
-            return self._pack_umma(w_out_major.contiguous(), 0), 1, n // 64
+            return self._pack(w_out_major.contiguous(), 0), 1, n // 64
         if n != 64:
             raise ValueError("tensor-core channel linear needs a 64-wide side")
-        return self._pack_umma(w_in_major.contiguous(), 1), k // 64, 1
+        return self._pack(w_in_major.contiguous(), 1), k // 64, 1
 
     def _lin(self, L, key, rows, in_t, in_off, in_mm, in_ld, out_t, out_off, out_mm, out_ld):
         """out rows = in rows @ W on the tensor cores, reading / writing per-degree blocks in place."""
@@ -137,6 +137,20 @@ class ForceEngine:
                                                    packed.data_ptr(), out_t.data_ptr() + 4 * out_off, out_mm, out_ld,
                                                    self._st()), "channel_linear_tc")
         self._done("channel_linear_tc", t0)
+
+    def _lin_blocks(self, L, key, rows, in_t, out_t, in_wide=None, out_wide=None, degrees=3):
+        """One channel linear per degree block of [rows, 9C] buffers; ``in_wide`` / ``out_wide`` = path-slot counts
+        per degree when that side is the [rows, 35C]-style slot-major tensor-product layout."""
+        c = self.c
+        in_off = out_off = 0
+        for l, (off, mm) in enumerate(_DEGREES[:degrees]):
+            i_off, i_ld = (in_off, in_t.shape[1]) if in_wide else (off * c, in_t.shape[1])
+            o_off, o_ld = (out_off, out_t.shape[1]) if out_wide else (off * c, out_t.shape[1])
+            self._lin(L, (key, l), rows * mm, in_t, i_off, mm, i_ld, out_t, o_off, mm, o_ld)
+            if in_wide:
+                in_off += in_wide[l] * mm * c
+            if out_wide:
+                out_off += out_wide[l] * mm * c
 
     # ---------------------------------------------------------------- buffers
     @staticmethod
@@ -169,111 +183,6 @@ class ForceEngine:
                                                self._st()), "silu_backward")
         return dx
 
-    def _fused_mlp_ok(self, L):
-        fc = L["fc"]
-        return (self.fused_mlp and len(fc) == 4 and fc[0].shape[0] == 64 and fc[0].shape[1] <= 8
-                and tuple(fc[1].shape) == (64, 64) and tuple(fc[2].shape) == (64, 64)
-                and fc[3].shape[1] == 64 and fc[3].shape[0] % 64 == 0)
-
-    def _chain_ok(self, L):
-        return self._fused_mlp_ok(L) and "w3_umma" in L and self.mlp_chain
-
-    def _mlp(self, rb, L, rows=None, limit=None):
-        """Radial MLP: returns gates and the pre-activations needed by the reverse sweep.  ``rows`` (tensor-memory
-        chain kernels only) makes row r of the MLP read rb[rows[r]]; ``limit`` is a device scalar with the number
-        of rows that are really in use (fixed-capacity buffers of a recorded step)."""
-        if self._fused_mlp_ok(L):
-            e, fc = (rb.shape[0] if rows is None else rows.numel()), L["fc"]
-            nout = fc[3].shape[0]
-            gates = self._rows(e, nout)
-            pre = [self._rows(e, 64) for _ in range(3)]
-            t0 = self._mark()
-            if "w3_umma" in L:
-                if self.mlp_chain:
-                    _lib.check(self.lib.ictc_mlp_chain_forward(e, rb.shape[1], _lib.ptr(rb), _lib.ptr(rows),
-                                                               fc[0].data_ptr(),
-                                                               L["hid_umma"][0].data_ptr(), L["hid_umma"][1].data_ptr(),
-                                                               _lib.ptr(pre[0]), _lib.ptr(pre[1]), _lib.ptr(pre[2]),
-                                                               _lib.ptr(limit), self._st()), "mlp_chain_forward")
-                else:
-                    _lib.check(self.lib.ictc_radial_mlp_hidden_forward(e, rb.shape[1], _lib.ptr(rb), fc[0].data_ptr(),
-                                                                       fc[1].data_ptr(), fc[2].data_ptr(),
-                                                                       _lib.ptr(pre[0]), _lib.ptr(pre[1]),
-                                                                       _lib.ptr(pre[2]), self._st()),
-                               "radial_mlp_hidden_forward")
-                self._done(f"radial_mlp_hidden_forward_{nout}", t0)
-                t0 = self._mark()
-                _lib.check(self.lib.ictc_gate_gemm_forward(e, nout, _lib.ptr(pre[2]), L["w3_umma"].data_ptr(),
-                                                           _lib.ptr(gates), 1, _lib.ptr(limit), self._st()),
-                           "gate_gemm_forward")
-                self._done(f"gate_gemm_forward_{nout}", t0)
-                return gates, pre
-            _lib.check(self.lib.ictc_radial_mlp_forward(e, rb.shape[1], nout, _lib.ptr(rb), fc[0].data_ptr(),
-                                                        fc[1].data_ptr(), fc[2].data_ptr(), L["w3_split"].data_ptr(),
-                                                        _lib.ptr(gates), _lib.ptr(pre[0]), _lib.ptr(pre[1]),
-                                                        _lib.ptr(pre[2]), self._st()), "radial_mlp_forward")
-            self._done(f"radial_mlp_forward_{nout}", t0)
-            return gates, pre
-        pre, h = [], rb
-        for k, wt in enumerate(L["fc_t"]):
-            z = torch.mm(h, wt)
-            if k + 1 < len(L["fc_t"]):
-                pre.append(z)
-                h = self._silu(z)
-            else:
-                return z, pre
-
-    def _mlp_bwd(self, dgates, pre, L, pairs=None, out=None, accumulate=False, limit=None):
-        """Input gradient of the radial MLP.  With ``out`` [E, num_basis] (chain kernels, paired rows) the result of
-        pair u is written or added to out[rep_edge[u]] and ``out`` is returned."""
-        if pairs is not None and not self._fused_mlp_ok(L):
-            dgates = dgates.index_select(0, pairs[1]) + torch.where(
-                (pairs[2] >= 0).unsqueeze(1), dgates.index_select(0, pairs[2].clamp_min(0)), dgates.new_zeros(()))
-            pairs = None
-        if self._fused_mlp_ok(L):
-            ft = L["fc_t"]
-            e = pre[0].shape[0]
-            nb = ft[0].shape[0]
-            drb = self._rows(e, nb) if out is None else out
-            t0 = self._mark()
-            pa, pb = (None, None) if pairs is None else (pairs[1], pairs[2])
-            if "w3t_umma" in L:
-                da3 = self._rows(e, 64)
-                _lib.check(self.lib.ictc_gate_gemm_backward(e, dgates.shape[1], _lib.ptr(dgates), _lib.ptr(pa),
-                                                            _lib.ptr(pb), L["w3t_umma"].data_ptr(), _lib.ptr(da3),
-                                                            _lib.ptr(limit), self._st()), "gate_gemm_backward")
-                self._done(f"gate_gemm_backward_{dgates.shape[1]}", t0)
-                t0 = self._mark()
-                if self.mlp_chain:
-                    _lib.check(self.lib.ictc_mlp_chain_backward(e, nb, _lib.ptr(da3), L["fc"][0].data_ptr(),
-                                                                L["hid_t_umma"][0].data_ptr(),
-                                                                L["hid_t_umma"][1].data_ptr(), _lib.ptr(pre[0]),
-                                                                _lib.ptr(pre[1]), _lib.ptr(pre[2]), _lib.ptr(drb),
-                                                                _lib.ptr(pa) if out is not None else None,
-                                                                int(accumulate), _lib.ptr(limit), self._st()),
-                               "mlp_chain_backward")
-                else:
-                    _lib.check(self.lib.ictc_radial_mlp_hidden_backward(e, nb, _lib.ptr(da3), ft[0].data_ptr(),
-                                                                        ft[1].data_ptr(), ft[2].data_ptr(),
-                                                                        _lib.ptr(pre[0]), _lib.ptr(pre[1]),
-                                                                        _lib.ptr(pre[2]), _lib.ptr(drb), self._st()),
-                               "radial_mlp_hidden_backward")
-                self._done(f"radial_mlp_hidden_backward_{dgates.shape[1]}", t0)
-                return drb
-            _lib.check(self.lib.ictc_radial_mlp_backward_paired(e, nb, dgates.shape[1], _lib.ptr(dgates), _lib.ptr(pa),
-                                                                _lib.ptr(pb), ft[0].data_ptr(),
-                                                                ft[1].data_ptr(), ft[2].data_ptr(),
-                                                                L["w3t_split"].data_ptr(), _lib.ptr(pre[0]),
-                                                                _lib.ptr(pre[1]), _lib.ptr(pre[2]), _lib.ptr(drb),
-                                                                self._st()), "radial_mlp_backward")
-            self._done(f"radial_mlp_backward_{dgates.shape[1]}", t0)
-            return drb
-        d = torch.mm(dgates, L["fc"][-1])
-        for k in range(len(pre) - 1, -1, -1):
-            d = self._silu_bwd(pre[k], d)
-            d = torch.mm(d, L["fc"][k])
-        return d                                                            # [E, num_basis]
-
     def _species_linear(self, x, species, w, s):
         full = torch.mm(x, w).view(x.shape[0], s, self.c)
         return full.gather(1, species.view(-1, 1, 1).expand(-1, 1, self.c)).squeeze(1)
@@ -289,36 +198,127 @@ class ForceEngine:
         if start is not None:
             self.profile.append((name, start, self._mark()))
 
-    def _tp_forward(self, layer, x, sh, g, src, rowptr, rows, e, tpw, grow=None):
-        c = self.c
-        out = self._rows(rows, (9 if layer == 0 else 35) * c)
+    # ---------------------------------------------------------------- radial MLP
+    def _hidden(self, rb, L, rows, count, limit):
+        """Hidden layers of the radial MLP: pre-activations z1..z3 [count, 64]; row r reads rb[rows[r]] (rows None:
+        rb[r]); ``limit`` = device scalar with the number of rows in use when ``count`` is a capacity."""
+        pre = [self._rows(count, 64) for _ in range(3)]
         t0 = self._mark()
-        _lib.check(self.lib.ictc_tp_graph_forward_shared(self._spec[layer], c, rows, e, x.data_ptr(), sh.data_ptr(),
-                                                         _lib.ptr(tpw), g.data_ptr(), _lib.ptr(grow), src.data_ptr(),
-                                                         rowptr.data_ptr(), None, None, out.data_ptr(), self._st()),
-                   "tp_graph_forward")
-        self._done(f"graph_forward_l{layer}", t0)
-        return out
+        _lib.check(self.lib.ictc_mlp_chain_forward(count, rb.shape[1], _lib.ptr(rb), _lib.ptr(rows), L["fc0"].data_ptr(),
+                                                   L["hid"][0].data_ptr(), L["hid"][1].data_ptr(), _lib.ptr(pre[0]),
+                                                   _lib.ptr(pre[1]), _lib.ptr(pre[2]), _lib.ptr(limit), self._st()),
+                   "mlp_chain_forward")
+        self._done(f"radial_mlp_hidden_forward_{L['nout']}", t0)
+        return pre
 
-    def _tp_adjoint(self, layer, x, sh, g, dst, src_csr, v, n_rows, e, tpw, need_x, grow=None):
-        c = self.c
-        dx = self._rows(x.shape[0], x.shape[1]) if need_x else None
-        dsh = self._rows(e, 9)
-        dg = self._rows(e, g.shape[1])
+    def _gate_table(self, z3, L, limit):
+        """Gates of every row of z3 (one row per edge pair, or per edge without pairing)."""
+        count, nout = z3.shape[0], L["nout"]
+        gates = self._rows(count, nout)
+        t0 = self._mark()
+        _lib.check(self.lib.ictc_gate_gemm_forward(count, nout, _lib.ptr(z3), L["w3"].data_ptr(), _lib.ptr(gates), 1,
+                                                   _lib.ptr(limit), self._st()), "gate_gemm_forward")
+        self._done(f"gate_gemm_forward_{nout}", t0)
+        return gates
+
+    def _gate_chunk(self, z3, L, buf, index, begin_ptr, end_ptr):
+        """Gates of the list entries [*begin, *end) into ``buf``: row r = act(z3[index[*begin + r]]) @ W3^T."""
+        t0 = self._mark()
+        _lib.check(self.lib.ictc_gate_gemm_forward_rows(buf.shape[0], L["nout"], _lib.ptr(z3), _lib.ptr(index), begin_ptr,
+                                                        end_ptr, L["w3"].data_ptr(), buf.data_ptr(), 1, self._st()),
+                   "gate_gemm_forward_rows")
+        self._done(f"gate_gemm_forward_{L['nout']}", t0)
+
+    def _chunks(self, rows, rowptr, edges):
+        """[(first row, end row)] of the owner-row chunks and the edge capacity of a chunk buffer; also raises the
+        device-side overflow flag when a chunk holds more edges than the buffer."""
+        if self.chunk_rows is None or self.chunk_rows >= rows:
+            return [(0, rows)], None
+        step = self.chunk_rows
+        key = (rows, step)
+        if key not in self._bounds:        # built outside any stream capture: the first call is a warm-up step
+            bounds = list(range(0, rows, step)) + [rows]
+            self._bounds[key] = (bounds, torch.tensor(bounds, dtype=torch.int64, device=self.dev))
+        bounds, idx = self._bounds[key]
+        cap = self.bucket(int(step * (edges / max(rows, 1)) * self.chunk_margin) + 1024)
+        cuts = rowptr.index_select(0, idx)
+        self.overflow.logical_or_(((cuts[1:] - cuts[:-1]) > cap).any())
+        return list(zip(bounds[:-1], bounds[1:])), cap
+
+    # ---------------------------------------------------------------- tensor-product sweeps
+    def _tp_forward(self, layer, L, x, sh, z3, src, rowptr, rows, e, grow, limit):
+        """Receiver-row sweep of one interaction: gates from z3 (pair rows through ``grow``), message rows out."""
+        c, lib = self.c, self.lib
+        width = (9 if layer == 0 else 35) * c
+        out = self._rows(rows, width)
+        chunks, cap = self._chunks(rows, rowptr, e)
+        if cap is None:
+            gates = self._gate_table(z3, L, limit)
+            t0 = self._mark()
+            _lib.check(lib.ictc_tp_graph_forward_shared(self._spec[layer], c, rows, e, x.data_ptr(), sh.data_ptr(),
+                                                        _lib.ptr(L["tpw"]), gates.data_ptr(), _lib.ptr(grow),
+                                                        src.data_ptr(), rowptr.data_ptr(), None, None, out.data_ptr(),
+                                                        self._st()), "tp_graph_forward")
+            self._done(f"graph_forward_l{layer}", t0)
+            return out, gates
+        buf = torch.empty(cap, L["nout"], dtype=torch.float32, device=self.dev)
+        for r0, r1 in chunks:
+            b, en = rowptr.data_ptr() + 8 * r0, rowptr.data_ptr() + 8 * r1
+            self._gate_chunk(z3, L, buf, grow, b, en)
+            t0 = self._mark()
+            _lib.check(lib.ictc_tp_graph_forward_chunk(self._spec[layer], c, r1 - r0, x.data_ptr(), sh.data_ptr(),
+                                                       _lib.ptr(L["tpw"]), buf.data_ptr(), None, b, cap, src.data_ptr(),
+                                                       b, None, None, out.data_ptr() + 4 * r0 * width, self._st()),
+                       "tp_graph_forward_chunk")
+            self._done(f"graph_forward_l{layer}", t0)
+        return out, None
+
+    def _tp_adjoint(self, layer, L, x, sh, z3, gates, dst, src_csr, v, n_rows, e, grow, grow_by_pos, need_x):
+        """Sender-row sweep: dx [n_rows, .] (optional), dsh [E, 9] and the gradient of silu(z3) per EDGE
+        (da3e [E, 64], row = edge id).  The gate gradients exist per chunk only."""
+        c, lib = self.c, self.lib
         rowptr, order = src_csr
-        t0 = self._mark()
-        _lib.check(self.lib.ictc_tp_graph_adjoint_shared(self._spec[layer], c, n_rows, e, x.data_ptr(), sh.data_ptr(),
-                                                         _lib.ptr(tpw), g.data_ptr(), _lib.ptr(grow), dst.data_ptr(),
-                                                         rowptr.data_ptr(), _lib.ptr(order), None, v.data_ptr(),
-                                                         _lib.ptr(dx), dsh.data_ptr(), dg.data_ptr(), self._st()),
-                   "tp_graph_adjoint")
-        self._done(f"graph_adjoint_l{layer}", t0)
-        return dx, dsh, dg
+        nout = L["nout"]
+        xw = x.shape[1]
+        dx = self._rows(n_rows, xw) if need_x else None
+        dsh = self._rows(e, 9)
+        da3e = self._rows(e, 64)
+        chunks, cap = self._chunks(n_rows, rowptr, e)
+        whole = cap is None
+        if whole:
+            cap = max(e, 1)
+        dg = torch.empty(self.bucket(cap) if whole else cap, nout, dtype=torch.float32, device=self.dev)
+        gbuf = None if whole else torch.empty(cap, nout, dtype=torch.float32, device=self.dev)
+        for s0, s1 in chunks:
+            b, en = rowptr.data_ptr() + 8 * s0, rowptr.data_ptr() + 8 * s1
+            if not whole:      # the chunk's gates are recomputed for the reverse sweep
+                self._gate_chunk(z3, L, gbuf, grow_by_pos, b, en)
+            t0 = self._mark()
+            _lib.check(lib.ictc_tp_graph_adjoint_chunk(
+                self._spec[layer], c, s1 - s0, x.data_ptr() + 4 * s0 * xw, sh.data_ptr(), _lib.ptr(L["tpw"]),
+                (gates if whole else gbuf).data_ptr(), _lib.ptr(grow) if whole else None, 0 if whole else 1,
+                None if whole else b, 0 if whole else cap, dst.data_ptr(), b, _lib.ptr(order), None, v.data_ptr(),
+                None if dx is None else dx.data_ptr() + 4 * s0 * xw, dsh.data_ptr(), dg.data_ptr(), b, cap, self._st()),
+                "tp_graph_adjoint_chunk")
+            self._done(f"graph_adjoint_l{layer}", t0)
+            t0 = self._mark()
+            _lib.check(lib.ictc_gate_gemm_backward_rows(cap, nout, dg.data_ptr(), b, en, _lib.ptr(order),
+                                                        L["w3t"].data_ptr(), da3e.data_ptr(), self._st()),
+                       "gate_gemm_backward_rows")
+            self._done(f"gate_gemm_backward_{nout}", t0)
+        return dx, dsh, da3e
 
-    def _transpose(self, rows, count, m, in_t, in_off, in_stride, out_t, out_off, out_stride, to_gemm):
-        _lib.check(self.lib.ictc_slot_transpose(rows, count, m, self.c, in_stride, out_stride,
-                                                in_t.data_ptr() + 4 * in_off, out_t.data_ptr() + 4 * out_off,
-                                                int(to_gemm), self._st()), "slot_transpose")
+    def _hidden_bwd(self, da3e, pre, L, pairs, drb, accumulate, limit):
+        """Input gradient of the hidden layers: row u starts from da3e[rep[u]] + da3e[other[u]] (the two edges of a
+        pair) and adds / writes its result to drb[rep[u]]; without pairing row = edge."""
+        count = pre[0].shape[0]
+        pa, pb = (None, None) if pairs is None else (pairs[1], pairs[2])
+        t0 = self._mark()
+        _lib.check(self.lib.ictc_mlp_chain_backward_paired(
+            count, L["fc0"].shape[1], _lib.ptr(da3e), _lib.ptr(pa), _lib.ptr(pb), L["fc0"].data_ptr(),
+            L["hid_t"][0].data_ptr(), L["hid_t"][1].data_ptr(), _lib.ptr(pre[0]), _lib.ptr(pre[1]), _lib.ptr(pre[2]),
+            _lib.ptr(drb), _lib.ptr(pa), int(accumulate), _lib.ptr(limit), self._st()), "mlp_chain_backward")
+        self._done(f"radial_mlp_hidden_backward_{L['nout']}", t0)
 
     # ---------------------------------------------------------------- the sweep
     @torch.no_grad()
@@ -329,7 +329,8 @@ class ForceEngine:
         per-atom energies [n_owned]).  ``n_rows`` < N_local marks trailing rows of ``pos`` as padding: they may
         be named by inert edges (whose sender index is then outside the sender CSR) but carry no features.
         ``pairs`` = (gate_row [E], rep_edge [U], other_edge [U]) evaluates the radial MLP once per edge pair; an
-        optional fourth element is a device int64 scalar with the number of pair rows in use when U is a capacity."""
+        optional fourth element is a device int64 scalar with the number of pair rows in use when U is a capacity.
+        ``plan`` (an exchange plan of ``mace_ictc.domain``) refreshes the ghost rows between the interactions."""
         self.refresh()
         m, c, lib, dev = self.model, self.c, self.lib, self.dev
         n_local, e = (pos.shape[0] if n_rows is None else int(n_rows)), int(src.numel())
@@ -349,69 +350,46 @@ class ForceEngine:
                                                       _lib.ptr(unit), _lib.ptr(length), st), "edge_geometry_forward")
             src_csr = build_csr(src, n_local, assume_sorted=False)
             grow = None if pairs is None else pairs[0]
-            by_rows = pairs is not None and self._chain_ok(L0) and self._chain_ok(L1)
-            rb_rows = pairs[1] if by_rows else None          # the MLP kernels gather / scatter the pair rows
-            live = pairs[3] if (by_rows and len(pairs) > 3) else None   # device count of pair rows in use
-            rb_u = rb if (pairs is None or by_rows) else rb.index_select(0, pairs[1])
+            rep = None if pairs is None else pairs[1]               # the MLP kernels gather / scatter the pair rows
+            live = pairs[3] if (pairs is not None and len(pairs) > 3) else None
+            count = e if pairs is None else int(rep.numel())
+            chunked = self.chunk_rows is not None and self.chunk_rows < max(n_owned, n_local)
+            # gate row of the edge at every position of the sender order (reverse sweep of the chunked mode)
+            grow_by_pos = None
+            if chunked:
+                grow_by_pos = src_csr[1] if grow is None else grow.index_select(0, src_csr[1])
             sp_owned = species[:n_owned]
             s_count = self.emb.shape[0]
             # ---- layer 0
             x0 = self.emb.index_select(0, species)                               # [N_local, C]
-            tc = "packed" in L0 and "packed" in L1
-            if tc:
-                u0 = self._rows(n_local, c)
-                self._lin(L0, ("up", 0), n_local, x0, 0, 1, c, u0, 0, 1, c)
-            else:
-                u0 = torch.mm(x0, L0["up_t"][0])
-            g0, pre0 = self._mlp(rb_u, L0, rb_rows, live)
-            M0 = self._tp_forward(0, u0, sh, g0, src, dst_rowptr, n_owned, e, L0["tpw"], grow)   # [n, 9C]
+            u0 = self._rows(n_local, c)
+            self._lin(L0, ("up", 0), n_local, x0, 0, 1, c, u0, 0, 1, c)
+            pre0 = self._hidden(rb, L0, rep, count, live)
+            M0, g0 = self._tp_forward(0, L0, u0, sh, pre0[2], src, dst_rowptr, n_owned, e, grow, live)   # [n, 9C]
             m0 = self._rows(n_owned, 9 * c)
-            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
-                if tc:
-                    self._lin(L0, ("ml", l), n_owned * mm, M0, off * c, mm, 9 * c, m0, off * c, mm, 9 * c)
-                    continue
-                m0[:, off * c:(off + mm) * c] = torch.mm(M0[:, off * c:(off + mm) * c].reshape(-1, c),
-                                                         L0["ml_t"][l]).view(n_owned, mm * c)
+            self._lin_blocks(L0, "ml", n_owned, M0, m0)
             sc0 = self._species_linear(x0[:n_owned], sp_owned, L0["sc_fwd"], s_count)
             call0 = _ScCall(c, 2, s_count, sp_owned, True)
             y0 = call0.forward(m0, L0["bank"])                                    # [n, 9C]
             h1 = self._rows(n_owned, 9 * c)
-            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
-                if tc:
-                    self._lin(L0, ("pl", l), n_owned * mm, y0, off * c, mm, 9 * c, h1, off * c, mm, 9 * c)
-                    continue
-                h1[:, off * c:(off + mm) * c] = torch.mm(y0[:, off * c:(off + mm) * c].reshape(-1, c),
-                                                         L0["pl"][l]).view(n_owned, mm * c)
+            self._lin_blocks(L0, "pl", n_owned, y0, h1)
             h1[:, :c] += sc0
             e0 = torch.mv(h1[:, :c], self.ro0)
-            # ---- halo: the ghost rows travel while the layer-1 gates (which need only the radial basis) are computed
+            # ---- halo: the ghost rows travel while the layer-1 hidden state (which needs only the radial basis) is computed
             halo = None if plan is None else plan.forward_async(h1)
-            g1, pre1 = self._mlp(rb_u, L1, rb_rows, live)
+            pre1 = self._hidden(rb, L1, rep, count, live)
             h1_full = h1 if plan is None else torch.cat((h1, halo()), 0)
             # ---- layer 1
             u1 = self._rows(n_local, 9 * c)
-            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
-                if tc:
-                    self._lin(L1, ("up", l), n_local * mm, h1_full, off * c, mm, 9 * c, u1, off * c, mm, 9 * c)
-                    continue
-                u1[:, off * c:(off + mm) * c] = torch.mm(h1_full[:, off * c:(off + mm) * c].reshape(-1, c),
-                                                         L1["up_t"][l]).view(n_local, mm * c)
-            M1 = self._tp_forward(1, u1, sh, g1, src, dst_rowptr, n_owned, e, L1["tpw"], grow)   # [n, 35C]
+            self._lin_blocks(L1, "up", n_local, h1_full, u1)
+            M1, g1 = self._tp_forward(1, L1, u1, sh, pre1[2], src, dst_rowptr, n_owned, e, grow, live)   # [n, 35C]
             m1 = self._rows(n_owned, 9 * c)
-            in_off = 0
-            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
-                cnt = L1["counts"][l]
-                if tc:      # the slot-major block is contracted in place: no transposed copy
-                    self._lin(L1, ("ml", l), n_owned * mm, M1, in_off, mm, 35 * c, m1, off * c, mm, 9 * c)
-                else:
-                    buf = torch.empty(n_owned * mm, cnt * c, dtype=torch.float32, device=dev)
-                    self._transpose(n_owned, cnt, mm, M1, in_off, 35 * c, buf, 0, mm * cnt * c, True)
-                    m1[:, off * c:(off + mm) * c] = torch.mm(buf, L1["ml_t"][l]).view(n_owned, mm * c)
-                in_off += cnt * mm * c
+            self._lin_blocks(L1, "ml", n_owned, M1, m1, in_wide=L1["counts"])     # slot-major block contracted in place
+            del M1
             sc1 = self._species_linear(h1[:, :c].contiguous(), sp_owned, L1["sc_fwd"], s_count)
             call1 = _ScCall(c, 0, s_count, sp_owned, True)
             y1 = call1.forward(m1, L1["bank"])                                    # [n, C]
-            h2 = torch.mm(y1, L1["pl"][0]) + sc1
+            h2 = torch.mm(y1, L1["pl0"]) + sc1
             z = torch.mm(h2, self.ro1_w1.t())
             a = self._silu(z)
             e1 = torch.mv(a, self.ro1_w2)
@@ -422,62 +400,36 @@ class ForceEngine:
             da = self.ro1_w2.unsqueeze(0).expand(n_owned, -1).contiguous()
             dz = self._silu_bwd(z, da)
             dh2 = torch.mm(dz, self.ro1_w1)                                        # [n, C]
-            dy1 = torch.mm(dh2, L1["pl_t"][0])
+            dy1 = torch.mm(dh2, L1["pl0_t"])
             dm1, _ = call1.adjoint(m1, L1["bank"], dy1, (True, False))             # [n, 9C]
             v1 = self._rows(n_owned, 35 * c)
-            out_off = 0
-            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
-                cnt = L1["counts"][l]
-                if tc:
-                    self._lin(L1, ("ml_b", l), n_owned * mm, dm1, off * c, mm, 9 * c, v1, out_off, mm, 35 * c)
-                else:
-                    buf = torch.mm(dm1[:, off * c:(off + mm) * c].reshape(-1, c), L1["ml"][l])   # [n*mm, cnt*C]
-                    self._transpose(n_owned, cnt, mm, buf, 0, mm * cnt * c, v1, out_off, 35 * c, False)
-                out_off += cnt * mm * c
-            du1, dsh1, dg1 = self._tp_adjoint(1, u1, sh, g1, dst, src_csr, v1, n_local, e, L1["tpw"], True, grow)
+            self._lin_blocks(L1, "ml_b", n_owned, dm1, v1, out_wide=L1["counts"])
+            du1, dsh1, da3e = self._tp_adjoint(1, L1, u1, sh, pre1[2], g1, dst, src_csr, v1, n_local, e, grow,
+                                               grow_by_pos, True)
+            del v1, g1
             dh1_full = self._rows(n_local, 9 * c)
-            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
-                if tc:
-                    self._lin(L1, ("up_b", l), n_local * mm, du1, off * c, mm, 9 * c, dh1_full, off * c, mm, 9 * c)
-                    continue
-                dh1_full[:, off * c:(off + mm) * c] = torch.mm(du1[:, off * c:(off + mm) * c].reshape(-1, c),
-                                                               L1["up"][l]).view(n_local, mm * c)
+            self._lin_blocks(L1, "up_b", n_local, du1, dh1_full)
             # the ghost rows' cotangents travel back while the layer-1 MLP is differentiated
             halo = None if plan is None else plan.adjoint_async(dh1_full[n_owned:].contiguous())
-            drb = self._rows(e, nb, zero=True) if by_rows else None
-            drb = self._mlp_bwd(dg1, pre1, L1, pairs, drb, False, live)
-            del dg1, g1, pre1
+            drb = self._rows(e, nb, zero=True)
+            self._hidden_bwd(da3e, pre1, L1, pairs, drb, False, live)
+            del pre1
             dh1 = dh1_full[:n_owned]
             if plan is not None:
                 dh1 = dh1 + halo()
             else:
                 dh1 = dh1.clone()
-            dsc1 = dh2
-            full = torch.mm(dsc1, L1["sc_bwd"]).view(n_owned, s_count, c)
+            full = torch.mm(dh2, L1["sc_bwd"]).view(n_owned, s_count, c)
             dh1[:, :c] += full.gather(1, sp_owned.view(-1, 1, 1).expand(-1, 1, c)).squeeze(1)
             dh1[:, :c] += self.ro0
             dy0 = self._rows(n_owned, 9 * c)
-            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
-                if tc:
-                    self._lin(L0, ("pl_b", l), n_owned * mm, dh1, off * c, mm, 9 * c, dy0, off * c, mm, 9 * c)
-                    continue
-                dy0[:, off * c:(off + mm) * c] = torch.mm(dh1[:, off * c:(off + mm) * c].reshape(-1, c),
-                                                          L0["pl_t"][l]).view(n_owned, mm * c)
+            self._lin_blocks(L0, "pl_b", n_owned, dh1, dy0)
             dm0, _ = call0.adjoint(m0, L0["bank"], dy0, (True, False))
             v0 = self._rows(n_owned, 9 * c)
-            for l, (off, mm) in enumerate(((0, 1), (1, 3), (4, 5))):
-                if tc:
-                    self._lin(L0, ("ml_b", l), n_owned * mm, dm0, off * c, mm, 9 * c, v0, off * c, mm, 9 * c)
-                    continue
-                v0[:, off * c:(off + mm) * c] = torch.mm(dm0[:, off * c:(off + mm) * c].reshape(-1, c),
-                                                         L0["ml"][l]).view(n_owned, mm * c)
-            _, dsh0, dg0 = self._tp_adjoint(0, u0, sh, g0, dst, src_csr, v0, n_local, e, L0["tpw"], False, grow)
-            if by_rows:
-                self._mlp_bwd(dg0, pre0, L0, pairs, drb, True, live)
-            else:
-                drb += self._mlp_bwd(dg0, pre0, L0, pairs)
-                if pairs is not None:      # the pair's length gradient is carried by its representative edge
-                    drb = torch.zeros(e, nb, dtype=torch.float32, device=dev).index_copy_(0, pairs[1], drb)
+            self._lin_blocks(L0, "ml_b", n_owned, dm0, v0)
+            _, dsh0, da3e = self._tp_adjoint(0, L0, u0, sh, pre0[2], g0, dst, src_csr, v0, n_local, e, grow,
+                                             grow_by_pos, False)
+            self._hidden_bwd(da3e, pre0, L0, pairs, drb, True, live)
             dsh1 += dsh0
             dvec = self._rows(e, 3)
             _lib.check(lib.ictc_edge_geometry_backward(_lib.ptr(unit), _lib.ptr(length), rmax, nb, pcut, e,

@@ -1,15 +1,28 @@
-"""Molecular-dynamics step on the B200 kernels: neighbour build, energy and forces, velocity Verlet,
-optional spatial domain decomposition over the GPUs of one node.
+"""Molecular-dynamics step on the B200 kernels: neighbour build, energy and forces, velocity Verlet, and
+spatial domain decomposition over the GPUs of one node with distributed state.
 
-The reference runs MD through LAMMPS (``examples/in.hco``: metal units, NVE, neighbour rebuild with
-0.5 A skin) with its pair style building the edge list from LAMMPS' full neighbour list
+The reference runs MD through LAMMPS (``examples/in.hco``: metal units, NVE, ``neighbor 0.5 bin``) with its
+pair style building the edge list from LAMMPS' full neighbour list
 (lammps_user_mfftorch/src/USER-MFFTORCH/pair_mff_torch_kokkos.cpp:661-871) and calling the model for
-``E_local = sum over owned atoms`` and ``F = -dE/dpos`` (mff_torch_engine.cpp:1739-1859).  LAMMPS is not
-part of this build; this module is the stand-alone driver with the same step semantics.
+``E_local = sum over owned atoms`` and ``F = -dE/dpos`` (mff_torch_engine.cpp:1739-1859); every MPI rank holds
+its own atoms and ghosts and ghost forces go back to the owners per peer (pair_mff_torch.cpp:222-274).
+LAMMPS is not part of this build; this module is the stand-alone driver with the same step semantics.
 Units: A, fs, eV, amu (1 eV/(A amu) = 9.64853321e-3 A/fs^2).
+
+One rank: positions of all atoms, wrapped into the box; the step can be recorded as one CUDA graph.
+Several ranks (``distributed=True``, one process per GPU): every rank keeps only the atoms of its brick
+(positions, velocities, species, global ids) plus ghosts within ``cutoff + skin`` of the brick.  Per step:
+position halo, edge list of the owned centres (rebuilt every step from the current coordinates, so the list is
+exactly the ``r <= cutoff`` list), two feature halos inside the model, gradient halo back to the owners.  The
+ghost LISTS are refreshed every few steps only: they stay valid while 2 x (largest displacement since the
+refresh) + (largest distance of an owned atom outside its brick) <= skin.  Buffers and collectives have fixed
+sizes, so the step, NCCL calls included, is recorded as one CUDA graph that survives the refreshes.  Ownership
+itself changes only at a re-decomposition (atoms migrate to the brick that contains them), which happens when an
+owned atom has strayed more than skin/2 from its brick.
 """
 from __future__ import annotations
 
+import ctypes as C
 import math
 
 import numpy as np
@@ -33,19 +46,20 @@ def _bucket(rows):
     return (rows + g - 1) // g * g
 
 
+def _arr(values, ctype):
+    return (ctype * 3)(*[values[i] for i in range(3)])
+
+
 def neighbor_list(pos, num_centres, lo, hi, box, periodic, cutoff, return_keys=False):
     """Edges (src=j, dst=i) of the first ``num_centres`` rows, sorted by (dst, src, shift).
 
     pos [N,3] fp32 CUDA; lo/hi: bounds of the cell grid; box: periodic lengths; periodic: 3 flags.
     Returns src, dst (int64 [E]), shifts (float32 [E,3], lattice units), rowptr (int64 [centres+1]).
     """
-    import ctypes as C
     lib, dev = _lib.load(), pos.device
     n = pos.shape[0]
-    arr = lambda v, t: (t * 3)(*[v[i] for i in range(3)])
-    lo_c, hi_c, box_c = arr([float(x) for x in lo], C.c_double), arr([float(x) for x in hi], C.c_double), \
-        arr([float(x) for x in box], C.c_double)
-    per_c = arr([int(x) for x in periodic], C.c_int)
+    lo_c, hi_c = _arr([float(x) for x in lo], C.c_double), _arr([float(x) for x in hi], C.c_double)
+    box_c, per_c = _arr([float(x) for x in box], C.c_double), _arr([int(x) for x in periodic], C.c_int)
     nbytes = int(lib.ictc_neighbor_scratch_bytes(n, lo_c, hi_c, float(cutoff)))
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     rowptr = torch.empty(num_centres + 1, dtype=torch.int64, device=dev)
@@ -97,27 +111,32 @@ class StaticNeighborList:
     """Neighbour list into fixed-capacity buffers, with no host read-back: the tail of the edge arrays
     is padded with inert edges (sender = the extra row ``num_atoms`` of the position buffer, which the
     sender CSR ignores; receiver 0) and an overflow flag stays on the device.  All buffers are allocated
-    once, so the sequence can be recorded in a CUDA graph."""
+    once, so the sequence can be recorded in a CUDA graph.
 
-    def __init__(self, num_atoms, box, cutoff, capacity, device):
-        import ctypes as C
+    ``num_centres`` (default: all atoms) rows get edges; ``lo`` / ``hi`` bound the cell grid (default: the
+    periodic box); ``periodic`` = three flags (a domain-decomposed rank passes zeros: its ghost rows already
+    carry the image shifts); ``pair_fraction`` sizes the pair table relative to the edge capacity (0.5 when
+    every edge has its reverse in the list, more when senders can be ghosts)."""
+
+    def __init__(self, num_atoms, box, cutoff, capacity, device, *, num_centres=None, lo=None, hi=None,
+                 periodic=(1, 1, 1), pair_fraction=0.5):
         self.n, self.cap, self.cutoff, self.dev = int(num_atoms), int(capacity), float(cutoff), device
+        self.centres = self.n if num_centres is None else int(num_centres)
         lib = _lib.load()
-        arr = lambda v, t: (t * 3)(*[v[i] for i in range(3)])
-        self.lo, self.hi = arr([0.0, 0.0, 0.0], C.c_double), arr([float(b) for b in box], C.c_double)
-        self.box, self.per = arr([float(b) for b in box], C.c_double), arr([1, 1, 1], C.c_int)
+        self.lo = _arr([0.0, 0.0, 0.0] if lo is None else [float(v) for v in lo], C.c_double)
+        self.hi = _arr([float(b) for b in box] if hi is None else [float(v) for v in hi], C.c_double)
+        self.box, self.per = _arr([float(b) for b in box], C.c_double), _arr([int(v) for v in periodic], C.c_int)
         n1 = self.n + 1                                   # the position buffer carries one extra (dummy) row
         self.scratch = torch.empty(int(lib.ictc_neighbor_scratch_bytes(n1, self.lo, self.hi, self.cutoff)),
                                    dtype=torch.uint8, device=device)
-        self.scan = torch.empty(int(lib.ictc_scan_scratch_bytes(self.n + 1)), dtype=torch.uint8, device=device)
-        self.rowptr = torch.zeros(self.n + 1, dtype=torch.int64, device=device)
+        self.scan = torch.empty(int(lib.ictc_scan_scratch_bytes(self.centres + 1)), dtype=torch.uint8, device=device)
+        self.rowptr = torch.zeros(self.centres + 1, dtype=torch.int64, device=device)
         self.src = torch.zeros(self.cap, dtype=torch.int64, device=device)
         self.dst = torch.zeros(self.cap, dtype=torch.int64, device=device)
         self.shifts = torch.zeros(self.cap, 3, dtype=torch.float32, device=device)
         self.keys = torch.zeros(self.cap, dtype=torch.int64, device=device)
         self.overflow = torch.zeros(1, dtype=torch.int32, device=device)
-        # radial pairing: on one GPU every edge has its reverse in the list, so there are E/2 pairs
-        self.ucap = self.cap // 2 + 1024
+        self.ucap = int(self.cap * pair_fraction) + 1024
         self.rev = torch.zeros(self.cap, dtype=torch.int64, device=device)
         self.pscan = torch.zeros(self.cap, dtype=torch.int64, device=device)
         self.gate_row = torch.zeros(self.cap, dtype=torch.int64, device=device)
@@ -127,9 +146,9 @@ class StaticNeighborList:
         self.pscratch = torch.empty(int(lib.ictc_scan_scratch_bytes(self.cap)), dtype=torch.uint8, device=device)
 
     def build(self, pos_ext):
-        """pos_ext [n+1, 3]: the real atoms followed by the dummy row (far away from every atom)."""
+        """pos_ext [n+1, 3]: the atoms followed by the dummy row (far away from every atom)."""
         lib, st = _lib.load(), _lib.stream(self.dev)
-        n, n1 = self.n, self.n + 1
+        n, n1 = self.centres, self.n + 1
         _lib.check(lib.ictc_neighbor_count(pos_ext.data_ptr(), n1, n, self.lo, self.hi, self.box, self.per,
                                            self.cutoff, self.rowptr.data_ptr(), self.scratch.data_ptr(), st),
                    "ictc_neighbor_count")
@@ -140,7 +159,7 @@ class StaticNeighborList:
                                           self.rowptr.data_ptr(), self.cap, self.src.data_ptr(), self.dst.data_ptr(),
                                           self.shifts.data_ptr(), self.keys.data_ptr(), self.scratch.data_ptr(), st),
                    "ictc_neighbor_fill")
-        _lib.check(lib.ictc_neighbor_pad(self.rowptr.data_ptr() + 8 * n, self.cap, n, 0, self.src.data_ptr(),
+        _lib.check(lib.ictc_neighbor_pad(self.rowptr.data_ptr() + 8 * n, self.cap, self.n, 0, self.src.data_ptr(),
                                          self.dst.data_ptr(), self.shifts.data_ptr(), None, st),
                    "ictc_neighbor_pad")
         _lib.check(lib.ictc_neighbor_pairs(self.rowptr.data_ptr(), self.dst.data_ptr(), self.keys.data_ptr(), n,
@@ -169,28 +188,47 @@ def maxwell_boltzmann(masses: np.ndarray, temperature: float, seed: int) -> np.n
 class MolecularDynamics:
     """NVE velocity-Verlet driver around a model created by ``mace_ictc.hp.create_model``.
 
-    With ``torch.distributed`` initialised (one rank per GPU) atoms are split over a brick grid: each
-    rank evaluates energies of its own atoms, node features of ghost atoms cross ranks inside the model
-    (``domain.exchange``) and the position gradients are summed over ranks.
+    ``positions`` [N,3], ``atomic_numbers`` [N] and ``velocities`` describe the WHOLE system on every rank; with
+    ``distributed=True`` (``torch.distributed`` initialised, one rank per GPU) each rank keeps the atoms of its
+    brick and forgets the rest.  ``pos``, ``vel``, ``forces`` then hold the owned atoms only, ``gid`` their
+    indices in the arrays given here; ``gather`` reassembles a global array.  Positions outside the box are
+    wrapped into it; an atomic number the model does not know raises ``ValueError``.
+    ``skin``: extra halo width of the decomposed run (see the module text).  ``chunk_rows``: owner rows per
+    chunk of the force engine's streamed gate evaluation (None: whole tables).  ``use_engine``: None picks the
+    tape-free force engine for the 64-channel two-interaction model and autograd through the same kernels
+    otherwise.  ``watch_peers``: check before every block of steps that all ranks are still there.
     """
 
     def __init__(self, model, positions, atomic_numbers, box, *, dt=1.0, temperature=300.0, seed=0,
-                 velocities=None, distributed=False, use_engine=True, share_gates=True):
+                 velocities=None, distributed=False, use_engine=None, share_gates=True, skin=1.0, chunk_rows=None,
+                 watch_peers=False):
         self.model = model
         dev = next(model.parameters()).device
         self.device = dev
         self.box = torch.as_tensor(np.asarray(box, dtype=np.float64))
         self.box_f = self.box.to(dev, torch.float32)
-        self.pos = torch.as_tensor(np.asarray(positions, dtype=np.float32)).to(dev).contiguous()
-        self.z = torch.as_tensor(np.asarray(atomic_numbers)).long().to(dev)
-        masses = np.array([MASSES[int(a)] for a in np.asarray(atomic_numbers)], dtype=np.float64)
-        self.masses = torch.as_tensor(masses, dtype=torch.float32).to(dev)
-        self.inv_mass = (1.0 / self.masses).contiguous()
-        if velocities is None:
-            velocities = maxwell_boltzmann(masses, temperature, seed)
-        self.vel = torch.as_tensor(np.asarray(velocities, dtype=np.float32)).to(dev).contiguous()
-        self.dt = float(dt)
         self.cutoff = float(model.max_radius)
+        z_all = np.asarray(atomic_numbers).astype(np.int64)
+        pos_all = np.asarray(positions, dtype=np.float32)
+        if pos_all.ndim != 2 or pos_all.shape[1] != 3 or z_all.shape != (pos_all.shape[0],):
+            raise ValueError("positions must be [N, 3] and atomic_numbers [N]")
+        if not np.isfinite(pos_all).all():
+            raise ValueError("positions must be finite")
+        model.skip_input_validation = False
+        species_all = model.species_index(torch.as_tensor(z_all).to(dev))        # raises ValueError on an unknown Z
+        unknown = [int(a) for a in np.unique(z_all) if int(a) not in MASSES]
+        if unknown:
+            raise ValueError(f"no mass tabulated for atomic numbers {unknown}")
+        masses_all = np.array([MASSES[int(a)] for a in z_all], dtype=np.float64)
+        if velocities is None:
+            velocities = maxwell_boltzmann(masses_all, temperature, seed)
+        vel_all = np.asarray(velocities, dtype=np.float32)
+        box32 = np.asarray(box, dtype=np.float32)
+        pos_all = pos_all - np.floor(pos_all / box32) * box32                    # wrap into [0, box)
+        pos_all = np.where(pos_all >= box32, pos_all - box32, pos_all).astype(np.float32)
+        self.num_atoms_total = int(pos_all.shape[0])
+        self.dt = float(dt)
+        self.skin = float(skin)
         self.distributed = bool(distributed)
         if self.distributed:
             import torch.distributed as dist
@@ -200,26 +238,54 @@ class MolecularDynamics:
             self.rank, self.world, self.grid = 0, 1, (1, 1, 1)
         model.preserve_edge_order = True
         model.skip_input_validation = True
-        self.species = model.species_index(self.z)
+        pos_t = torch.as_tensor(pos_all).to(dev)
+        if self.world > 1:
+            owner = D.owner_of(pos_t, self.box.tolist(), self.grid)
+            counts = torch.bincount(owner, minlength=self.world)
+            if int(counts.min()) == 0:      # the same decision on every rank: all ranks hold the whole system here
+                raise RuntimeError("a brick owns no atoms; use fewer ranks for this box")
+            mine = torch.nonzero(owner == self.rank).flatten()
+        else:
+            mine = torch.arange(self.num_atoms_total, device=dev)
+        self.gid = mine
+        self.pos = pos_t.index_select(0, mine).contiguous()
+        self.vel = torch.as_tensor(vel_all).to(dev).index_select(0, mine).contiguous()
+        self.z = torch.as_tensor(z_all).to(dev).index_select(0, mine)
+        self.species = species_all.index_select(0, mine)
+        self.masses = torch.as_tensor(masses_all, dtype=torch.float32).to(dev).index_select(0, mine)
+        self.inv_mass = (1.0 / self.masses).contiguous()
+        if use_engine is None:       # the tape-free engine exists for the 64-channel model; other widths differentiate
+            use_engine = model.channels == 64 and len(model.interactions) == 2      # through the same kernels by autograd
         if use_engine:
             from .engine import ForceEngine
-            self.engine = ForceEngine(model)
+            self.engine = ForceEngine(model, chunk_rows=chunk_rows)
         else:
             self.engine = None
         self.forces = None
         self.energy = None
         self.num_edges = 0
         self.num_gate_rows = 0       # rows of the gate table of the last force call (edge pairs, or edges)
-        self.launches = 0
         self.graph = None
         self._static = None
+        self._dist = None            # buffers of the decomposed step
         self.share_gates = bool(share_gates)     # evaluate the radial MLP once per (edge, reverse edge) pair
+        self.graph_rebuilds = 0
+        self.refreshes = 0           # ghost-list refreshes of the decomposed run
+        self.redecompositions = 0
+        self.block = 8               # steps between ghost-list refreshes (adapted by ``run``)
+        self._period_stale = True    # the first period does not lengthen the next one
+        self.capture_collectives = True
+        self.zero_box = torch.zeros(3, dtype=torch.float32, device=dev)
+        self._watch = D.PeerWatch() if (watch_peers and self.world > 1) else None
 
     # ------------------------------------------------------------------ forces
     def compute_forces(self):
         if self.world == 1:
             return self._forces_single()
-        return self._forces_decomposed()
+        if self._dist is None:
+            self._setup_distributed()
+        self._forces_distributed()
+        return self.forces
 
     def _forces_single(self):
         n = self.pos.shape[0]
@@ -251,63 +317,156 @@ class MolecularDynamics:
         self.forces = (-grad).contiguous()
         return self.forces
 
-    def _forces_decomposed(self):
-        import torch.distributed as dist
-        dom = D.decompose(self.pos, self.box.to(self.device), self.grid, self.rank, self.cutoff)
-        plan = D.ExchangePlan(dom, self.rank, self.world)
-        n_owned = dom.num_owned
-        if n_owned == 0:
-            raise RuntimeError("a rank owns no atoms; use fewer ranks for this box")
-        local = dom.local_positions(self.pos, self.box.to(self.device)).contiguous()
-        ids = dom.local_ids()
-        lo = (dom.lo - self.cutoff).tolist()
-        hi = (dom.hi + self.cutoff).tolist()
-        src, dst, shifts, rowptr, keys = neighbor_list(local, n_owned, lo, hi, self.box.tolist(), (0, 0, 0),
-                                                       self.cutoff, True)
-        self.num_edges = int(src.numel())
-        n_local = local.shape[0]
-        if self.engine is not None:
-            pairs = edge_pairs(rowptr, dst, keys, n_owned) if self.share_gates else None
-            self.num_gate_rows = int(pairs[1].numel()) if pairs is not None else self.num_edges
-            energy, grad, _ = self.engine.energy_and_gradient(local, self.species.index_select(0, ids), src, dst, None,
-                                                              self.box.tolist(), n_owned, rowptr, plan, pairs=pairs)
-            total = torch.zeros_like(self.pos)
-            total.index_add_(0, ids, grad)
-            e = energy.reshape(1).clone()
-            dist.all_reduce(total)
+    # ------------------------------------------------------------------ decomposed run: set-up and refresh
+    def _setup_distributed(self, edge_margin=1.15):
+        """Halo plan, fixed-capacity local buffers and neighbour-list buffers of this rank (collective)."""
+        if self.engine is None:
+            raise RuntimeError("the decomposed run uses the force engine (use_engine=True)")
+        dev, n_own = self.device, int(self.pos.shape[0])
+        halo = self.cutoff + self.skin
+        lo, hi = D.brick_bounds(self.rank, self.grid, self.box.tolist())
+        plan = D.HaloPlan(self.rank, self.world, self.grid, self.box.tolist(), halo, n_own, dev)
+        while not plan.refresh(self.pos):
+            pass
+        n_ghost = plan.num_ghost
+        n_local = n_own + n_ghost
+        # cell grid: the halo plus the room atoms may move before the next refresh
+        ext = halo + self.skin
+        grid_lo, grid_hi = [v - ext for v in lo], [v + ext for v in hi]
+        pos_ext = torch.zeros(n_local + 1, 3, dtype=torch.float32, device=dev)
+        pos_ext[n_local] = -1.0e6
+        species_ext = torch.zeros(n_local + 1, dtype=torch.long, device=dev)
+        species_ext[:n_own] = self.species
+        species_ext[n_own:n_local] = plan.integers(self.species)
+        pos_ext[:n_own] = self.pos
+        pos_ext[n_own:n_local] = plan.positions(self.pos)
+        # edge capacity from one eager build
+        src, _d, _s, rowptr = neighbor_list(pos_ext[:n_local], n_own, grid_lo, grid_hi, self.box.tolist(), (0, 0, 0),
+                                            self.cutoff)
+        edges = torch.tensor([float(src.numel())], device=dev)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(edges, op=dist.ReduceOp.MAX)
+        cap = int(float(edges.item()) * edge_margin) + 4096
+        nl = StaticNeighborList(n_local, self.box.tolist(), self.cutoff, cap, dev, num_centres=n_own, lo=grid_lo,
+                                hi=grid_hi, periodic=(0, 0, 0), pair_fraction=0.7)
+        self._dist = {"plan": plan, "nl": nl, "pos_ext": pos_ext, "species_ext": species_ext, "n_own": n_own,
+                      "n_local": n_local, "lo": lo, "hi": hi, "cap": cap, "edge_margin": edge_margin,
+                      "pos_ref": self.pos.clone(), "stale": torch.zeros(1, dtype=torch.int32, device=dev),
+                      "energy": torch.zeros(1, dtype=torch.float32, device=dev),
+                      "limit2": torch.zeros(1, dtype=torch.float32, device=dev), "since_refresh": 0}
+        self.forces = torch.zeros(n_own, 3, dtype=torch.float32, device=dev)
+        self.energy = self._dist["energy"][0]
+        self._set_displacement_budget()
+        self.graph = None
+
+    def _set_displacement_budget(self):
+        """limit on the displacement since the refresh: 2 * d + (distance outside the brick) <= skin."""
+        d = self._dist
+        out = float(D.outside_distance(d["pos_ref"], d["lo"], d["hi"]).max()) if d["n_own"] else 0.0
+        d["outside"] = out
+        budget = max(0.5 * (self.skin - out), 0.0)
+        d["limit2"].fill_(budget * budget)
+        d["stale"].zero_()
+
+    def refresh_ghosts(self):
+        """New ghost lists from the current coordinates, in place (collective; no buffer changes size).  Returns
+        False when the capacities no longer fit or an owned atom strayed too far: the caller re-decomposes."""
+        d = self._dist
+        stray = float(D.outside_distance(self.pos, d["lo"], d["hi"]).max()) > 0.5 * self.skin
+        if D.same_on_all_ranks(stray):
+            return False
+        if not d["plan"].refresh(self.pos):
+            return False
+        d["species_ext"][d["n_own"]:d["n_local"]] = d["plan"].integers(self.species)
+        d["pos_ref"].copy_(self.pos)
+        self._set_displacement_budget()
+        self.refreshes += 1
+        return True
+
+    def redecompose(self):
+        """Ownership from the current coordinates: atoms move to the rank whose brick contains them, the halo
+        plan and every buffer are rebuilt, a recorded graph is dropped (collective)."""
+        dev = self.device
+        box32 = self.box_f
+        self.pos -= torch.floor(self.pos / box32) * box32
+        self.pos = torch.where(self.pos >= box32, self.pos - box32, self.pos)
+        dest = D.owner_of(self.pos, self.box.tolist(), self.grid)
+        f = self.forces if self.forces is not None else torch.zeros_like(self.pos)
+        payload = torch.cat((self.pos.double(), self.vel.double(), f.double(), self.gid.double().unsqueeze(1),
+                             self.z.double().unsqueeze(1)), 1)
+        got = D.migrate(dest, payload, self.world)
+        if D.same_on_all_ranks(got.shape[0] == 0):
+            raise RuntimeError("a brick owns no atoms; use fewer ranks for this box")
+        order = torch.argsort(got[:, 9].long())          # ascending global id: a reproducible row order
+        got = got.index_select(0, order)
+        self.pos = got[:, 0:3].float().contiguous()
+        self.vel = got[:, 3:6].float().contiguous()
+        forces = got[:, 6:9].float().contiguous()
+        self.gid = got[:, 9].long()
+        self.z = got[:, 10].long()
+        self.species = self.model.atomic_number_to_index[self.z]
+        self.masses = torch.tensor([MASSES[int(a)] for a in self.z.tolist()], dtype=torch.float32, device=dev)
+        self.inv_mass = (1.0 / self.masses).contiguous()
+        self.graph, self._dist = None, None
+        self._setup_distributed()
+        self.forces.copy_(forces)
+        self.redecompositions += 1
+
+    # ------------------------------------------------------------------ decomposed run: one step
+    def _forces_distributed(self):
+        """Forces of the owned atoms from their current coordinates, on fixed buffers only: no host read-back, no
+        data-dependent host control flow (the sequence is what a recorded graph replays)."""
+        d = self._dist
+        plan, nl, n_own, n_local = d["plan"], d["nl"], d["n_own"], d["n_local"]
+        pos_ext = d["pos_ext"]
+        pos_ext[:n_own].copy_(self.pos)
+        pos_ext[n_own:n_local].copy_(plan.positions(self.pos))
+        # has any owned atom used up its displacement budget?  (sticky flag, read by ``run`` between blocks)
+        moved2 = (self.pos - d["pos_ref"]).square().sum(1).max()
+        d["stale"].logical_or_(moved2 > d["limit2"])
+        with _lib.on_device(self.device):
+            nl.build(pos_ext)
+        energy, grad, _ = self.engine.energy_and_gradient(pos_ext, d["species_ext"], nl.src, nl.dst, None,
+                                                          self.box.tolist(), n_own, nl.rowptr, plan=plan,
+                                                          n_rows=n_local,
+                                                          pairs=nl.pairs() if self.share_gates else None)
+        back = plan.adjoint(grad[n_own:n_local])          # ghost rows' gradients return to their owners
+        torch.add(grad[:n_own], back, out=self.forces)
+        self.forces.neg_()
+        e = energy.reshape(1).clone()
+        if self.world > 1:
+            import torch.distributed as dist
             dist.all_reduce(e)
-            self.energy = e[0]
-            self.forces = (-total).contiguous()
-            return self.forces
-        topo = Topology(src, dst, n_local, dst_sorted=True)
-        pad = rowptr.new_full((n_local - n_owned,), int(rowptr[-1].item()))
-        topo._by_dst = (torch.cat((rowptr, pad)), None)
-        pos = local.detach().requires_grad_(True)
-        batch = torch.zeros(n_local, dtype=torch.long, device=self.device)
-        cell = torch.diag(self.box_f).unsqueeze(0)
+        d["energy"].copy_(e)
 
-        def callback(layer, h_owned):
-            if layer == len(self.model.interactions) - 1:
-                return h_owned
-            return torch.cat((h_owned, D.exchange(h_owned, plan)), 0)
+    def _step_distributed(self):
+        self._kick(True)
+        self._forces_distributed()
+        self._kick(False)
 
-        with torch.enable_grad():
-            atomic = self.model(pos, self.z.index_select(0, ids), batch, src, dst, shifts, cell,
-                                local_atom_count=n_owned, layer_state_callback=callback, topology=topo)
-            energy = atomic[:n_owned].sum()
-            (grad,) = torch.autograd.grad(energy, pos)
-        total = torch.zeros_like(self.pos)
-        total.index_add_(0, ids, grad)
-        e = energy.detach().reshape(1).clone()
-        dist.all_reduce(total)
-        dist.all_reduce(e)
-        self.energy = e[0]
-        self.forces = (-total).contiguous()
-        return self.forces
+    def _flags(self):
+        """(edge or chunk or pair capacity exceeded, displacement budget used up), agreed between the ranks."""
+        d = self._dist
+        nl = d["nl"]
+        over = (nl.overflow.to(torch.int64) + self.engine.overflow.to(torch.int64)
+                + (nl.num_unique > nl.ucap).to(torch.int64)).clamp(max=1)
+        both = torch.cat((over, d["stale"].to(torch.int64)))
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(both, op=dist.ReduceOp.MAX)
+        v = both.tolist()
+        return bool(v[0]), bool(v[1])
 
-    # ------------------------------------------------------------------ CUDA-graph replay (single GPU)
+    def _reset_flags(self):
+        d = self._dist
+        d["nl"].overflow.zero_()
+        self.engine.overflow.zero_()
+        d["stale"].zero_()
+
+    # ------------------------------------------------------------------ CUDA-graph replay
     def _step_static(self):
-        """One full step on fixed buffers only (no host read-back, no data-dependent host control flow)."""
+        """One full single-GPU step on fixed buffers only (no host read-back, no data-dependent host control flow)."""
         st = self._static
         n = self.pos.shape[0]
         self._kick(True)
@@ -321,13 +480,16 @@ class MolecularDynamics:
         self.forces.copy_(grad).neg_()
         self._kick(False)
 
-    graph_rebuilds = 0
-
     def run(self, steps, check_every=25, margin=1.10, on_step=None):
-        """Advance ``steps`` MD steps.  With a recorded graph the edge-capacity flag is read every
-        ``check_every`` steps; if the neighbour list outgrew the recorded buffers the block of steps is
-        repeated from a snapshot with a larger capacity (steps run after an overflow are invalid).
-        ``on_step`` is called on the host after every step has been launched."""
+        """Advance ``steps`` MD steps.
+
+        One rank with a recorded graph: the capacity flags are read every ``check_every`` steps; when the
+        neighbour list (or a gate chunk) outgrew its buffers the block of steps is repeated from a snapshot with
+        a larger capacity.  Several ranks: steps run in blocks that start with a ghost-list refresh; after a
+        block the ranks agree on the flags, and a block that used up its displacement budget is repeated from
+        the snapshot with half the length.  ``on_step`` is called on the host after every step was launched."""
+        if self.world > 1:
+            return self._run_distributed(steps, on_step)
         if self.graph is None:
             for _ in range(steps):
                 self.step()
@@ -346,22 +508,105 @@ class MolecularDynamics:
                 self.pos.copy_(snap[0])
                 self.vel.copy_(snap[1])
                 self.graph, self._static = None, None
+                if bool(int(self.engine.overflow.item())):
+                    self.engine.chunk_margin += 0.15
+                self.engine.overflow.zero_()
                 self.compute_forces()
                 self.enable_graph(margin=margin)
                 self.graph_rebuilds += 1
                 continue
             done += block
 
-    def enable_graph(self, margin=1.10, warmup=2, spare=1024):
-        """Record the whole MD step (integration, neighbour build, forces) as one CUDA graph.
+    def _run_distributed(self, steps, on_step):
+        if self._dist is None:
+            self.compute_forces()
+        done = 0
+        while done < steps:
+            if self._watch is not None:
+                self._watch.check()          # a missing rank is noticed here, on the host, before the next collectives
+            d = self._dist
+            if d["since_refresh"] >= self.block:
+                if not self.refresh_ghosts():
+                    recorded = self.graph is not None
+                    self.redecompose()
+                    if recorded:
+                        self.enable_graph()
+                d = self._dist
+                d["since_refresh"] = 0
+                if not self._period_stale and self.block < 64:
+                    self.block += max(1, self.block // 4)         # lengthen the period while periods complete
+                self._period_stale = False
+            block = min(self.block - d["since_refresh"], steps - done)
+            snap = (self.pos.clone(), self.vel.clone(), self.forces.clone())
+            for _ in range(block):
+                if self.graph is not None:
+                    self.graph.replay()
+                else:
+                    self._step_distributed()
+                if on_step is not None:
+                    on_step()
+            over, stale = self._flags()
+            if over or stale:
+                self.pos.copy_(snap[0])
+                self.vel.copy_(snap[1])
+                self.forces.copy_(snap[2])
+                self._reset_flags()
+                if over:                    # larger capacities: new buffers, new recording
+                    recorded = self.graph is not None
+                    margin = d["edge_margin"] + 0.15
+                    self.engine.chunk_margin += 0.15
+                    since = d["since_refresh"]
+                    self.graph, self._dist = None, None
+                    self._setup_distributed(edge_margin=margin)
+                    self._dist["since_refresh"] = since
+                    self.forces.copy_(snap[2])
+                    if recorded:
+                        self.enable_graph()
+                    self.graph_rebuilds += 1
+                if stale:
+                    if block == 1 and d["since_refresh"] == 0:
+                        raise RuntimeError("an atom uses up the skin within one step: use a larger skin or a smaller dt")
+                    self.block = max(1, min(self.block, block) // 2)
+                    self._dist["since_refresh"] = self.block      # the repeated block starts with a refresh
+                    self._period_stale = True
+                continue
+            done += block
+            d["since_refresh"] += block
 
-        Edge buffers get a fixed capacity of ``margin`` times the current edge count plus ``spare``; the device-side
-        overflow flag is checked by ``check_overflow``.  Single-GPU, engine path only."""
-        if self.world != 1 or self.engine is None:
-            raise RuntimeError("graph replay covers the single-GPU engine path")
+    def enable_graph(self, margin=1.10, warmup=2, spare=1024):
+        """Record the whole MD step (integration, neighbour build, forces, halo exchanges) as one CUDA graph.
+
+        One rank: edge buffers get a fixed capacity of ``margin`` times the current edge count plus ``spare``; the
+        device-side overflow flag is checked by ``check_overflow``.  Several ranks: the decomposed step already
+        runs on fixed buffers; the recording includes its collectives (collective call)."""
+        if self.engine is None:
+            raise RuntimeError("graph replay covers the engine path")
+        dev = self.device
+        if self.world > 1:
+            if self._dist is None:
+                self.compute_forces()
+            keep = (self.pos.clone(), self.vel.clone(), self.forces.clone(), self._dist["energy"].clone())
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(warmup):
+                    self._step_distributed()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize(dev)
+            # thread-local capture mode: the collective library's watchdog thread keeps polling its events
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self._step_distributed()
+            self.graph = graph
+            self.pos.copy_(keep[0])
+            self.vel.copy_(keep[1])
+            self.forces.copy_(keep[2])
+            self._dist["energy"].copy_(keep[3])
+            self._reset_flags()
+            return self._dist["cap"]
         if self.forces is None:
             self.compute_forces()
-        n, dev = self.pos.shape[0], self.device
+        n = self.pos.shape[0]
         cap = int(self.num_edges * margin) + int(spare)
         pos_ext = torch.zeros(n + 1, 3, dtype=torch.float32, device=dev)
         pos_ext[n] = -1.0e6          # the dummy row sits far outside every cutoff sphere
@@ -386,26 +631,38 @@ class MolecularDynamics:
         self.forces.copy_(keep[2])
         self._static["energy"].copy_(keep[3])
         self._static["nl"].overflow.zero_()
+        self.engine.overflow.zero_()
         self.energy = self._static["energy"][0]
         return cap
 
     def check_overflow(self):
-        """True when a replayed step needed more edges than the recorded capacity (results invalid)."""
+        """True when a replayed step needed more edges than a recorded capacity (results invalid)."""
         if self._static is None:
             return False
         nl = self._static["nl"]
-        return bool(int(nl.overflow.item())) or int(nl.num_unique.item()) > nl.ucap
+        return (bool(int(nl.overflow.item())) or int(nl.num_unique.item()) > nl.ucap
+                or bool(int(self.engine.overflow.item())))
+
+    def check_kernels(self):
+        """Raise when a kernel with bounded waits gave up (its results are then invalid)."""
+        status = _lib.kernel_status()
+        if status != 0:
+            raise RuntimeError(f"a kernel gave up a bounded wait (status {status}); the step's results are invalid")
 
     # ------------------------------------------------------------------ integration
     def _kick(self, drift):
         lib = _lib.load()
+        # a decomposed run keeps coordinates unwrapped between re-decompositions (ghost images are owner + shift)
+        box = self.box_f if self.world == 1 else self.zero_box
         with _lib.on_device(self.device):
             _lib.check(lib.ictc_md_kick(self.pos.shape[0], self.dt, self.forces.data_ptr(), self.inv_mass.data_ptr(),
-                                        self.vel.data_ptr(), self.pos.data_ptr(), self.box_f.data_ptr(), int(drift),
+                                        self.vel.data_ptr(), self.pos.data_ptr(), box.data_ptr(), int(drift),
                                         _lib.stream(self.device)), "ictc_md_kick")
 
     def step(self):
-        """One velocity-Verlet step; neighbours are rebuilt every step."""
+        """One velocity-Verlet step; the edge list is rebuilt from the current coordinates every step."""
+        if self.world > 1:
+            return self._run_distributed(1, None)
         if self.graph is not None:
             self.graph.replay()
             return
@@ -415,8 +672,23 @@ class MolecularDynamics:
         self.compute_forces()
         self._kick(False)
 
+    # ------------------------------------------------------------------ observables
+    def gather(self, owned_rows: torch.Tensor) -> torch.Tensor:
+        """Rows of the owned atoms -> the array of the whole system (row = global id), on every rank."""
+        if self.world == 1:
+            return owned_rows
+        import torch.distributed as dist
+        full = owned_rows.new_zeros(self.num_atoms_total, *owned_rows.shape[1:])
+        full.index_copy_(0, self.gid, owned_rows)
+        dist.all_reduce(full)
+        return full
+
     def kinetic_energy(self):
-        return 0.5 * float((self.masses.double().unsqueeze(1) * self.vel.double() ** 2).sum()) / ACCEL
+        ke = 0.5 * (self.masses.double().unsqueeze(1) * self.vel.double() ** 2).sum().reshape(1) / ACCEL
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(ke)
+        return float(ke)
 
     def temperature(self):
-        return 2.0 * self.kinetic_energy() / ((3 * self.pos.shape[0] - 3) * KB_EV)
+        return 2.0 * self.kinetic_energy() / ((3 * self.num_atoms_total - 3) * KB_EV)

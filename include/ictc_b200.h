@@ -107,6 +107,32 @@ int ictc_tp_graph_adjoint_shared(int spec, int channels, int64_t num_nodes, int6
                                  const int64_t* dst, const int64_t* src_rowptr, const int64_t* src_order,
                                  const float* mask, const float* v, float* dx, float* dsh, float* dg, void* stream);
 
+/* Chunked graph message: the same kernels over a range of owner rows, with the gates (and, for the adjoint, the
+ * gate gradients) of the chunk's edges in buffers that cover the chunk only, so that no [E, np*C] table has to
+ * exist whole.  Follows the reference's bounded-memory gate streaming: gates of an edge tile are produced, consumed
+ * and dropped, and recomputed for the reverse sweep (ictc_o3/ops/streamed_gate_message.py:112-116, 193-221; tile
+ * sizes mace_ictc/interfaces/lammps_hp.py:163-172).
+ * forward: num_rows receiver rows; dst_rowptr points at the chunk's first of num_rows + 1 CSR entries (entries keep
+ *   their global values), out at the chunk's first output row; x, sh, src are the whole arrays.  Gate row of edge e =
+ *   (gate_row ? gate_row[e] : e) - *g_base, clamped to [0, g_capacity); g_base is a DEVICE scalar (normally the
+ *   chunk's first CSR entry itself), NULL = 0 and no clamp.
+ * adjoint: num_rows sender rows; src_rowptr, x and dx point at the chunk's first row; dst, v, sh, dsh are whole.
+ *   g_by_position != 0: gate row = q - *g_base for the edge at position q of the sender CSR order (gate_row is
+ *   ignored).  dg_base (DEVICE scalar) != NULL: the gate gradient of the edge at position q is stored in row
+ *   q - *dg_base of dg when that lies in [0, dg_capacity) and dropped otherwise; NULL: row = edge id as in
+ *   ictc_tp_graph_adjoint.  Capacities make an under-sized buffer safe: results are then incomplete, never out of
+ *   bounds; the caller compares the chunk's edge count with its capacity. */
+int ictc_tp_graph_forward_chunk(int spec, int channels, int64_t num_rows, const float* x, const float* sh,
+                                const float* w, const float* g, const int64_t* gate_row, const int64_t* g_base,
+                                int64_t g_capacity, const int64_t* src, const int64_t* dst_rowptr,
+                                const int64_t* dst_order, const float* mask, float* out, void* stream);
+int ictc_tp_graph_adjoint_chunk(int spec, int channels, int64_t num_rows, const float* x, const float* sh,
+                                const float* w, const float* g, const int64_t* gate_row, int g_by_position,
+                                const int64_t* g_base, int64_t g_capacity, const int64_t* dst,
+                                const int64_t* src_rowptr, const int64_t* src_order, const float* mask, const float* v,
+                                float* dx, float* dsh, float* dg, const int64_t* dg_base, int64_t dg_capacity,
+                                void* stream);
+
 /* ------------------------------------------------------------------ CSR topology
  * Counting sort of edges by an int64 key in [0, num_nodes): rowptr [N+1], order [E] (edge ids,
  * ascending inside a row, i.e. a stable sort), *sorted_flag (device int32) = 1 when the keys were
@@ -216,11 +242,6 @@ int ictc_position_gradient(int64_t num_rows, int64_t num_dst_rows, const int64_t
  * ictc_o3/backends/k100/hip_activation.py:27-38. */
 int ictc_silu_forward(int64_t n, float scale, const float* x, float* y, void* stream);
 int ictc_silu_backward(int64_t n, float scale, const float* x, const float* dy, float* dx, void* stream);
-/* One degree block between the TP output layout [rows][count][m][C] (to_gemm = 1: input) and the
- * GEMM-ready layout [rows][m][count*C]; strides are row strides in floats.  Replaces copy_layout of
- * ictc_o3/backends/k100/hip_message_layout.py:27-34 for the message linear. */
-int ictc_slot_transpose(int64_t rows, int count, int m, int channels, int64_t in_stride, int64_t out_stride,
-                        const float* in, float* out, int to_gemm, void* stream);
 /* Whole-row conversion between the model-native mul_ir layout (every block [C, 2l+1], channel outer) and the
  * kernel-native ir_mul layout (every block [2l+1, C], channel contiguous) in one launch.  A row is a sequence of
  * num_blocks degree blocks; block b holds host_counts[b] path slots of host_ms[b] components each (HOST int
@@ -230,43 +251,11 @@ int ictc_slot_transpose(int64_t rows, int count, int m, int channels, int64_t in
 int ictc_layout_copy(int64_t rows, int channels, int num_blocks, const int* host_counts, const int* host_ms,
                      const float* in, float* out, int to_ir_mul, void* stream);
 
-/* Radial gate MLP num_basis -> 64 -> 64 -> 64 -> num_out (bias-free, SiLU*1.6791767923989418 between
- * layers) on the tensor cores with error-compensated TF32 splitting (fp32-level accuracy).
- * Replaces the per-layer F.linear chain of the interaction block's `fc`
- * (mace_ictc/models/mace/layers.py:825-835; ictc_o3/ops/streamed_gate_message.py:112-116).
- * forward : rb [E,num_basis], w0 [64,num_basis], w1,w2 [64,64], w3_split [num_out,64] pairs -> gates
- *           [E,num_out]; z1,z2,z3 [E,64] receive the hidden pre-activations when not NULL.
- * backward: drb [E,num_basis] = (d gates / d rb)^T dgates, from the stored z1..z3 and the TRANSPOSED
- *           weights w0t [num_basis,64], w1t, w2t [64,64], w3t_split [64,num_out] pairs.
- * The wide last-layer matrix is passed pre-split by ictc_split_tf32 (dst_pairs holds 2*n floats:
- * {tf32(x), tf32(x - tf32(x))} per element), so the kernels stage it with plain asynchronous copies.
- * Limits: 1 <= num_basis <= 8, num_out a multiple of 64, hidden width 64. */
-int ictc_split_tf32(int64_t n, const float* src, float* dst_pairs, void* stream);
-int ictc_radial_mlp_forward(int64_t num_edges, int num_basis, int num_out, const float* rb, const float* w0,
-                            const float* w1, const float* w2, const float* w3_split, float* gates, float* z1,
-                            float* z2, float* z3, void* stream);
-int ictc_radial_mlp_backward(int64_t num_edges, int num_basis, int num_out, const float* dgates, const float* w0t,
-                             const float* w1t, const float* w2t, const float* w3t_split, const float* z1,
-                             const float* z2, const float* z3, float* drb, void* stream);
-
-/* Backward of the gate MLP over a pair table: row u reads dgates[pair_a[u]] + dgates[pair_b[u]]
- * (pair_b[u] < 0: single edge); z1..z3 and drb are indexed by u.  No counterpart in the reference. */
-int ictc_radial_mlp_backward_paired(int64_t num_rows, int num_basis, int num_out, const float* dgates,
-                                    const int64_t* pair_a, const int64_t* pair_b, const float* w0t, const float* w1t,
-                                    const float* w2t, const float* w3t_split, const float* z1, const float* z2,
-                                    const float* z3, float* drb, void* stream);
-
-/* The same MLP with the wide last layer taken out: the three hidden layers only (pre-activations z1..z3 are
- * the output of the forward; the backward starts from da3 = d loss / d silu(z3), [num_edges, 64]).  The last
- * layer then runs as ictc_gate_gemm_forward / ictc_gate_gemm_backward on the tcgen05 tensor cores. */
-int ictc_radial_mlp_hidden_forward(int64_t num_edges, int num_basis, const float* rb, const float* w0, const float* w1,
-                                   const float* w2, float* z1, float* z2, float* z3, void* stream);
-int ictc_radial_mlp_hidden_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0t,
-                                    const float* w1t, const float* w2t, const float* z1, const float* z2,
-                                    const float* z3, float* drb, void* stream);
-
-/* Last layer of the gate MLP (reference: mace_ictc/models/mace/layers.py:825-835, tiled by
- * ictc_o3/ops/streamed_gate_message.py:112-116; input gradient streamed_gate_message.py:224-260) as
+/* Radial gate MLP num_basis -> 64 -> 64 -> 64 -> num_out (bias-free, SiLU * 1.6791767923989418 between layers; the
+ * `fc` stack of the interaction block, mace_ictc/models/mace/layers.py:825-835) runs as two kernels: the hidden
+ * layers as a chain through tensor memory (ictc_mlp_chain_*, below) and the wide last layer as a tcgen05 GEMM.
+ * Last layer (tiled per edge chunk in the reference by ictc_o3/ops/streamed_gate_message.py:112-116; input
+ * gradient streamed_gate_message.py:224-260) as
  * tcgen05.mma TF32 products with a three-term operand split (fp32-level accuracy), accumulators in TMEM.
  * ictc_gate_pack_weights: W3 [num_out, 64] -> `packed` [2 * num_out * 64] floats in the shared-memory operand
  *   layout, 64-unit chunks, transpose = 0 for the forward, 1 for the backward.  num_out % 64 == 0.
@@ -282,6 +271,17 @@ int ictc_gate_gemm_forward(int64_t num_rows, int num_out, const float* z3, const
 int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, const int64_t* pair_a,
                             const int64_t* pair_b, const float* w_packed_t, float* da3, const int64_t* row_limit,
                             void* stream);
+/* The same two products over a window of a longer row list (one edge chunk of the streamed gate evaluation,
+ * reference as above): the launch covers list entries [*row_begin, min(*row_begin + capacity, *row_end)), both
+ * DEVICE scalars (normally two entries of a CSR row-offset array), local row r = entry *row_begin + r.
+ * forward : gates[r, :] = act(z3[row_index[*row_begin + r], :]) @ W3^T   (row_index NULL: z3[*row_begin + r]);
+ * backward: da3[out_index[*row_begin + r], :] = dgates[r, :] @ W3        (out_index NULL: da3[*row_begin + r]). */
+int ictc_gate_gemm_forward_rows(int64_t capacity, int num_out, const float* z3, const int64_t* row_index,
+                                const int64_t* row_begin, const int64_t* row_end, const float* w_packed, float* gates,
+                                int apply_silu, void* stream);
+int ictc_gate_gemm_backward_rows(int64_t capacity, int num_out, const float* dgates, const int64_t* row_begin,
+                                 const int64_t* row_end, const int64_t* out_index, const float* w_packed_t, float* da3,
+                                 void* stream);
 
 /* Per-degree channel linear map on the same tcgen05 kernels (reference: ictc_o3/operators.py:609-628
  * channel_linear; mace_ictc/models/mace/layers.py:21-87 linear_up / message_linear; products.py:817): rows are
@@ -297,7 +297,7 @@ int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, 
 int ictc_channel_linear_tc(int64_t num_rows, int k_chunks, int n_chunks, const float* in, int in_mm, int64_t in_ld,
                            const float* w_packed, float* out, int out_mm, int64_t out_ld, void* stream);
 
-/* Hidden layers of the gate MLP as a chain through tensor memory (same reference as ictc_radial_mlp_forward):
+/* Hidden layers of the gate MLP as a chain through tensor memory (same reference as the last layer above):
  * the two 64 x 64 layers are three-term TF32 tcgen05.mma products with the activations kept in TMEM, the
  * num_basis-wide layer is fp32 FMA.  w1_packed / w2_packed come from ictc_gate_pack_weights(64, W, 0, ...),
  * w1t_packed / w2t_packed from ictc_gate_pack_weights(64, W, 1, ...); w0 is the plain [64, num_basis] matrix.
@@ -313,6 +313,14 @@ int ictc_mlp_chain_forward(int64_t num_edges, int num_basis, const float* rb, co
 int ictc_mlp_chain_backward(int64_t num_edges, int num_basis, const float* da3, const float* w0, const float* w1t_packed,
                             const float* w2t_packed, const float* z1, const float* z2, const float* z3, float* drb,
                             const int64_t* drb_rows, int accumulate, const int64_t* row_limit, void* stream);
+/* ictc_mlp_chain_backward over a pair table: row r starts from da3[pair_a[r]] + da3[pair_b[r]] (pair_b[r] < 0:
+ * the first term only; both NULL: da3[r]), i.e. the two edges of a radial pair add their gradients as they are
+ * read.  No counterpart in the reference (it has no pairing). */
+int ictc_mlp_chain_backward_paired(int64_t num_edges, int num_basis, const float* da3, const int64_t* pair_a,
+                                   const int64_t* pair_b, const float* w0, const float* w1t_packed,
+                                   const float* w2t_packed, const float* z1, const float* z2, const float* z3,
+                                   float* drb, const int64_t* drb_rows, int accumulate, const int64_t* row_limit,
+                                   void* stream);
 
 /* ------------------------------------------------------------------ direction harmonics
  * Component-normalised Cartesian harmonics of unit vectors, degrees 0..lmax (lmax <= 2 here).

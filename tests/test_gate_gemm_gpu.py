@@ -78,48 +78,84 @@ def test_gate_gemm_backward(rows, nout, paired):
     assert err < 1e-5, err
 
 
-def test_hidden_layers_plus_gate_gemm_equal_the_single_kernel_mlp():
+def test_row_windows_match_the_whole_products_bit_for_bit():
+    """Streamed gate evaluation: the forward over a window of an index list and the backward with scattered output
+    rows give exactly the rows of the whole-table products; the window bounds are device scalars and an under-sized
+    buffer truncates instead of overrunning."""
     from ictc_o3 import _lib
     lib = _lib.load()
-    torch.manual_seed(5)
-    edges, nb, nout = 3000, 8, 704
-    rb = (torch.randn(edges, nb) * 0.7).cuda()
-    ws = [torch.randn(64, nb) / nb ** 0.5, torch.randn(64, 64) / 8, torch.randn(64, 64) / 8, torch.randn(nout, 64) / 8]
-    ws = [w.cuda().contiguous() for w in ws]
-    wt = [w.t().contiguous() for w in ws]
-
-    def split(w):
-        out = torch.empty(*w.shape, 2, device="cuda")
-        _lib.check(lib.ictc_split_tf32(w.numel(), w.data_ptr(), out.data_ptr(), None), "split")
-        return out
+    torch.manual_seed(12)
+    pairs, edges, nout = 900, 1700, 704
+    z3 = torch.randn(pairs, 64).cuda()
+    w3 = (torch.randn(nout, 64) / 8).cuda().contiguous()
+    packed, packed_t = _pack(lib, w3, 0), _pack(lib, w3, 1)
     st = torch.cuda.current_stream().cuda_stream
-    gates_a = torch.empty(edges, nout, device="cuda")
-    za = [torch.empty(edges, 64, device="cuda") for _ in range(3)]
-    _lib.check(lib.ictc_radial_mlp_forward(edges, nb, nout, rb.data_ptr(), *[w.data_ptr() for w in ws[:3]],
-                                           split(ws[3]).data_ptr(), gates_a.data_ptr(), *[z.data_ptr() for z in za], st),
+    table = torch.empty(pairs, nout, device="cuda")
+    _lib.check(lib.ictc_gate_gemm_forward(pairs, nout, z3.data_ptr(), packed.data_ptr(), table.data_ptr(), 1, None, st),
                "fwd")
-    gates_b = torch.empty(edges, nout, device="cuda")
-    zb = [torch.empty(edges, 64, device="cuda") for _ in range(3)]
-    _lib.check(lib.ictc_radial_mlp_hidden_forward(edges, nb, rb.data_ptr(), *[w.data_ptr() for w in ws[:3]],
-                                                  *[z.data_ptr() for z in zb], st), "hidden fwd")
-    _lib.check(lib.ictc_gate_gemm_forward(edges, nout, zb[2].data_ptr(), _pack(lib, ws[3], 0).data_ptr(),
-                                          gates_b.data_ptr(), 1, None, st), "gate fwd")
-    for x, y in zip(za, zb):
-        assert torch.equal(x, y)
-    assert float((gates_a - gates_b).abs().max()) < 3e-6 * float(gates_a.abs().max())
-    dg = torch.randn(edges, nout, device="cuda")
-    drb_a = torch.empty(edges, nb, device="cuda")
-    _lib.check(lib.ictc_radial_mlp_backward(edges, nb, nout, dg.data_ptr(), *[w.data_ptr() for w in wt[:3]],
-                                            split(wt[3]).data_ptr(), *[z.data_ptr() for z in za], drb_a.data_ptr(), st),
-               "bwd")
-    da3 = torch.empty(edges, 64, device="cuda")
-    drb_b = torch.empty(edges, nb, device="cuda")
-    _lib.check(lib.ictc_gate_gemm_backward(edges, nout, dg.data_ptr(), None, None, _pack(lib, ws[3], 1).data_ptr(),
-                                           da3.data_ptr(), None, st), "gate bwd")
-    _lib.check(lib.ictc_radial_mlp_hidden_backward(edges, nb, da3.data_ptr(), *[w.data_ptr() for w in wt[:3]],
-                                                   *[z.data_ptr() for z in zb], drb_b.data_ptr(), st), "hidden bwd")
+    index = torch.randint(0, pairs, (edges,)).cuda()
+    bounds = torch.tensor([0, 130, 131, 800, 1700], dtype=torch.int64, device="cuda")      # a CSR-like offset array
+    cap = 700
+    for k in range(4):
+        lo, hi = int(bounds[k]), int(bounds[k + 1])
+        buf = torch.full((cap, nout), float("nan"), device="cuda")
+        _lib.check(lib.ictc_gate_gemm_forward_rows(cap, nout, z3.data_ptr(), index.data_ptr(), bounds.data_ptr() + 8 * k,
+                                                   bounds.data_ptr() + 8 * (k + 1), packed.data_ptr(), buf.data_ptr(), 1,
+                                                   st), "fwd rows")
+        used = min(hi - lo, cap)
+        assert torch.equal(buf[:used], table[index[lo:lo + used]])
+        assert bool(torch.isnan(buf[used:]).all())
+    # identity index (no pairing): row = list entry
+    buf = torch.empty(cap, nout, device="cuda")
+    _lib.check(lib.ictc_gate_gemm_forward_rows(cap, nout, z3.data_ptr(), None, bounds.data_ptr() + 8, bounds.data_ptr() + 24,
+                                               packed.data_ptr(), buf.data_ptr(), 1, st), "fwd rows id")
+    assert torch.equal(buf[:669], table[130:799])
+    # backward: chunk rows in, rows scattered through an index out
+    dg = torch.randn(edges, nout).cuda()
+    whole = torch.empty(edges, 64, device="cuda")
+    _lib.check(lib.ictc_gate_gemm_backward(edges, nout, dg.data_ptr(), None, None, packed_t.data_ptr(), whole.data_ptr(),
+                                           None, st), "bwd")
+    order = torch.randperm(edges).cuda()
+    out = torch.full((edges, 64), float("nan"), device="cuda")
+    for k in range(4):
+        lo, hi = int(bounds[k]), int(bounds[k + 1])
+        if hi - lo > cap:
+            continue
+        chunk = dg[lo:hi].contiguous()
+        _lib.check(lib.ictc_gate_gemm_backward_rows(cap, nout, chunk.data_ptr(), bounds.data_ptr() + 8 * k,
+                                                    bounds.data_ptr() + 8 * (k + 1), order.data_ptr(),
+                                                    packed_t.data_ptr(), out.data_ptr(), st), "bwd rows")
+        assert torch.equal(out[order[lo:hi]], whole[lo:hi])
     assert _status(lib) == 0
-    assert float((drb_a - drb_b).abs().max()) < 5e-6 * float(drb_a.abs().max())
+
+
+def test_chain_backward_adds_the_two_edges_of_a_pair_on_load():
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    torch.manual_seed(13)
+    pairs, edges, nb = 500, 900, 8
+    ws = [w.cuda().contiguous() for w in (torch.randn(64, nb) / nb ** 0.5, torch.randn(64, 64) / 8, torch.randn(64, 64) / 8)]
+    packed = [_pack(lib, ws[1], 0), _pack(lib, ws[2], 0), _pack(lib, ws[1], 1), _pack(lib, ws[2], 1)]
+    st = torch.cuda.current_stream().cuda_stream
+    rb = (torch.randn(pairs, nb) * 0.7).cuda()
+    zs = [torch.empty(pairs, 64, device="cuda") for _ in range(3)]
+    _lib.check(lib.ictc_mlp_chain_forward(pairs, nb, rb.data_ptr(), None, ws[0].data_ptr(), packed[0].data_ptr(),
+                                          packed[1].data_ptr(), *[z.data_ptr() for z in zs], None, st), "fwd")
+    per_edge = torch.randn(edges, 64).cuda()
+    pa = torch.randint(0, edges, (pairs,)).cuda()
+    pb = torch.randint(-1, edges, (pairs,)).cuda()
+    summed = per_edge[pa] + torch.where((pb >= 0).unsqueeze(1), per_edge[pb.clamp(min=0)], torch.zeros((), device="cuda"))
+    want = torch.empty(pairs, nb, device="cuda")
+    _lib.check(lib.ictc_mlp_chain_backward(pairs, nb, summed.data_ptr(), ws[0].data_ptr(), packed[2].data_ptr(),
+                                           packed[3].data_ptr(), *[z.data_ptr() for z in zs], want.data_ptr(), None, 0,
+                                           None, st), "bwd")
+    got = torch.empty(pairs, nb, device="cuda")
+    _lib.check(lib.ictc_mlp_chain_backward_paired(pairs, nb, per_edge.data_ptr(), pa.data_ptr(), pb.data_ptr(),
+                                                  ws[0].data_ptr(), packed[2].data_ptr(), packed[3].data_ptr(),
+                                                  *[z.data_ptr() for z in zs], got.data_ptr(), None, 0, None, st),
+               "bwd paired")
+    assert _status(lib) == 0
+    assert torch.equal(got, want)
     assert lib.ictc_gate_gemm_forward(10, 100, *([None] * 3), 1, None, None) == -1
 
 

@@ -102,6 +102,66 @@ def test_force_engine_matches_autograd_path():
     assert torch.equal(ff, f2)
 
 
+def test_chunked_gate_streaming_is_bitwise_equal_to_whole_tables():
+    """Streaming the gates in chunks of owner rows (no [E, P*C] tensor exists whole; the reverse sweep recomputes
+    each chunk's gates) gives bit-identical energy and forces, eagerly and in a recorded step; a chunk buffer
+    that is too small raises the device flag and nothing is written out of bounds."""
+    from mace_ictc import synthetic as S
+    from mace_ictc.hp import create_model
+    from mace_ictc.md import MolecularDynamics
+    torch.manual_seed(6)
+    pos, box, species = S.jittered_lattice(10, 9, 8, 2.15, 0.1, 21)
+    z = np.array([1, 6, 8])[species]
+    model = create_model(channels=64, lmax=2, cutoff=4.5, avg_num_neighbors=32.0)
+    whole = MolecularDynamics(model, pos, z, box, seed=2)
+    f0 = whole.compute_forces().clone()
+    for rows in (97, 256):
+        for share in (True, False):
+            part = MolecularDynamics(model, pos, z, box, seed=2, chunk_rows=rows, share_gates=share)
+            ref = f0 if share else MolecularDynamics(model, pos, z, box, seed=2, share_gates=False).compute_forces()
+            assert torch.equal(part.compute_forces(), ref), (rows, share)
+            assert int(part.engine.overflow.item()) == 0
+    a = MolecularDynamics(model, pos, z, box, dt=1.0, seed=4)
+    b = MolecularDynamics(model, pos, z, box, dt=1.0, seed=4, chunk_rows=128)
+    a.compute_forces()
+    b.compute_forces()
+    assert float(a.energy) == float(b.energy)
+    a.enable_graph()
+    b.enable_graph()
+    a.run(4)
+    b.run(4)
+    assert torch.equal(a.pos, b.pos) and torch.equal(a.forces, b.forces) and not b.check_overflow()
+    tight = MolecularDynamics(model, pos, z, box, seed=2, chunk_rows=97)
+    tight.engine.chunk_margin = 0.5
+    tight.engine.bucket = lambda rows: int(rows)          # exact sizes: the buffer really is too small
+    tight.compute_forces()
+    assert int(tight.engine.overflow.item()) == 1
+
+
+def test_positions_are_wrapped_and_unknown_species_raise():
+    """Coordinates outside the box are wrapped on entry (same forces as the wrapped system); an atomic number the
+    model has no embedding for raises ValueError on the host."""
+    from mace_ictc import synthetic as S
+    from mace_ictc.hp import create_model
+    from mace_ictc.md import MolecularDynamics
+    torch.manual_seed(8)
+    pos, box, species = S.jittered_lattice(8, 8, 8, 2.15, 0.1, 13)
+    z = np.array([1, 6, 8])[species]
+    model = create_model(channels=64, lmax=2, cutoff=4.5, avg_num_neighbors=32.0)
+    inside = MolecularDynamics(model, pos, z, box, seed=1)
+    rng = np.random.default_rng(3)
+    images = rng.integers(-2, 3, size=pos.shape).astype(np.float64)
+    outside = MolecularDynamics(model, np.asarray(pos, dtype=np.float64) + images * box, z, box, seed=1)
+    assert float(outside.pos.min()) >= 0.0 and bool((outside.pos < outside.box_f).all())
+    f_in, f_out = inside.compute_forces(), outside.compute_forces()
+    assert outside.num_edges == inside.num_edges
+    assert float((f_in - f_out).abs().max()) < 1e-4 * float(f_in.abs().max())
+    bad = z.copy()
+    bad[5] = 7
+    with pytest.raises(ValueError):
+        MolecularDynamics(model, pos, bad, box, seed=1)
+
+
 def test_graph_replay_matches_eager_steps():
     """The recorded MD step (fixed-capacity edge buffers, no host read-back) follows the eager trajectory."""
     from mace_ictc import synthetic as S

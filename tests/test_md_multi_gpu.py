@@ -1,4 +1,6 @@
-"""Domain-decomposed MD force evaluation on 2+ GPUs (NCCL) against the single-GPU evaluation.
+"""Domain-decomposed MD with distributed state on 2+ GPUs (NCCL) against the single-GPU evaluation: forces and
+energy, a trajectory through ghost-list refreshes, the recorded step with its collectives, and a forced
+re-decomposition with atom migration.
 
 Needs at least two visible GPUs; skipped otherwise.  Ranks run as child processes, leave only between
 steps, and NVLS is switched off for the test.
@@ -32,27 +34,50 @@ def _worker(rank, world, port, out):
         single = MolecularDynamics(model, pos, z, box, dt=1.0, seed=3)
         f_ref = single.compute_forces().clone()
         e_ref = float(single.energy)
-        multi = MolecularDynamics(model, pos, z, box, dt=1.0, seed=3, distributed=True)
-        f = multi.compute_forces()
+        multi = MolecularDynamics(model, pos, z, box, dt=1.0, seed=3, distributed=True, skin=1.0, watch_peers=True)
+        assert multi.pos.shape[0] < pos.shape[0]           # a rank holds its own atoms only
+        f = multi.gather(multi.compute_forces())
         scale = float(f_ref.abs().max())
         assert float((f - f_ref).abs().max()) < 2e-5 * scale, float((f - f_ref).abs().max()) / scale
         assert abs(float(multi.energy) - e_ref) < 1e-5 * abs(e_ref)
-        for _ in range(3):
-            single.step()
-            multi.step()
-        assert float((multi.pos - single.pos).abs().max()) < 1e-4
-        # replicated state stays bitwise identical across ranks
-        probe = multi.pos.clone()
-        dist.broadcast(probe, 0)
-        assert torch.equal(probe, multi.pos)
+        # eager trajectory with a short refresh period, so that ghost lists are rewritten on the way
+        multi.block = 2
+        single.run(7)
+        multi.run(7)
+        assert multi.refreshes >= 2
+
+        def wrapped(md):
+            p = md.gather(md.pos)
+            return p - torch.floor(p / md.box_f) * md.box_f
+        d = (wrapped(multi) - single.pos).abs()
+        d = torch.minimum(d, (d - single.box_f).abs())     # an atom sitting on the box face may wrap either way
+        assert float(d.max()) < 1e-4
+        assert float((multi.gather(multi.forces) - single.forces).abs().max()) < 5e-5 * scale
+        # the recorded step (collectives inside the graph) continues the same trajectory
+        multi.enable_graph()
+        single.run(6)
+        multi.run(6)
+        d = (wrapped(multi) - single.pos).abs()
+        d = torch.minimum(d, (d - single.box_f).abs())
+        assert float(d.max()) < 2e-4
+        assert float((multi.gather(multi.forces) - single.forces).abs().max()) < 1e-4 * scale
+        # ownership re-derived from the coordinates: atoms migrate, nothing is lost, forces stay the same
+        before = multi.gather(multi.forces).clone()
+        multi.redecompose()
+        count = torch.tensor([multi.pos.shape[0]], device=f"cuda:{rank}")
+        dist.all_reduce(count)
+        assert int(count) == pos.shape[0]
+        assert torch.equal(multi.gather(multi.forces), before)
+        f2 = multi.gather(multi.compute_forces())
+        assert float((f2 - before).abs().max()) < 2e-5 * scale
         assert _lib.kernel_status() == 0
-        out[rank] = multi.num_edges
+        out[rank] = multi.refreshes
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_decomposed_forces_match_single_gpu(world):
+def test_decomposed_md_matches_single_gpu(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     out = mp.Manager().dict()
