@@ -259,7 +259,7 @@ def parity_against_oracle(dev, side=10):
                          atomic_numbers=(1, 6, 8), avg_num_neighbors=32.0, device=dev)
     model.load_state_dict(weights)
     md = MolecularDynamics(model, pos, z, box, dt=MD_DT, seed=1)
-    f = md.compute_forces().double().cpu()
+    f = md.gather(md.compute_forces()).double().cpu()
     rf = ref["forces"].detach()
     return {"forces_rel": float((f - rf).abs().max() / rf.abs().max()),
             "energy_rel": abs(float(md.energy) - float(ref["energy"])) / abs(float(ref["energy"])),
@@ -275,7 +275,7 @@ def parity_multi_gpu(model, dev, rank, world):
     pos, box, species = S.jittered_lattice(24, 20, 16, MD_SPACING, MD_SIGMA, 17)
     z = np.array([1, 6, 8])[species]
     single = MolecularDynamics(model, pos, z, box, dt=MD_DT, seed=2)
-    f_ref = single.compute_forces().clone()
+    f_ref = single.gather(single.compute_forces())
     e_ref = float(single.energy)
     multi = MolecularDynamics(model, pos, z, box, dt=MD_DT, seed=2, distributed=True)
     f = multi.gather(multi.compute_forces())
@@ -542,7 +542,8 @@ def main_md(args, rank, world, local):
     pos, box, species = S.jittered_lattice(*dims, MD_SPACING, MD_SIGMA, 0)
     z = np.array([1, 6, 8])[species]
     md = MolecularDynamics(model, pos, z, box, dt=MD_DT, temperature=MD_T, seed=1, distributed=world > 1,
-                           skin=args.skin, chunk_rows=chunk_rows or None)
+                           skin=args.skin, chunk_rows=chunk_rows or None, sort_atoms=not args.no_sort,
+                           stream_gates={"auto": None, "yes": True, "no": False}[args.stream_gates])
     del pos, species
     warm = max(3, args.warmup)
     md.compute_forces()
@@ -566,7 +567,6 @@ def main_md(args, rank, world, local):
     if not args.no_graph:
         graph_cap = md.enable_graph()
         md.run(2)
-    torch.cuda.reset_peak_memory_stats()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -581,7 +581,7 @@ def main_md(args, rank, world, local):
     clocks = sampler.stop() if rank == 0 else None
     ms = start.elapsed_time(stop) / args.steps
     calls = calls_per_step * args.steps
-    peak_mem = torch.cuda.max_memory_allocated() / 2 ** 30
+    peak_mem = torch.cuda.max_memory_reserved() / 2 ** 30       # whole run so far: set-up, eager steps, recorded step
     if md.world == 1:
         nl = md._static["nl"] if md._static is not None else None
         edges = int(nl.rowptr[-1].item()) if nl is not None else md.num_edges
@@ -617,6 +617,7 @@ def main_md(args, rank, world, local):
         t2.record()
         barrier()
         e2e = [s2.elapsed_time(t2) / e2e_steps, n * 12, n * 12 + 4 + n * 12, e2e_steps]
+    streamed = bool(chunk_rows) and md.engine._streaming(gate_rows)
     status = _lib.kernel_status()
     if world > 1:
         t = torch.tensor([ms, e2e[0] if e2e else 0.0, float(edges), peak_mem], device=dev, dtype=torch.float64)
@@ -635,7 +636,7 @@ def main_md(args, rank, world, local):
         # layer-1 adjoint, every operand once: reads x, sh, the gates (one row per edge PAIR when the pair table is
         # kept whole, one per edge when streamed in chunks), cotangent rows, indices (edge id, neighbour, gate
         # row); writes dx, dsh and the per-edge gate gradient
-        g_rows = edges if chunk_rows else gate_rows
+        g_rows = edges if streamed else gate_rows
         bwd_b = (4 * (n_local * NX * CHANNELS + edges * NH + g_rows * NP * CHANNELS + per_gpu * NO * CHANNELS)
                  + 24 * edges + 4 * (n_local * NX * CHANNELS + edges * NH + edges * NP * CHANNELS))
         adj_ms = kern_ms.get("graph_adjoint_l1")
@@ -645,7 +646,7 @@ def main_md(args, rank, world, local):
                 "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": dict(workload, edges_total=total_edges, edges_per_atom=total_edges / atoms_total,
                                step_replayed_as_cuda_graph=md.graph is not None, edge_capacity=graph_cap,
-                               gate_chunk_rows=chunk_rows or None, skin=args.skin if world > 1 else None,
+                               atoms_sorted_along_morton_curve=not args.no_sort, gate_chunk_rows=chunk_rows or None, gates_streamed=streamed, skin=args.skin if world > 1 else None,
                                ghost_refreshes=md.refreshes, redecompositions=md.redecompositions,
                                graph_rebuilds_in_timed_region=md.graph_rebuilds - rebuilds0,
                                kernels_ms_from=f"{probe_steps} eager steps before the timed region (per step, "
@@ -847,9 +848,13 @@ def main():
     ap.add_argument("--chunk-rows", type=int, default=-1,
                     help="owner rows per chunk of the streamed gate evaluation (0: whole tables; default: 65536 above "
                          "300,000 atoms per GPU)")
+    ap.add_argument("--stream-gates", default="auto", choices=["auto", "yes", "no"],
+                    help="with chunks: stream the gates too (yes), keep the pair table and stream only the gate "
+                         "gradient (no), or decide by the table's size (auto)")
     ap.add_argument("--skin", type=float, default=1.0, help="extra halo width of the decomposed run (A)")
     ap.add_argument("--train-side", type=int, default=32, help="train workload: lattice sites per edge (atoms = side^3)")
     ap.add_argument("--cpu-md-side", type=int, default=24, help="CPU arm: sites per edge of the periodic sample")
+    ap.add_argument("--no-sort", action="store_true", help="keep the atoms in lattice order (no space-filling-curve sort)")
     ap.add_argument("--no-graph", action="store_true", help="do not record the MD step as a CUDA graph")
     ap.add_argument("--atoms", type=int, default=NUM_ATOMS)
     ap.add_argument("--nodes", type=int, default=SC_NODES)

@@ -36,9 +36,10 @@ class ForceEngine:
     """``chunk_rows``: owner rows per chunk of the streamed gate evaluation (None: one pass over everything).
     ``chunk_margin``: a chunk buffer holds ``chunk_rows x mean degree x chunk_margin`` edges; a chunk with more
     edges than that raises ``overflow`` (device flag) and its surplus edges are dropped, never written out of
-    bounds."""
+    bounds.  ``stream_gates``: see the attribute."""
 
-    def __init__(self, model: MaceIctcModel, chunk_rows: int | None = None, chunk_margin: float = 1.3):
+    def __init__(self, model: MaceIctcModel, chunk_rows: int | None = None, chunk_margin: float = 1.3,
+                 stream_gates: bool | None = None):
         if len(model.interactions) != 2:
             raise ValueError("the force engine covers the two-interaction model")
         if model.channels != 64:
@@ -52,6 +53,11 @@ class ForceEngine:
         self._spec = {0: _lib.tp_spec(0, 2, 2), 1: _lib.tp_spec(2, 2, 2)}
         self.chunk_rows = None if chunk_rows is None else int(chunk_rows)
         self.chunk_margin = float(chunk_margin)
+        # with chunks: True = the gates are streamed too (produced per chunk in the forward sweep, recomputed per chunk
+        # in the reverse sweep: nothing of size [E, P*C] exists); False = the gate table of the edge pairs is kept whole
+        # and only the gate GRADIENT, the largest tensor, lives per chunk (half the GEMM work of streaming);
+        # None = keep the table while both layers' tables take less than 40 % of the device memory
+        self.stream_gates = stream_gates
         self.overflow = torch.zeros(1, dtype=torch.int32, device=self.dev)   # sticky: a chunk buffer was too small
         self.profile = None      # list of (kernel name, start event, end event) when enabled by a benchmark
         self._bounds = {}
@@ -229,6 +235,13 @@ class ForceEngine:
                    "gate_gemm_forward_rows")
         self._done(f"gate_gemm_forward_{L['nout']}", t0)
 
+    def _streaming(self, table_rows):
+        """Are the gates streamed per chunk (True) or is the table of ``table_rows`` rows kept for both sweeps?"""
+        if self.stream_gates is not None:
+            return bool(self.stream_gates)
+        total = torch.cuda.get_device_properties(self.dev).total_memory
+        return 4 * table_rows * sum(L["nout"] for L in self.layers) > 0.4 * total
+
     def _chunks(self, rows, rowptr, edges):
         """[(first row, end row)] of the owner-row chunks and the edge capacity of a chunk buffer; also raises the
         device-side overflow flag when a chunk holds more edges than the buffer."""
@@ -252,7 +265,7 @@ class ForceEngine:
         width = (9 if layer == 0 else 35) * c
         out = self._rows(rows, width)
         chunks, cap = self._chunks(rows, rowptr, e)
-        if cap is None:
+        if cap is None or not self._streaming(z3.shape[0]):
             gates = self._gate_table(z3, L, limit)
             t0 = self._mark()
             _lib.check(lib.ictc_tp_graph_forward_shared(self._spec[layer], c, rows, e, x.data_ptr(), sh.data_ptr(),
@@ -284,20 +297,20 @@ class ForceEngine:
         dsh = self._rows(e, 9)
         da3e = self._rows(e, 64)
         chunks, cap = self._chunks(n_rows, rowptr, e)
-        whole = cap is None
-        if whole:
-            cap = max(e, 1)
-        dg = torch.empty(self.bucket(cap) if whole else cap, nout, dtype=torch.float32, device=self.dev)
-        gbuf = None if whole else torch.empty(cap, nout, dtype=torch.float32, device=self.dev)
+        if cap is None:
+            cap = self.bucket(max(e, 1))
+        table = gates is not None            # the pair table of the forward sweep is still there
+        dg = torch.empty(cap, nout, dtype=torch.float32, device=self.dev)
+        gbuf = None if table else torch.empty(cap, nout, dtype=torch.float32, device=self.dev)
         for s0, s1 in chunks:
             b, en = rowptr.data_ptr() + 8 * s0, rowptr.data_ptr() + 8 * s1
-            if not whole:      # the chunk's gates are recomputed for the reverse sweep
+            if not table:      # the chunk's gates are recomputed for the reverse sweep
                 self._gate_chunk(z3, L, gbuf, grow_by_pos, b, en)
             t0 = self._mark()
             _lib.check(lib.ictc_tp_graph_adjoint_chunk(
                 self._spec[layer], c, s1 - s0, x.data_ptr() + 4 * s0 * xw, sh.data_ptr(), _lib.ptr(L["tpw"]),
-                (gates if whole else gbuf).data_ptr(), _lib.ptr(grow) if whole else None, 0 if whole else 1,
-                None if whole else b, 0 if whole else cap, dst.data_ptr(), b, _lib.ptr(order), None, v.data_ptr(),
+                (gates if table else gbuf).data_ptr(), _lib.ptr(grow) if table else None, 0 if table else 1,
+                None if table else b, 0 if table else cap, dst.data_ptr(), b, _lib.ptr(order), None, v.data_ptr(),
                 None if dx is None else dx.data_ptr() + 4 * s0 * xw, dsh.data_ptr(), dg.data_ptr(), b, cap, self._st()),
                 "tp_graph_adjoint_chunk")
             self._done(f"graph_adjoint_l{layer}", t0)
@@ -353,8 +366,9 @@ class ForceEngine:
             rep = None if pairs is None else pairs[1]               # the MLP kernels gather / scatter the pair rows
             live = pairs[3] if (pairs is not None and len(pairs) > 3) else None
             count = e if pairs is None else int(rep.numel())
-            chunked = self.chunk_rows is not None and self.chunk_rows < max(n_owned, n_local)
-            # gate row of the edge at every position of the sender order (reverse sweep of the chunked mode)
+            chunked = (self.chunk_rows is not None and self.chunk_rows < max(n_owned, n_local)
+                       and self._streaming(count))
+            # gate row of the edge at every position of the sender order (reverse sweep of the streamed mode)
             grow_by_pos = None
             if chunked:
                 grow_by_pos = src_csr[1] if grow is None else grow.index_select(0, src_csr[1])

@@ -190,18 +190,20 @@ class MolecularDynamics:
 
     ``positions`` [N,3], ``atomic_numbers`` [N] and ``velocities`` describe the WHOLE system on every rank; with
     ``distributed=True`` (``torch.distributed`` initialised, one rank per GPU) each rank keeps the atoms of its
-    brick and forgets the rest.  ``pos``, ``vel``, ``forces`` then hold the owned atoms only, ``gid`` their
-    indices in the arrays given here; ``gather`` reassembles a global array.  Positions outside the box are
+    brick and forgets the rest.  ``pos``, ``vel``, ``forces`` hold this rank's atoms only, in an internal order
+    (``sort_atoms``: along a space-filling curve, for cache locality of the gathers); ``gid`` gives their indices
+    in the arrays passed here and ``gather`` reassembles an array in that original order.  Positions outside the box are
     wrapped into it; an atomic number the model does not know raises ``ValueError``.
     ``skin``: extra halo width of the decomposed run (see the module text).  ``chunk_rows``: owner rows per
-    chunk of the force engine's streamed gate evaluation (None: whole tables).  ``use_engine``: None picks the
+    chunk of the force engine's streamed gate evaluation (None: whole tables) and ``stream_gates`` whether the
+    gates themselves are streamed or only their gradient (``ForceEngine.stream_gates``).  ``use_engine``: None picks the
     tape-free force engine for the 64-channel two-interaction model and autograd through the same kernels
     otherwise.  ``watch_peers``: check before every block of steps that all ranks are still there.
     """
 
     def __init__(self, model, positions, atomic_numbers, box, *, dt=1.0, temperature=300.0, seed=0,
                  velocities=None, distributed=False, use_engine=None, share_gates=True, skin=1.0, chunk_rows=None,
-                 watch_peers=False):
+                 stream_gates=None, watch_peers=False, sort_atoms=True):
         self.model = model
         dev = next(model.parameters()).device
         self.device = dev
@@ -247,6 +249,9 @@ class MolecularDynamics:
             mine = torch.nonzero(owner == self.rank).flatten()
         else:
             mine = torch.arange(self.num_atoms_total, device=dev)
+        self.sort_atoms = bool(sort_atoms)
+        if self.sort_atoms:          # rows along a space-filling curve: gathered neighbour rows stay in L2
+            mine = mine.index_select(0, D.morton_order(pos_t.index_select(0, mine)))
         self.gid = mine
         self.pos = pos_t.index_select(0, mine).contiguous()
         self.vel = torch.as_tensor(vel_all).to(dev).index_select(0, mine).contiguous()
@@ -258,7 +263,7 @@ class MolecularDynamics:
             use_engine = model.channels == 64 and len(model.interactions) == 2      # through the same kernels by autograd
         if use_engine:
             from .engine import ForceEngine
-            self.engine = ForceEngine(model, chunk_rows=chunk_rows)
+            self.engine = ForceEngine(model, chunk_rows=chunk_rows, stream_gates=stream_gates)
         else:
             self.engine = None
         self.forces = None
@@ -400,6 +405,8 @@ class MolecularDynamics:
             raise RuntimeError("a brick owns no atoms; use fewer ranks for this box")
         order = torch.argsort(got[:, 9].long())          # ascending global id: a reproducible row order
         got = got.index_select(0, order)
+        if self.sort_atoms:
+            got = got.index_select(0, D.morton_order(got[:, 0:3].float()))
         self.pos = got[:, 0:3].float().contiguous()
         self.vel = got[:, 3:6].float().contiguous()
         forces = got[:, 6:9].float().contiguous()
@@ -582,6 +589,7 @@ class MolecularDynamics:
         if self.engine is None:
             raise RuntimeError("graph replay covers the engine path")
         dev = self.device
+        torch.cuda.empty_cache()        # the eager steps' cached blocks go back before the recording gets its own pool
         if self.world > 1:
             if self._dist is None:
                 self.compute_forces()
@@ -674,13 +682,14 @@ class MolecularDynamics:
 
     # ------------------------------------------------------------------ observables
     def gather(self, owned_rows: torch.Tensor) -> torch.Tensor:
-        """Rows of the owned atoms -> the array of the whole system (row = global id), on every rank."""
-        if self.world == 1:
-            return owned_rows
-        import torch.distributed as dist
+        """Rows of this rank's atoms (``pos``, ``vel``, ``forces`` are stored in an internal, spatially sorted order)
+        -> the array of the whole system in the order of the constructor's arguments (row = ``gid``), on every
+        rank."""
         full = owned_rows.new_zeros(self.num_atoms_total, *owned_rows.shape[1:])
         full.index_copy_(0, self.gid, owned_rows)
-        dist.all_reduce(full)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(full)
         return full
 
     def kinetic_energy(self):

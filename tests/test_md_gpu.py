@@ -56,7 +56,7 @@ def test_md_forces_match_public_api_and_energy_is_conserved():
     z = np.array([1, 6, 8])[species]
     model = create_model(channels=32, lmax=2, cutoff=4.5, avg_num_neighbors=32.0)
     md = MolecularDynamics(model, pos, z, box, dt=0.5, temperature=300.0, seed=7)
-    f = md.compute_forces().clone()
+    f = md.gather(md.compute_forces())
     hs, hd, hsh = S.neighbor_list_host(pos, box, 4.5)
     n = pos.shape[0]
     dev = "cuda"
@@ -115,14 +115,16 @@ def test_chunked_gate_streaming_is_bitwise_equal_to_whole_tables():
     model = create_model(channels=64, lmax=2, cutoff=4.5, avg_num_neighbors=32.0)
     whole = MolecularDynamics(model, pos, z, box, seed=2)
     f0 = whole.compute_forces().clone()
+    unshared = MolecularDynamics(model, pos, z, box, seed=2, share_gates=False).compute_forces().clone()
     for rows in (97, 256):
         for share in (True, False):
-            part = MolecularDynamics(model, pos, z, box, seed=2, chunk_rows=rows, share_gates=share)
-            ref = f0 if share else MolecularDynamics(model, pos, z, box, seed=2, share_gates=False).compute_forces()
-            assert torch.equal(part.compute_forces(), ref), (rows, share)
-            assert int(part.engine.overflow.item()) == 0
+            for stream in (True, False):      # gates and gate gradients per chunk / gate gradients only
+                part = MolecularDynamics(model, pos, z, box, seed=2, chunk_rows=rows, share_gates=share,
+                                         stream_gates=stream)
+                assert torch.equal(part.compute_forces(), f0 if share else unshared), (rows, share, stream)
+                assert int(part.engine.overflow.item()) == 0
     a = MolecularDynamics(model, pos, z, box, dt=1.0, seed=4)
-    b = MolecularDynamics(model, pos, z, box, dt=1.0, seed=4, chunk_rows=128)
+    b = MolecularDynamics(model, pos, z, box, dt=1.0, seed=4, chunk_rows=128, stream_gates=True)
     a.compute_forces()
     b.compute_forces()
     assert float(a.energy) == float(b.energy)
@@ -131,7 +133,7 @@ def test_chunked_gate_streaming_is_bitwise_equal_to_whole_tables():
     a.run(4)
     b.run(4)
     assert torch.equal(a.pos, b.pos) and torch.equal(a.forces, b.forces) and not b.check_overflow()
-    tight = MolecularDynamics(model, pos, z, box, seed=2, chunk_rows=97)
+    tight = MolecularDynamics(model, pos, z, box, seed=2, chunk_rows=97, stream_gates=True)
     tight.engine.chunk_margin = 0.5
     tight.engine.bucket = lambda rows: int(rows)          # exact sizes: the buffer really is too small
     tight.compute_forces()
@@ -153,7 +155,7 @@ def test_positions_are_wrapped_and_unknown_species_raise():
     images = rng.integers(-2, 3, size=pos.shape).astype(np.float64)
     outside = MolecularDynamics(model, np.asarray(pos, dtype=np.float64) + images * box, z, box, seed=1)
     assert float(outside.pos.min()) >= 0.0 and bool((outside.pos < outside.box_f).all())
-    f_in, f_out = inside.compute_forces(), outside.compute_forces()
+    f_in, f_out = inside.gather(inside.compute_forces()), outside.gather(outside.compute_forces())
     assert outside.num_edges == inside.num_edges
     assert float((f_in - f_out).abs().max()) < 1e-4 * float(f_in.abs().max())
     bad = z.copy()
@@ -345,7 +347,8 @@ def test_full_size_step_properties():
     shift = np.array([0.37, -1.21, 2.05])
     moved = np.mod(np.asarray(pos, dtype=np.float64) + shift, box)
     md2 = MolecularDynamics(model, moved, z, box, dt=1.0, seed=1)
-    f2 = md2.compute_forces()
+    f2 = md2.gather(md2.compute_forces())
+    f1 = md.gather(f1)
     # the translated fp32 coordinates round differently (1e-5 A at 100 A): forces agree to that rounding
     assert float((f2 - f1).abs().max()) < 1e-4 * fmax
     assert abs(float(md2.energy) - e1) < 2e-6 * abs(e1)

@@ -32,7 +32,7 @@ def _worker(rank, world, port, out):
         for p in model.parameters():                       # same weights on every rank
             dist.broadcast(p.data, 0)
         single = MolecularDynamics(model, pos, z, box, dt=1.0, seed=3)
-        f_ref = single.compute_forces().clone()
+        f_ref = single.gather(single.compute_forces())
         e_ref = float(single.energy)
         multi = MolecularDynamics(model, pos, z, box, dt=1.0, seed=3, distributed=True, skin=1.0, watch_peers=True)
         assert multi.pos.shape[0] < pos.shape[0]           # a rank holds its own atoms only
@@ -49,18 +49,18 @@ def _worker(rank, world, port, out):
         def wrapped(md):
             p = md.gather(md.pos)
             return p - torch.floor(p / md.box_f) * md.box_f
-        d = (wrapped(multi) - single.pos).abs()
+        d = (wrapped(multi) - single.gather(single.pos)).abs()
         d = torch.minimum(d, (d - single.box_f).abs())     # an atom sitting on the box face may wrap either way
         assert float(d.max()) < 1e-4
-        assert float((multi.gather(multi.forces) - single.forces).abs().max()) < 5e-5 * scale
+        assert float((multi.gather(multi.forces) - single.gather(single.forces)).abs().max()) < 5e-5 * scale
         # the recorded step (collectives inside the graph) continues the same trajectory
         multi.enable_graph()
         single.run(6)
         multi.run(6)
-        d = (wrapped(multi) - single.pos).abs()
+        d = (wrapped(multi) - single.gather(single.pos)).abs()
         d = torch.minimum(d, (d - single.box_f).abs())
         assert float(d.max()) < 2e-4
-        assert float((multi.gather(multi.forces) - single.forces).abs().max()) < 1e-4 * scale
+        assert float((multi.gather(multi.forces) - single.gather(single.forces)).abs().max()) < 1e-4 * scale
         # ownership re-derived from the coordinates: atoms migrate, nothing is lost, forces stay the same
         before = multi.gather(multi.forces).clone()
         multi.redecompose()
