@@ -600,8 +600,14 @@ def main_md(args, rank, world, local):
         host_e = torch.empty(1, pin_memory=True)
 
         def e2e_step():
+            nonlocal host_pos, host_f
+            if host_pos.shape[0] != md.pos.shape[0]:       # the decomposed run re-sized its per-atom arrays
+                host_pos = torch.empty(md.pos.shape[0], 3, pin_memory=True).copy_(md.pos)
+                host_f = torch.empty(md.pos.shape[0], 3, pin_memory=True)
             md.pos.copy_(host_pos, non_blocking=True)
             md.run(1)
+            if host_pos.shape[0] != md.pos.shape[0]:
+                return
             host_f.copy_(md.forces, non_blocking=True)
             host_e.copy_(md.energy.reshape(1), non_blocking=True)
             host_pos.copy_(md.pos, non_blocking=True)

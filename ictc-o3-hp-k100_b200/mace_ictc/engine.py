@@ -336,14 +336,16 @@ class ForceEngine:
     # ---------------------------------------------------------------- the sweep
     @torch.no_grad()
     def energy_and_gradient(self, pos, species, src, dst, shifts, box, n_owned, dst_rowptr, plan=None, n_rows=None,
-                            pairs=None):
+                            pairs=None, row_mask=None):
         """pos [N_local,3] (owned rows first), species [N_local] (index), edges sorted by receiver with all
         receivers < n_owned, dst_rowptr [n_owned+1].  Returns (energy of owned atoms, dE/dpos [N_local,3],
         per-atom energies [n_owned]).  ``n_rows`` < N_local marks trailing rows of ``pos`` as padding: they may
         be named by inert edges (whose sender index is then outside the sender CSR) but carry no features.
         ``pairs`` = (gate_row [E], rep_edge [U], other_edge [U]) evaluates the radial MLP once per edge pair; an
         optional fourth element is a device int64 scalar with the number of pair rows in use when U is a capacity.
-        ``plan`` (an exchange plan of ``mace_ictc.domain``) refreshes the ghost rows between the interactions."""
+        ``plan`` (an exchange plan of ``mace_ictc.domain``) refreshes the ghost rows between the interactions.
+        ``row_mask`` [n_owned] (0 / 1) leaves padding rows among the owned rows out of the energy (and hence of
+        the gradient: a padding row has no edges)."""
         self.refresh()
         m, c, lib, dev = self.model, self.c, self.lib, self.dev
         n_local, e = (pos.shape[0] if n_rows is None else int(n_rows)), int(src.numel())
@@ -408,10 +410,14 @@ class ForceEngine:
             a = self._silu(z)
             e1 = torch.mv(a, self.ro1_w2)
             atomic = e0 + e1
+            if row_mask is not None:
+                atomic = atomic * row_mask
             energy = atomic.sum()
 
             # ================= reverse sweep (dE = 1 for every owned atom) =================
             da = self.ro1_w2.unsqueeze(0).expand(n_owned, -1).contiguous()
+            if row_mask is not None:
+                da = da * row_mask.unsqueeze(1)
             dz = self._silu_bwd(z, da)
             dh2 = torch.mm(dz, self.ro1_w1)                                        # [n, C]
             dy1 = torch.mm(dh2, L1["pl0_t"])
@@ -435,7 +441,7 @@ class ForceEngine:
                 dh1 = dh1.clone()
             full = torch.mm(dh2, L1["sc_bwd"]).view(n_owned, s_count, c)
             dh1[:, :c] += full.gather(1, sp_owned.view(-1, 1, 1).expand(-1, 1, c)).squeeze(1)
-            dh1[:, :c] += self.ro0
+            dh1[:, :c] += self.ro0 if row_mask is None else self.ro0.unsqueeze(0) * row_mask.unsqueeze(1)
             dy0 = self._rows(n_owned, 9 * c)
             self._lin_blocks(L0, "pl_b", n_owned, dh1, dy0)
             dm0, _ = call0.adjoint(m0, L0["bank"], dy0, (True, False))

@@ -35,8 +35,10 @@ def _worker(rank, world, port, out):
         f_ref = single.gather(single.compute_forces())
         e_ref = float(single.energy)
         multi = MolecularDynamics(model, pos, z, box, dt=1.0, seed=3, distributed=True, skin=1.0, watch_peers=True)
-        assert multi.pos.shape[0] < pos.shape[0]           # a rank holds its own atoms only
+        assert multi.num_owned < pos.shape[0]              # a rank holds its own atoms only
         f = multi.gather(multi.compute_forces())
+        assert multi.pos.shape[0] > multi.num_owned        # fixed-capacity arrays: the tail is inert padding
+        assert float(multi.forces[multi.num_owned:].abs().max()) == 0.0
         scale = float(f_ref.abs().max())
         assert float((f - f_ref).abs().max()) < 2e-5 * scale, float((f - f_ref).abs().max()) / scale
         assert abs(float(multi.energy) - e_ref) < 1e-5 * abs(e_ref)
@@ -64,7 +66,7 @@ def _worker(rank, world, port, out):
         # ownership re-derived from the coordinates: atoms migrate, nothing is lost, forces stay the same
         before = multi.gather(multi.forces).clone()
         multi.redecompose()
-        count = torch.tensor([multi.pos.shape[0]], device=f"cuda:{rank}")
+        count = torch.tensor([multi.num_owned], device=f"cuda:{rank}")
         dist.all_reduce(count)
         assert int(count) == pos.shape[0]
         assert torch.equal(multi.gather(multi.forces), before)
