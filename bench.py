@@ -282,6 +282,7 @@ def parity_multi_gpu(model, dev, rank, world):
     out = {"forces_rel": float((f - f_ref).abs().max() / f_ref.abs().max()),
            "energy_rel": abs(float(multi.energy) - e_ref) / abs(e_ref), "atoms": int(pos.shape[0]),
            "ranks": world, "tolerance": 2e-5}
+    multi.close()
     del single, multi
     torch.cuda.empty_cache()
     return out
@@ -567,12 +568,16 @@ def main_md(args, rank, world, local):
     if not args.no_graph:
         graph_cap = md.enable_graph()
         md.run(2)
+    if world > 1:
+        md.redecompose()          # one refresh before the timed region: the first one pays one-time set-up costs
+        md._dist["since_refresh"] = 0
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     rebuilds0 = md.graph_rebuilds
+    md.events.clear()
     start.record()
     md.run(args.steps, on_step=sampler.tick)
     stop.record()
@@ -580,6 +585,7 @@ def main_md(args, rank, world, local):
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = start.elapsed_time(stop) / args.steps
+    run_events = [(k, n, round(t * 1e3, 2)) for k, n, t in md.events]
     calls = calls_per_step * args.steps
     peak_mem = torch.cuda.max_memory_reserved() / 2 ** 30       # whole run so far: set-up, eager steps, recorded step
     if md.world == 1:
@@ -653,7 +659,7 @@ def main_md(args, rank, world, local):
                 "config": dict(workload, edges_total=total_edges, edges_per_atom=total_edges / atoms_total,
                                step_replayed_as_cuda_graph=md.graph is not None, edge_capacity=graph_cap,
                                atoms_sorted_along_morton_curve=not args.no_sort, gate_chunk_rows=chunk_rows or None, gates_streamed=streamed, skin=args.skin if world > 1 else None,
-                               ghost_refreshes=md.refreshes, redecompositions=md.redecompositions,
+                               timed_region_events_ms=run_events, ghost_refreshes=md.refreshes, refresh_seconds_total=md.refresh_seconds, refresh_period_steps=md.block, redecompositions=md.redecompositions,
                                graph_rebuilds_in_timed_region=md.graph_rebuilds - rebuilds0,
                                kernels_ms_from=f"{probe_steps} eager steps before the timed region (per step, "
                                                "chunk launches summed)"),
@@ -670,6 +676,7 @@ def main_md(args, rank, world, local):
                          "d2h_bytes_per_step": e2e[2], "ms_per_step": e2e[0], "steps": e2e[3]} if e2e else None)}
         if par_multi is not None:
             line["parity_multi_gpu"] = par_multi
+    md.close()
     del md
     torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_extras:
@@ -857,7 +864,7 @@ def main():
     ap.add_argument("--stream-gates", default="auto", choices=["auto", "yes", "no"],
                     help="with chunks: stream the gates too (yes), keep the pair table and stream only the gate "
                          "gradient (no), or decide by the table's size (auto)")
-    ap.add_argument("--skin", type=float, default=1.0, help="extra halo width of the decomposed run (A)")
+    ap.add_argument("--skin", type=float, default=2.0, help="extra halo width of the decomposed run (A)")
     ap.add_argument("--train-side", type=int, default=32, help="train workload: lattice sites per edge (atoms = side^3)")
     ap.add_argument("--cpu-md-side", type=int, default=24, help="CPU arm: sites per edge of the periodic sample")
     ap.add_argument("--no-sort", action="store_true", help="keep the atoms in lattice order (no space-filling-curve sort)")

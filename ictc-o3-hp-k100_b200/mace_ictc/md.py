@@ -202,7 +202,7 @@ class MolecularDynamics:
     """
 
     def __init__(self, model, positions, atomic_numbers, box, *, dt=1.0, temperature=300.0, seed=0,
-                 velocities=None, distributed=False, use_engine=None, share_gates=True, skin=1.0, chunk_rows=None,
+                 velocities=None, distributed=False, use_engine=None, share_gates=True, skin=2.0, chunk_rows=None,
                  stream_gates=None, watch_peers=False, sort_atoms=True):
         self.model = model
         dev = next(model.parameters()).device
@@ -278,8 +278,11 @@ class MolecularDynamics:
         self.graph_rebuilds = 0
         self.refreshes = 0           # ghost-list refreshes of the decomposed run
         self.redecompositions = 0
-        self.block = 8               # steps between ghost-list refreshes (adapted by ``run``)
-        self._period_stale = True    # the first period does not lengthen the next one
+        self.block = 8               # steps between refreshes; set at every refresh from the atoms' speeds
+        self._period_stale = False
+        self._stale_block = 8
+        self.refresh_seconds = 0.0   # host time spent in refreshes (they synchronise)
+        self.events = []             # (what, steps, host seconds) of the decomposed run's blocks and refreshes
         self.capture_collectives = True
         self.zero_box = torch.zeros(3, dtype=torch.float32, device=dev)
         self._watch = D.PeerWatch() if (watch_peers and self.world > 1) else None
@@ -325,11 +328,12 @@ class MolecularDynamics:
 
     # ------------------------------------------------------------------ decomposed run: set-up and refresh
     def _pad_rows(self, count, own_cap):
-        """Coordinates of the padding rows [count, own_cap): a far line with 10 A spacing, so that padding rows
-        are neither neighbours of atoms nor of each other."""
+        """Coordinates of the padding rows [count, own_cap): a far line with 16 A spacing on the NEGATIVE side
+        (padding ghost rows sit at +10^6 A, the sender of inert edges at -10^6 A), so that padding rows are
+        neighbours neither of atoms, nor of padding ghosts, nor of each other."""
         k = torch.arange(own_cap - count, dtype=torch.float32, device=self.device)
-        pad = torch.full((own_cap - count, 3), D.PAD_SHIFT, dtype=torch.float32, device=self.device)
-        pad[:, 0] += 10.0 * k
+        pad = torch.full((own_cap - count, 3), -3.0 * D.PAD_SHIFT, dtype=torch.float32, device=self.device)
+        pad[:, 0] -= 16.0 * k
         return pad
 
     def _store_owned(self, pos, vel, forces, gid, z):
@@ -454,6 +458,17 @@ class MolecularDynamics:
         d["stale"].zero_()
         self.refreshes += 1
         return True
+
+    def _steps_within_budget(self):
+        """How many steps the fastest atom (of any rank) needs to use up 70 % of the displacement budget skin/2 at
+        its present speed: the length of the next period between refreshes (collective)."""
+        n = self.num_owned
+        vmax = self.vel[:n].square().sum(1).max().sqrt().reshape(1)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(vmax, op=dist.ReduceOp.MAX)
+        speed = max(float(vmax.item()), 1e-12)
+        return int(max(1, min(64, 0.7 * 0.5 * self.skin / (speed * self.dt))))
 
     def redecompose(self):
         """Refresh, and set all buffers up again (a recorded graph is dropped) when a capacity did not fit."""
@@ -581,16 +596,24 @@ class MolecularDynamics:
                 self._watch.check()          # a missing rank is noticed here, on the host, before the next collectives
             d = self._dist
             if d["since_refresh"] >= self.block:
+                import time
+                t0 = time.perf_counter()
                 recorded = self.graph is not None
                 if not self.redecompose() and recorded:
                     self.enable_graph()
+                torch.cuda.synchronize(self.device)
+                self.refresh_seconds += time.perf_counter() - t0
+                self.events.append(("refresh", 0, time.perf_counter() - t0))
                 d = self._dist
                 d["since_refresh"] = 0
-                if not self._period_stale and self.block < 64:
-                    self.block += max(1, self.block // 4)         # lengthen the period while periods complete
+                ahead = self._steps_within_budget()
+                # after a period that ran out of budget, at most half its length; otherwise what the speeds allow
+                self.block = min(ahead, max(1, self._stale_block // 2)) if self._period_stale else ahead
                 self._period_stale = False
             block = min(self.block - d["since_refresh"], steps - done)
             snap = (self.pos.clone(), self.vel.clone(), self.forces.clone())
+            import time
+            t_block = time.perf_counter()
             for _ in range(block):
                 if self.graph is not None:
                     self.graph.replay()
@@ -599,6 +622,7 @@ class MolecularDynamics:
                 if on_step is not None:
                     on_step()
             over, stale = self._flags()
+            self.events.append(("repeat" if (over or stale) else "block", block, time.perf_counter() - t_block))
             if over or stale:
                 self.pos.copy_(snap[0])
                 self.vel.copy_(snap[1])
@@ -620,8 +644,8 @@ class MolecularDynamics:
                 if stale:
                     if block == 1 and d["since_refresh"] == 0:
                         raise RuntimeError("an atom uses up the skin within one step: use a larger skin or a smaller dt")
-                    self.block = max(1, min(self.block, block) // 2)
-                    self._dist["since_refresh"] = self.block      # the repeated block starts with a refresh
+                    self._stale_block = max(1, min(self.block, d["since_refresh"] + block))
+                    self.block = 0                                # the repeated block starts with a refresh
                     self._period_stale = True
                 continue
             done += block
@@ -703,6 +727,17 @@ class MolecularDynamics:
         status = _lib.kernel_status()
         if status != 0:
             raise RuntimeError(f"a kernel gave up a bounded wait (status {status}); the step's results are invalid")
+
+    def close(self):
+        """Release the recorded graph.  A decomposed run MUST call this before the process group is destroyed: a
+        live CUDA graph that holds captured collectives keeps the communicator busy and its tear-down waits
+        forever."""
+        if self.graph is not None:
+            torch.cuda.synchronize(self.device)
+            self.graph = None
+            import gc
+            gc.collect()
+            torch.cuda.synchronize(self.device)
 
     # ------------------------------------------------------------------ integration
     def _kick(self, drift):

@@ -34,7 +34,7 @@ def _worker(rank, world, port, out):
         single = MolecularDynamics(model, pos, z, box, dt=1.0, seed=3)
         f_ref = single.gather(single.compute_forces())
         e_ref = float(single.energy)
-        multi = MolecularDynamics(model, pos, z, box, dt=1.0, seed=3, distributed=True, skin=1.0, watch_peers=True)
+        multi = MolecularDynamics(model, pos, z, box, dt=1.0, seed=3, distributed=True, skin=0.6, watch_peers=True)
         assert multi.num_owned < pos.shape[0]              # a rank holds its own atoms only
         f = multi.gather(multi.compute_forces())
         assert multi.pos.shape[0] > multi.num_owned        # fixed-capacity arrays: the tail is inert padding
@@ -42,7 +42,8 @@ def _worker(rank, world, port, out):
         scale = float(f_ref.abs().max())
         assert float((f - f_ref).abs().max()) < 2e-5 * scale, float((f - f_ref).abs().max()) / scale
         assert abs(float(multi.energy) - e_ref) < 1e-5 * abs(e_ref)
-        # eager trajectory with a short refresh period, so that ghost lists are rewritten on the way
+        # eager trajectory; the thin skin makes the refresh period short, so atoms migrate and ghost lists are
+        # rewritten on the way
         multi.block = 2
         single.run(7)
         multi.run(7)
@@ -74,6 +75,7 @@ def _worker(rank, world, port, out):
         assert float((f2 - before).abs().max()) < 2e-5 * scale
         assert _lib.kernel_status() == 0
         out[rank] = multi.refreshes
+        multi.close()                   # a live graph with captured collectives would block the tear-down
     finally:
         dist.destroy_process_group()
 
