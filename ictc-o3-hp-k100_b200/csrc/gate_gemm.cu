@@ -13,8 +13,7 @@
 //   warp 0      streams pre-packed 64-unit weight chunks (32 KB: big and small part) into a 2-stage ring
 //               with cp.async.bulk, completing on mbarriers;
 //   warp 1      allocates TMEM and issues the MMAs (one thread), committing to mbarriers;
-//   warps 2-9   epilogue (forward: two groups taking alternate chunks; backward: warps 2-5 only, warps 6-9 load
-//               the A rows into a shared-memory ring with cp.async.bulk or prefetch them into L2):
+//   warps 2-9   epilogue (forward: two groups taking alternate chunks; backward: warps 2-5 only):
 //               tcgen05.ld (thread = row), then coalesced row stores;
 //   warps 10-17 A-operand producers: global rows -> (activation | pair sum) -> split -> tcgen05.st into TMEM
 //               (the A operand is read from TMEM: lane = row, column = k; no shared memory for A at all).
@@ -69,14 +68,8 @@ __device__ __forceinline__ int64_t row_offset(int64_t g, int mm, int64_t ld) {
 constexpr int kWStages = 4;      // weight ring
 constexpr int kAStagesBwd = 3;   // TMEM A ring of the backward kernel
 
-constexpr int kSStages = 3;                          // shared-memory staging ring of the backward kernel's A rows
-constexpr int kSPitch = 272;                         // bytes per staged row (256 + 16: conflict-free 16-byte reads)
-constexpr int kSStageBytes = kRows * kSPitch;
-constexpr int kWStagesStaged = 3;                    // weight ring of the staged backward kernel
-
 struct Barriers {
   unsigned long long w_full[kWStages], w_empty[kWStages], a_full[4], a_empty[4], d_full[4], d_empty[4];
-  unsigned long long s_full[kSStages], s_empty[kSStages];
   unsigned tmem_base;
   volatile int failed;   // polled inside wait loops by other warps: every read must go to shared memory
   volatile long long progress;   // backward: chunks finished by the first producer warp (read by the prefetch warps)
@@ -275,25 +268,14 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_forward_kernel(Args a) 
 }
 
 // ------------------------------------------------------------------------------------------------
-// backward.  TMEM: two accumulators [128 x 64] that alternate between tiles | A ring of three stages (big + small,
-// 128 columns each); K runs over the nout / 64 chunks.  Two ways of bringing the A rows in:
-//   STAGED (plain rows): warps 6-9 copy the 128 rows of a chunk into a shared-memory ring with one cp.async.bulk per
-//     row (thread = row), three chunks in flight per SM, completing on mbarriers; the producer warps read their
-//     row from shared memory, split it and write it to TMEM.  The loads of the next chunks run while a chunk is
-//     converted and multiplied, which the register path cannot do within its register budget.
-//     Shared memory: W ring (3 x 32 KB) | row staging (3 x 34 KB) | barriers.
-//   register path (pair sums dG[a] + dG[b]): producers load both rows straight into registers; warps 6-9 prefetch
-//     the rows into L2 two chunks ahead.  Shared memory: W ring (4 x 32 KB) | barriers.
+// backward.  Shared memory: W ring (4 x 32 KB) | barriers.  TMEM: two accumulators [128 x 64] that alternate
+// between tiles | A ring of three stages (big + small, 128 columns each); K runs over the nout / 64 chunks.
 constexpr int kBwdSmem = kWStages * kWStageBytes + 256;
-constexpr int kBwdSmemStaged = kWStagesStaged * kWStageBytes + kSStages * kSStageBytes + 256;
 
-template <bool STAGED>
 __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a) {
   extern __shared__ __align__(128) unsigned char gg_smem[];
-  constexpr int WS = STAGED ? kWStagesStaged : kWStages;
   unsigned char* w_buf = gg_smem;
-  unsigned char* s_buf = w_buf + WS * kWStageBytes;
-  Barriers* bar = reinterpret_cast<Barriers*>(s_buf + (STAGED ? kSStages * kSStageBytes : 0));
+  Barriers* bar = reinterpret_cast<Barriers*>(w_buf + kWStages * kWStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = a.nout / kChunk;
   const int64_t base = a.begin ? ldg(a.begin) : 0;
@@ -303,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
   const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < WS; ++i) {
+    for (int i = 0; i < kWStages; ++i) {
       mbar_init(saddr(&bar->w_full[i]), 1);
       mbar_init(saddr(&bar->w_empty[i]), 1);
     }
@@ -314,10 +296,6 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
     for (int i = 0; i < 2; ++i) {
       mbar_init(saddr(&bar->d_full[i]), 1);
       mbar_init(saddr(&bar->d_empty[i]), 128);
-    }
-    for (int i = 0; i < kSStages; ++i) {
-      mbar_init(saddr(&bar->s_full[i]), kRows);          // every loader thread announces its own bytes
-      mbar_init(saddr(&bar->s_empty[i]), kProducerWarps * 32);
     }
     bar->failed = 0;
     bar->progress = 0;
@@ -340,8 +318,8 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
       int64_t it = 0;
       for (int64_t t = 0; t < my_tiles && !bar->failed; ++t) {
         for (int c = 0; c < chunks; ++c, ++it) {
-          const int s = int(it % WS);
-          if (!mbar_wait(saddr(&bar->w_empty[s]), unsigned((it / WS) & 1) ^ 1u)) { give_up(bar, a.status, 31); break; }
+          const int s = int(it % kWStages);
+          if (!mbar_wait(saddr(&bar->w_empty[s]), unsigned((it / kWStages) & 1) ^ 1u)) { give_up(bar, a.status, 31); break; }
           mbar_expect_tx(saddr(&bar->w_full[s]), kWStageBytes);
           bulk_g2s(saddr(w_buf + s * kWStageBytes), a.w + int64_t(c) * (kWStageBytes / 4), kWStageBytes,
                    saddr(&bar->w_full[s]));
@@ -356,8 +334,8 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
         if (!mbar_wait(saddr(&bar->d_empty[d]), unsigned((t >> 1) & 1) ^ 1u)) { give_up(bar, a.status, 32); break; }
         bool ok = true;
         for (int c = 0; c < chunks; ++c, ++it) {
-          const int s = int(it % WS), sa = int(it % kAStagesBwd);
-          if (!mbar_wait(saddr(&bar->w_full[s]), unsigned((it / WS) & 1)) ||
+          const int s = int(it % kWStages), sa = int(it % kAStagesBwd);
+          if (!mbar_wait(saddr(&bar->w_full[s]), unsigned((it / kWStages) & 1)) ||
               !mbar_wait(saddr(&bar->a_full[sa]), unsigned((it / kAStagesBwd) & 1))) {
             give_up(bar, a.status, 33);
             ok = false;
@@ -398,94 +376,64 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
       }
     }
   } else if (warp < kProducerWarp0) {
+    // ---- warps 6-9: L2 prefetch of the rows a few chunks ahead of the producers, across tile boundaries
+    // (thread = row).  They follow the producers through a progress counter and never wait when they are behind.
     const int q = warp & 3;
     const int row = q * 32 + lane;
-    if (STAGED) {
-      // ---- warps 6-9: row loader (thread = row): one 256-byte bulk copy per row and chunk into the staging ring
-      const int64_t cstep = int64_t(a.in_cs) * kChunk;
-      int64_t it = 0;
+    constexpr int kAhead = 2;
+    const int64_t cstep = int64_t(a.in_cs) * kChunk;
+    int64_t pf_tile = 0;
+    int pf_chunk = 0;
+    const float* pa = nullptr;
+    const float* pb = nullptr;
+    auto enter_tile = [&]() {
+      pa = pb = nullptr;
+      if (pf_tile >= my_tiles) return;
+      const int64_t g = (blockIdx.x + pf_tile * gridDim.x) * kRows + row;
+      if (g >= nrows) return;
+      const int64_t ra = a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g;
+      const int64_t rb = a.pair_b ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
+      pa = a.in + row_offset(ra, a.in_mm, a.in_ld);
+      if (rb >= 0) pb = a.in + row_offset(rb, a.in_mm, a.in_ld);
+    };
+    auto advance = [&]() {
+      if (pf_tile >= my_tiles) return;
+      if (pa) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pa + pf_chunk * cstep));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pa + pf_chunk * cstep + 32));
+      }
+      if (pb) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pb + pf_chunk * cstep));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pb + pf_chunk * cstep + 32));
+      }
+      if (++pf_chunk == chunks) {
+        pf_chunk = 0;
+        ++pf_tile;
+        enter_tile();
+      }
+    };
+    enter_tile();
+    for (int k = 0; k < kAhead; ++k) advance();
+    const int64_t total = my_tiles * chunks;
+    for (int64_t it = 0; it < total; ++it) {
+      advance();
+      const long long start = clock64();
       bool ok = true;
-      for (int64_t t = 0; t < my_tiles && ok; ++t) {
-        const int64_t row0 = (blockIdx.x + t * gridDim.x) * kRows;
-        const int64_t g = row0 + row;
-        const float* src = a.in + row_offset(g < nrows ? g : row0, a.in_mm, a.in_ld);
-        for (int c = 0; c < chunks; ++c, ++it) {
-          const int ss = int(it % kSStages);
-          if (bar->failed || !mbar_wait(saddr(&bar->s_empty[ss]), unsigned((it / kSStages) & 1) ^ 1u)) {
-            give_up(bar, a.status, 36);
-            ok = false;
-            break;
-          }
-          const unsigned full = saddr(&bar->s_full[ss]);
-          mbar_expect_tx(full, g < nrows ? 256u : 0u);       // arrival + this thread's byte count, before its copy
-          if (g < nrows) bulk_g2s(saddr(s_buf + ss * kSStageBytes + row * kSPitch), src + c * cstep, 256u, full);
-        }
+      while (bar->progress <= it && !bar->failed) {
+        if (clock64() - start > kWaitCycles) { ok = false; break; }
+        __nanosleep(64);
       }
-      if (!ok && row == 0) {
-        // leave no copy in flight behind: every stage this warp group filled either completes or times out
-        for (int k = 0; k < kSStages && it - 1 - k >= 0; ++k) {
-          const int64_t j = it - 1 - k;
-          mbar_wait(saddr(&bar->s_full[int(j % kSStages)]), unsigned((j / kSStages) & 1));
-        }
-      }
-    } else {
-      // ---- warps 6-9: L2 prefetch of the rows a few chunks ahead of the producers, across tile boundaries
-      // (thread = row).  They follow the producers through a progress counter and never wait when they are behind.
-      constexpr int kAhead = 2;
-      const int64_t cstep = int64_t(a.in_cs) * kChunk;
-      int64_t pf_tile = 0;
-      int pf_chunk = 0;
-      const float* pa = nullptr;
-      const float* pb = nullptr;
-      auto enter_tile = [&]() {
-        pa = pb = nullptr;
-        if (pf_tile >= my_tiles) return;
-        const int64_t g = (blockIdx.x + pf_tile * gridDim.x) * kRows + row;
-        if (g >= nrows) return;
-        const int64_t ra = a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g;
-        const int64_t rb = a.pair_b ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
-        pa = a.in + row_offset(ra, a.in_mm, a.in_ld);
-        if (rb >= 0) pb = a.in + row_offset(rb, a.in_mm, a.in_ld);
-      };
-      auto advance = [&]() {
-        if (pf_tile >= my_tiles) return;
-        if (pa) {
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(pa + pf_chunk * cstep));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(pa + pf_chunk * cstep + 32));
-        }
-        if (pb) {
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(pb + pf_chunk * cstep));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(pb + pf_chunk * cstep + 32));
-        }
-        if (++pf_chunk == chunks) {
-          pf_chunk = 0;
-          ++pf_tile;
-          enter_tile();
-        }
-      };
-      enter_tile();
-      for (int k = 0; k < kAhead; ++k) advance();
-      const int64_t total = my_tiles * chunks;
-      for (int64_t it = 0; it < total; ++it) {
-        advance();
-        const long long start = clock64();
-        bool ok = true;
-        while (bar->progress <= it && !bar->failed) {
-          if (clock64() - start > kWaitCycles) { ok = false; break; }
-          __nanosleep(64);
-        }
-        if (!ok || bar->failed) break;
-      }
+      if (!ok || bar->failed) break;
     }
   } else {
-    // ---- A producers: thread = (row, half of a 64-column chunk); row (or dG[a] + dG[b]) -> split -> TMEM ring
+    // ---- A producers: thread = (row, half of a 64-column chunk); (dG[a] + dG[b]) -> split -> TMEM ring
     const int q = warp & 3, half = (warp - kProducerWarp0) >> 2;
     const int row = q * 32 + lane;
     int64_t it = 0;
     for (int64_t t = 0; t < my_tiles; ++t) {
       const int64_t g = (blockIdx.x + t * gridDim.x) * kRows + row;
-      const int64_t ra = g < nrows ? ((!STAGED && a.pair_a) ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g) : -1;
-      const int64_t rb = (!STAGED && g < nrows && a.pair_b) ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
+      const int64_t ra = g < nrows ? (a.pair_a ? __ldg(reinterpret_cast<const long long*>(a.pair_a + g)) : g) : -1;
+      const int64_t rb = (g < nrows && a.pair_b) ? __ldg(reinterpret_cast<const long long*>(a.pair_b + g)) : -1;
       const float* pa = a.in + row_offset(ra >= 0 ? ra : 0, a.in_mm, a.in_ld) + half * 32;
       const float* pb = a.in + row_offset(rb >= 0 ? rb : 0, a.in_mm, a.in_ld) + half * 32;
       const int64_t cstep = int64_t(a.in_cs) * kChunk;
@@ -493,40 +441,19 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
       for (int c = 0; c < chunks; ++c, ++it) {
         const int sa = int(it % kAStagesBwd);
         float x[32];
-        if (STAGED) {
-          const int ss = int(it % kSStages);
-          if (bar->failed || !mbar_wait(saddr(&bar->s_full[ss]), unsigned((it / kSStages) & 1))) {
-            give_up(bar, a.status, 37);
-            ok = false;
-            break;
-          }
-          if (ra >= 0) {
-            const float4* sp = reinterpret_cast<const float4*>(s_buf + ss * kSStageBytes + row * kSPitch + half * 128);
+        if (ra >= 0) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 v = sp[j];
-              x[4 * j] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] = 0.f;
-          }
-          mbar_arrive(saddr(&bar->s_empty[ss]));
+          for (int j = 0; j < 4; ++j) ldg256(pa + c * cstep + j * 8, x + j * 8);
         } else {
-          if (ra >= 0) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) ldg256(pa + c * cstep + j * 8, x + j * 8);
-          } else {
+          for (int i = 0; i < 32; ++i) x[i] = 0.f;
+        }
+        if (rb >= 0) {
+          float y[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] = 0.f;
-          }
-          if (rb >= 0) {
-            float y[32];
+          for (int j = 0; j < 4; ++j) ldg256(pb + c * cstep + j * 8, y + j * 8);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) ldg256(pb + c * cstep + j * 8, y + j * 8);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] += y[i];
-          }
+          for (int i = 0; i < 32; ++i) x[i] += y[i];
         }
         if (bar->failed || !mbar_wait(saddr(&bar->a_empty[sa]), unsigned((it / kAStagesBwd) & 1) ^ 1u)) {
           give_up(bar, a.status, 35);
@@ -538,7 +465,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
         store_split_tmem(t_big, t_big + kK, x);
         tc_fence_before();
         mbar_arrive(saddr(&bar->a_full[sa]));
-        if (!STAGED && warp == kProducerWarp0 && lane == 0) bar->progress = it + 1;
+        if (warp == kProducerWarp0 && lane == 0) bar->progress = it + 1;
       }
       if (!ok) break;
     }
@@ -550,29 +477,6 @@ __global__ void __launch_bounds__(kThreads, 1) gate_gemm_backward_kernel(Args a)
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
   }
-}
-
-// Launches the backward kernel: staged row loads for plain rows, the register path when rows are pair sums.
-static int launch_backward(const Args& a, int64_t grid_rows, cudaStream_t st) {
-  const bool staged = !a.pair_a && !a.pair_b;
-  if (staged) {
-    static const cudaError_t attr = cudaFuncSetAttribute(gate_gemm_backward_kernel<true>,
-                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmemStaged);
-    if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
-  } else {
-    static const cudaError_t attr = cudaFuncSetAttribute(gate_gemm_backward_kernel<false>,
-                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
-    if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
-  }
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t tiles = (grid_rows + kRows - 1) / kRows;
-  const int grid = int(tiles < sms ? tiles : sms);
-  if (staged)
-    gate_gemm_backward_kernel<true><<<grid, kThreads, kBwdSmemStaged, st>>>(a);
-  else
-    gate_gemm_backward_kernel<false><<<grid, kThreads, kBwdSmem, st>>>(a);
-  return ICTC_OK;
 }
 
 // Packs W3 [nout, 64] into 64-unit chunks in the shared-memory operand layout, big part then small part.
@@ -649,11 +553,14 @@ int ictc_gate_gemm_backward(int64_t num_rows, int num_out, const float* dgates, 
     set_error("gate gemm backward: buffers must be 32-byte aligned");
     return ICTC_ERR_BAD_ARG;
   }
+  static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_backward_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kBwdSmem);
+  if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   gg::Args a{};
   a.in = dgates; a.w = w_packed_t; a.out = da3; a.pair_a = pair_a; a.pair_b = pair_b; a.rows = num_rows; a.limit = row_limit; a.nout = num_out;
   a.in_mm = a.out_mm = a.in_cs = a.out_cs = 1; a.in_ld = num_out; a.out_ld = gg::kK;
   a.status = kernel_status_word();
-  if (int rc = gg::launch_backward(a, num_rows, (cudaStream_t)stream)) return rc;
+  gg::gate_gemm_backward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kBwdSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("gate_gemm_backward");
 }
 
@@ -690,12 +597,15 @@ int ictc_gate_gemm_backward_rows(int64_t capacity, int num_out, const float* dga
     set_error("gate gemm backward rows: buffers must be 32-byte aligned");
     return ICTC_ERR_BAD_ARG;
   }
+  static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_backward_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kBwdSmem);
+  if (attr != cudaSuccess) { set_error("gate gemm smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
   gg::Args a{};
   a.in = dgates; a.w = w_packed_t; a.out = da3; a.rows = capacity; a.limit = row_end; a.begin = row_begin; a.out_index = out_index;
   a.nout = num_out;
   a.in_mm = a.out_mm = a.in_cs = a.out_cs = 1; a.in_ld = num_out; a.out_ld = gg::kK;
   a.status = kernel_status_word();
-  if (int rc = gg::launch_backward(a, capacity, (cudaStream_t)stream)) return rc;
+  gg::gate_gemm_backward_kernel<<<gg::grid_size(capacity), gg::kThreads, gg::kBwdSmem, (cudaStream_t)stream>>>(a);
   return finish_launch("gate_gemm_backward_rows");
 }
 
@@ -726,8 +636,11 @@ int ictc_channel_linear_tc(int64_t num_rows, int k_chunks, int n_chunks, const f
     a.nout = n_chunks * gg::kChunk;
     gg::gate_gemm_forward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kFwdSmem, (cudaStream_t)stream>>>(a);
   } else {
+    static const cudaError_t attr = cudaFuncSetAttribute(gg::gate_gemm_backward_kernel,
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, gg::kBwdSmem);
+    if (attr != cudaSuccess) { set_error("channel linear smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
     a.nout = k_chunks * gg::kChunk;
-    if (int rc = gg::launch_backward(a, num_rows, (cudaStream_t)stream)) return rc;
+    gg::gate_gemm_backward_kernel<<<gg::grid_size(num_rows), gg::kThreads, gg::kBwdSmem, (cudaStream_t)stream>>>(a);
   }
   return finish_launch("channel_linear_tc");
 }
