@@ -70,6 +70,8 @@ __global__ void scan_add_kernel(int64_t* data, int64_t n, const int64_t* sums) {
   if (i < n && tile > 0) data[i] += sums[tile - 1];
 }
 
+__global__ void csr_zero_kernel(int64_t* word) { *word = 0; }
+
 __global__ void csr_cursor_kernel(const int64_t* rowptr, int64_t N, int64_t* cursor) {
   const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < N) cursor[i] = rowptr[i];
@@ -93,20 +95,23 @@ __global__ void csr_fill_kernel(const int64_t* __restrict__ keys, int64_t E, int
 // ascending order (a stable sort of the whole list) by one of two kernels:
 //   rows of at most kLongRow edges: one warp per row ranks every id against the row (quadratic, but the row is
 //     short and stays in L1);
-//   longer rows: one block per row sorts the ids in place with a bitonic network whose every compare-exchange
+//   longer rows (listed by the first kernel): one block per row sorts the ids in place with a bitonic network whose every compare-exchange
 //     keeps the minimum at the lower index, so positions beyond the row's end act as +infinity and are never
 //     touched; O(L log^2 L) instead of O(L^2), which bounds the run time of degenerate inputs (few rows, a
 //     million edges).
 constexpr int64_t kLongRow = 2048;
 
 __global__ void csr_rank_kernel(const int64_t* __restrict__ rowptr, int64_t N, const int64_t* __restrict__ slots,
-                                int64_t* order, const int32_t* flag) {
+                                int64_t* order, const int32_t* flag, int64_t* long_rows, int64_t* long_count) {
   if (*flag == 1) return;
   const int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) / 32;
   if (row >= N) return;
   const int lane = threadIdx.x & 31;
   const int64_t begin = rowptr[row], end = rowptr[row + 1];
-  if (end - begin > kLongRow) return;          // csr_sort_long_rows_kernel handles it
+  if (end - begin > kLongRow) {                // handed to csr_sort_long_rows_kernel through a list
+    if (lane == 0) long_rows[atomicAdd(reinterpret_cast<unsigned long long*>(long_count), 1ULL)] = row;
+    return;
+  }
   for (int64_t a = begin + lane; a < end; a += 32) {
     const int64_t mine = slots[a];
     int64_t rank = 0;
@@ -115,12 +120,14 @@ __global__ void csr_rank_kernel(const int64_t* __restrict__ rowptr, int64_t N, c
   }
 }
 
-__global__ void csr_sort_long_rows_kernel(const int64_t* __restrict__ rowptr, int64_t N, int64_t* slots, int64_t* order,
-                                          const int32_t* flag) {
+// A small fixed grid walks the list of long rows (usually empty: the blocks read one counter and leave).
+__global__ void csr_sort_long_rows_kernel(const int64_t* __restrict__ rowptr, int64_t* slots, int64_t* order,
+                                          const int32_t* flag, const int64_t* long_rows, const int64_t* long_count) {
   if (*flag == 1) return;
-  for (int64_t row = blockIdx.x; row < N; row += gridDim.x) {
+  const int64_t count = *long_count;
+  for (int64_t item = blockIdx.x; item < count; item += gridDim.x) {
+    const int64_t row = long_rows[item];
     const int64_t begin = rowptr[row], len = rowptr[row + 1] - begin;
-    if (len <= kLongRow) continue;             // uniform over the block
     int64_t* v = slots + begin;
     int64_t padded = 1;
     while (padded < len) padded <<= 1;
@@ -261,11 +268,13 @@ int ictc_csr_build(const int64_t* keys, int64_t N, int64_t E, int64_t* rowptr, i
     if (N > 0) csr_cursor_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(rowptr, N, cursor);
     csr_fill_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(keys, E, N, cursor, slots, order, sorted_flag);
     if (N > 0) {
-      csr_rank_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(rowptr, N, slots, order, sorted_flag);
-      if (E > kLongRow) {      // a row longer than kLongRow can only exist when the list is
-        const unsigned blocks = (unsigned)(N < 1184 ? N : 1184);
-        csr_sort_long_rows_kernel<<<blocks, 512, 0, st>>>(rowptr, N, slots, order, sorted_flag);
-      }
+      // the cursor array is free again after the fill: it becomes the list of long rows, its counter sits behind
+      // the scan totals (the last of the spare words of the scratch)
+      int64_t* long_count = sums + scan_sums_elems(N + 1) + 1;
+      csr_zero_kernel<<<1, 1, 0, st>>>(long_count);
+      csr_rank_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(rowptr, N, slots, order, sorted_flag, cursor, long_count);
+      if (E > kLongRow)        // a row longer than kLongRow can only exist in a list this long
+        csr_sort_long_rows_kernel<<<64, 512, 0, st>>>(rowptr, slots, order, sorted_flag, cursor, long_count);
     }
   }
   return finish_launch("csr_build");

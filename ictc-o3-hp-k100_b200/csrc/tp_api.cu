@@ -50,6 +50,22 @@ int* kernel_status_word() {
   return cache[dev];
 }
 
+// A wait that nothing will ever satisfy: the same bounded polling loop as the kernels' mbarrier waits, with a short
+// limit.  It gives up, records `code` in the status word and returns normally.
+__global__ void bounded_wait_selftest_kernel(long long limit_cycles, int* status, int code) {
+  __shared__ __align__(8) unsigned long long bar;
+  const unsigned addr = smem_addr(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(addr, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const long long start = clock64();
+  bool done = mbar_try(addr, 0);
+  while (!done && clock64() - start <= limit_cycles) done = mbar_try(addr, 0);
+  if (!done && threadIdx.x == 0 && status) atomicExch(status, code);
+}
+
 static bool check(bool ok, const char* what) {
   if (!ok) set_error("invalid argument: %s", what);
   return ok;
@@ -221,6 +237,15 @@ int ictc_tp_graph_adjoint_chunk(int spec, int channels, int64_t num_rows, const 
   a.g_base = g_base; a.g_cap = g_capacity; a.g_by_pos = g_by_position ? 1 : 0;
   a.dg_base = dg ? dg_base : nullptr; a.dg_cap = dg_capacity;
   return o->adjoint(a, true, (cudaStream_t)stream);
+}
+
+int ictc_selftest_bounded_wait(int64_t limit_cycles, int code, void* stream) {
+  if (limit_cycles < 1 || limit_cycles > 200000000LL || code == 0) {
+    set_error("selftest: limit must be 1..2e8 cycles and the code non-zero");
+    return ICTC_ERR_BAD_ARG;
+  }
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((long long)limit_cycles, kernel_status_word(), code);
+  return finish_launch("selftest_bounded_wait");
 }
 
 }  // extern "C"

@@ -21,6 +21,7 @@ SIGNATURES = {
     "ictc_last_error": (C.c_char_p, []),
     "ictc_version": (C.c_char_p, []),
     "ictc_kernel_status": (_I, [C.POINTER(C.c_int), _I]),
+    "ictc_selftest_bounded_wait": (_I, [_L, _I, _P]),
     "ictc_tp_spec": (_I, [_I, _I, _I]),
     "ictc_tp_spec_info": (_I, [_I] + [C.POINTER(C.c_int)] * 5),
     "ictc_tp_edge_forward": (_I, [_I, _I, _L, _P, _P, _P, _P, _P, _P, _P]),

@@ -574,6 +574,7 @@ class MolecularDynamics:
                 self.graph.replay()
                 if on_step is not None:
                     on_step()
+            self.check_kernels()
             if self.check_overflow():
                 self.pos.copy_(snap[0])
                 self.vel.copy_(snap[1])
@@ -622,6 +623,7 @@ class MolecularDynamics:
                 if on_step is not None:
                     on_step()
             over, stale = self._flags()
+            self.check_kernels()
             self.events.append(("repeat" if (over or stale) else "block", block, time.perf_counter() - t_block))
             if over or stale:
                 self.pos.copy_(snap[0])

@@ -39,6 +39,11 @@ const char* ictc_last_error(void);
  * a wait runs out.  Synchronises the device, copies the word to *host_status (host pointer) and
  * clears it when reset != 0.  0 = every kernel so far completed normally. */
 int ictc_kernel_status(int* host_status, int reset);
+/* Exercises the give-up path of the bounded waits without any fault: one warp polls an mbarrier on which nothing
+ * ever arrives, with the kernels' own polling loop and a limit of `limit_cycles` SM cycles (at most 2e8, about 0.1 s),
+ * then records `code` (non-zero) in the status word and returns normally; ictc_kernel_status then reports `code`
+ * and the context stays usable.  No counterpart in the reference. */
+int ictc_selftest_bounded_wait(int64_t limit_cycles, int code, void* stream);
 /* Library build tag, e.g. "ictc_b200 sm_100a". */
 const char* ictc_version(void);
 

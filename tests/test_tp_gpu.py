@@ -250,3 +250,57 @@ def test_public_api_validation():
         tp(x.double(), torch.randn(4, 9, device="cuda"), torch.randn(4, 88, device="cuda"))
     out = tp(x[:0], torch.randn(0, 9, device="cuda"), torch.randn(0, 88, device="cuda"))
     assert out.shape == (0, 280)
+
+
+def test_bounded_wait_gives_up_and_reports_without_a_fault():
+    """A wait that nothing satisfies runs out after its (short) limit, the kernel returns normally, the status word
+    carries the code, resetting it works and the context keeps computing; an MD driver turns a non-zero status into
+    an exception instead of silently using the step's results."""
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    assert _lib.kernel_status() == 0
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.ictc_selftest_bounded_wait(200000, 77, st), "selftest")          # ~0.1 ms of polling
+    assert _lib.kernel_status(reset=False) == 77
+    from mace_ictc.md import MolecularDynamics
+    with pytest.raises(RuntimeError, match="gave up a bounded wait"):
+        MolecularDynamics.check_kernels(None)
+    assert _lib.kernel_status() == 0                                                  # the check above reset it
+    x = torch.arange(8, device="cuda").float()
+    assert float((x * 2).sum()) == 56.0                                               # the context is alive
+    assert lib.ictc_selftest_bounded_wait(0, 77, st) == -2 and lib.ictc_selftest_bounded_wait(1000, 0, st) == -2
+
+
+def test_graph_message_layouts_and_channel_linear_on_the_tensor_cores():
+    """GraphMessage converts its dictionaries with the one-launch layout kernel for 'fused_pack' / 'canonical' and with
+    reshapes for 'packed': same values and gradients; channel_linear with a 64-wide side runs on the tcgen05 kernel:
+    values and both gradients against float64."""
+    from ictc_o3 import EdgeTensorProduct, GraphMessage, channel_linear, direction_harmonics
+    torch.manual_seed(4)
+    n, e, c = 37, 210, 64
+    seed = EdgeTensorProduct.create(input_lmax=2, edge_lmax=2, channels=c)
+    feats = {l: torch.randn(n, c, 2 * l + 1, device="cuda", requires_grad=True) for l in range(3)}
+    unit = torch.nn.functional.normalize(torch.randn(e, 3, device="cuda"), dim=-1)
+    harm = {l: y.unsqueeze(1) for l, y in enumerate(direction_harmonics(unit, 2))}
+    gates = torch.randn(e, seed.gate_width, device="cuda", requires_grad=True)
+    src, dst = torch.randint(0, n, (e,), device="cuda"), torch.randint(0, n, (e,), device="cuda")
+    outs = {}
+    for layout in ("packed", "fused_pack", "canonical"):
+        op = GraphMessage(seed.tp, input_lmax=2, edge_lmax=2, layout=layout)
+        out = op(feats, harm, gates, src, dst)
+        grads = torch.autograd.grad(sum((o * o).sum() for o in out.values()), list(feats.values()) + [gates])
+        outs[layout] = ([out[l] for l in range(3)], grads)
+    for layout in ("fused_pack", "canonical"):
+        for a, b in zip(outs[layout][0] + list(outs[layout][1]), outs["packed"][0] + list(outs["packed"][1])):
+            assert a.shape == b.shape and float((a - b).abs().max()) <= 1e-6 * float(b.abs().max())
+    for cin, cout, m in ((64, 64, 5), (64, 192, 3), (256, 64, 1)):
+        x = torch.randn(23, cin, m, device="cuda", requires_grad=True)
+        w = (torch.randn(cout, cin, device="cuda") / cin ** 0.5).requires_grad_(True)
+        y = channel_linear(x, w)
+        cot = torch.randn_like(y)
+        gx, gw = torch.autograd.grad((y * cot).sum(), [x, w])
+        xr, wr = x.detach().double().cpu().requires_grad_(True), w.detach().double().cpu().requires_grad_(True)
+        yr = torch.einsum("oi,nim->nom", wr, xr)
+        rx, rw = torch.autograd.grad((yr * cot.double().cpu()).sum(), [xr, wr])
+        for got, want in ((y, yr), (gx, rx), (gw, rw)):
+            assert float((got.double().cpu() - want).abs().max() / want.abs().max()) < 5e-6
