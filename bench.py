@@ -90,9 +90,9 @@ def make_inputs(seed, device, num_atoms=NUM_ATOMS, dtype=torch.float32):
 
 # ------------------------------------------------------------------------------------ clocks
 class ClockSampler:
-    """SM clock and throttle reasons of one GPU, read through NVML from the benchmark's own thread between
-    steps (``tick``; at most one reading per ``period`` seconds).  A separate sampling process or an nvidia-smi
-    loop slows an eager multi-GPU step by tens of per cent on these hosts; two in-process queries do not."""
+    """SM clock and throttle reasons of one GPU, read through NVML inside the benchmark's own process (a light
+    thread, at most one reading per ``period`` seconds).  A separate sampling process or an nvidia-smi loop slows an
+    eager multi-GPU step by tens of per cent on these hosts; two in-process queries per reading do not."""
 
     def __init__(self, gpu_index, period=0.25):
         self.rows, self.period, self.last, self.active = [], period, 0.0, False
@@ -112,14 +112,24 @@ class ClockSampler:
             self.nvml = None
 
     def start(self):
+        """Sample from a daemon thread of this process every ``period`` seconds until ``stop`` (a recorded step is
+        queued in milliseconds, so the host thread would otherwise see the GPU only before and after the region)."""
+        import threading
         self.active, self.last = True, 0.0
 
+        def loop():
+            while self.active:
+                self.tick()
+                time.sleep(self.period)
+        self.thread = threading.Thread(target=loop, daemon=True)
+        self.thread.start()
+
     def tick(self):
-        """Called between steps of the timed region."""
+        """One reading (rate limited); also called between steps of the timed region."""
         if not self.active or self.nvml is None:
             return
         now = time.perf_counter()
-        if now - self.last < self.period:
+        if now - self.last < 0.8 * self.period:
             return
         self.last = now
         try:

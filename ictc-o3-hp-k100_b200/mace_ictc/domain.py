@@ -101,7 +101,7 @@ class HaloPlan:
     fixed offsets, ordered (image, sender row) inside a group, padding at the end of each group.
     """
 
-    def __init__(self, rank: int, world: int, grid, box, halo: float, num_owned: int, device, margin: float = 1.25,
+    def __init__(self, rank: int, world: int, grid, box, halo: float, num_owned: int, device, margin: float = 1.10,
                  group=None):
         self.rank, self.world, self.grid, self.group = rank, world, tuple(grid), group
         self.box = [float(b) for b in box]

@@ -364,7 +364,7 @@ class MolecularDynamics:
         d["n_own"] = n
         self.num_owned = n
 
-    def _setup_distributed(self, edge_margin=1.15, own_margin=1.02):
+    def _setup_distributed(self, edge_margin=1.15, own_margin=1.01):
         """Fixed-capacity arrays of this rank's atoms, halo plan, local buffers and neighbour-list buffers
         (collective).  On entry ``pos``, ``vel``, ``gid``, ``z`` (and ``forces``, if any) hold exactly the rank's
         atoms; afterwards they have ``own_cap`` rows, the first ``num_owned`` of them atoms."""
