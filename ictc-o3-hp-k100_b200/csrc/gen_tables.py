@@ -155,10 +155,18 @@ def emit_tp(lines):
             ent += [f"VG({k},{p_})" for k in slots]
             # couplings of the path ordered by (slot, input component): consecutive terms feed different harmonic
             # accumulators, so their FMAs do not wait for one another
+            # couplings of the path grouped by (harmonic j, coupling value): the products x[i] * vg[k] of a group are
+            # summed first (DF opens the group, DA adds to it) and the group meets its coupling once (DE: t = position
+            # of one member in CLIST)
+            groups = {}
             for (i, j, k, pp, c) in sorted((e_ for e_ in plan.nnz if e_[3] == p_), key=lambda e_: (e_[2], e_[0], e_[1])):
-                ent.append(f"DS({pos_t[(i, j, k, pp)]},{i},{j},{k})")
+                groups.setdefault((j, struct.pack("<f", c)), []).append((i, k, pos_t[(i, j, k, pp)]))
+            for (j, _c), members in groups.items():
+                for m_, (i, k, t) in enumerate(members):
+                    ent.append(f"{'DF' if m_ == 0 else 'DA'}({i},{k})")
+                ent.append(f"DE({members[0][2]},{j})")
             ent.append(f"PE({p_})")
-        lines.append(f"#define ICTC_TP_{n}_ADJP(PB,VL,ZF,ZA,Q,VG,DS,PE) \\\n  " + " \\\n  ".join(
+        lines.append(f"#define ICTC_TP_{n}_ADJP(PB,VL,ZF,ZA,Q,VG,DF,DA,DE,PE) \\\n  " + " \\\n  ".join(
             " ".join(ent[a:a + 6]) for a in range(0, len(ent), 6)))
         used_i = sorted({e[0] for e in plan.nnz})
         used_j = sorted({e[1] for e in plan.nnz})

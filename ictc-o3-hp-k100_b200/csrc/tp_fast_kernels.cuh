@@ -94,14 +94,16 @@ template <int ID, int CPL> struct TpConst;
 #define ICTC_M_VG2(k, p) vg[k] = vmul(v[k], ge[p]);
 // path-major fused adjoint (see the ADJP program in the generated tables)
 #define ICTC_M_P_PB(p) gp = gate(p); dgp = Vec<CPL>::dup(0.f);
-#define ICTC_M_P_VL(k) v[k] = Vec<CPL>::load(vp + (k) * (32 * CPL));
+#define ICTC_M_P_VL(k) v[k] = cot(k);
 #define ICTC_M_P_ZF(e, k) ICTC_LDB(e) z = vmul(ICTC_GETB(e), v[k]);
 #define ICTC_M_P_ZA(e, k) ICTC_LDB(e) z = vfma(ICTC_GETB(e), v[k], z);
 #define ICTC_M_P_Q(i, p)                         \
   if (NEEDX) dx[i] = vfma(z, gp, dx[i]);         \
   if (NEEDG) dgp = vfma(x[i], z, dgp);
 #define ICTC_M_P_VG(k, p) if (NEEDH) vg[k] = vmul(v[k], gp);
-#define ICTC_M_P_DS(t, i, j, k) if (NEEDH) dsh[j] = vfma(vmul(x[i], vg[k]), Vec<CPL>{K::c[t]}, dsh[j]);
+#define ICTC_M_P_DF(i, k) if (NEEDH) { Vec<CPL> s = vmul(x[i], vg[k]);
+#define ICTC_M_P_DA(i, k) s = vfma(x[i], vg[k], s);
+#define ICTC_M_P_DE(t, j) dsh[j] = vfma(s, Vec<CPL>{K::c[t]}, dsh[j]); }
 #define ICTC_M_P_PE(p) if (NEEDG) store_dg(p, dgp);
 #define ICTC_M_DSHT_F(t, i, j, k, p) dsh[j] = vmul(vmul(x[i], vg[k]), Vec<CPL>{K::c[t]});
 #define ICTC_M_DSHT_A(t, i, j, k, p) dsh[j] = vfma(vmul(x[i], vg[k]), Vec<CPL>{K::c[t]}, dsh[j]);
@@ -137,17 +139,17 @@ template <int ID, int CPL> struct TpConst;
       ICTC_TP_##S##_AB(ICTC_M_AB_F, ICTC_M_AB_A, ICTC_M_AB_Q)                                           \
     }                                                                                                   \
     /* Path-major adjoint of one edge: dx (accumulated), dsh (accumulated) and the gate gradient of every   \
-       path (handed to store_dg as soon as it is complete).  vp: this lane's cotangent row, loaded slot by    \
-       slot; gate(p): this lane's gate of path p; sb: geometry in AP order.  Only one path's slots are live. */ \
-    template <bool NEEDX, bool NEEDH, bool NEEDG, class GateF, class StoreF>                            \
-    static __device__ __forceinline__ void adjoint_fused(const V (&x)[Base::NX], const float* vp,       \
+       path (handed to store_dg as soon as it is complete).  cot(k): this lane's part of cotangent slot k;   \
+       gate(p): this lane's gate of path p; sb: geometry in AP order.  Only one path's slots are live. */ \
+    template <bool NEEDX, bool NEEDH, bool NEEDG, class CotF, class GateF, class StoreF>                \
+    static __device__ __forceinline__ void adjoint_fused(const V (&x)[Base::NX], CotF cot,              \
                                                          GateF gate, const V* sb, V (&dx)[Base::NX],    \
                                                          V (&dsh)[Base::NH], StoreF store_dg) {         \
       Chunk<CPL> ch;                                                                                    \
       V z, gp, dgp;                                                                                     \
       V v[Base::NO], vg[Base::NO];                                                                      \
       ICTC_TP_##S##_ADJP(ICTC_M_P_PB, ICTC_M_P_VL, ICTC_M_P_ZF, ICTC_M_P_ZA, ICTC_M_P_Q, ICTC_M_P_VG,   \
-                         ICTC_M_P_DS, ICTC_M_P_PE)                                                      \
+                         ICTC_M_P_DF, ICTC_M_P_DA, ICTC_M_P_DE, ICTC_M_P_PE)                            \
     }                                                                                                   \
     static __device__ __forceinline__ void dharm(const V (&x)[Base::NX], const V (&v)[Base::NO],        \
                                                  const V (&ge)[Base::NP], V (&dsh)[Base::NH]) {         \

@@ -61,8 +61,11 @@ template <> __device__ __forceinline__ Vec<2> lds_vec<2>(const unsigned char* p)
   return Vec<2>{*reinterpret_cast<const unsigned long long*>(p)};
 }
 
-// Only the gate rows (a pure HBM stream) go through the ring; the gathered feature / cotangent rows
-// are mostly L2 hits and are loaded straight into registers, which keeps shared-memory traffic low.
+// Only the gate rows (a pure HBM stream) go through the ring; the gathered feature / cotangent rows are mostly L2
+// hits and are loaded straight into registers.  Staging the 8,960-byte cotangent row of the 35-slot product in the
+// ring as well (two stages, which leaves room for 8 warps per SM) was measured slower (6.99 against 6.42 ms at
+// 4.3 M edges): without any memory traffic the adjoint still needs 68 % of its time, it is bound by the FP32 pipe
+// and by dependent-issue latency at 3 warps per scheduler, not by the row loads.
 constexpr bool kStageRows = false;
 
 #ifndef ICTC_TMA_WARPS
@@ -78,7 +81,7 @@ constexpr int kTmaMinBlocks = ICTC_TMA_MIN_WARPS / ICTC_TMA_WARPS;
 #ifndef ICTC_TMA_MIN_WARPS_ADJ
 #define ICTC_TMA_MIN_WARPS_ADJ 12
 #endif
-constexpr int kTmaMinBlocksAdj = ICTC_TMA_MIN_WARPS_ADJ / ICTC_TMA_WARPS;
+constexpr int kTmaMinWarpsAdj = ICTC_TMA_MIN_WARPS_ADJ;
 
 template <class S, class F, int CPL, int STAGES, bool ADJ> struct TmaLayout {
   static constexpr int C = 32 * CPL;
@@ -89,7 +92,12 @@ template <class S, class F, int CPL, int STAGES, bool ADJ> struct TmaLayout {
   static constexpr unsigned GEO_BYTES = 2 * NBP * sizeof(Vec<CPL>);
   static constexpr unsigned BAR_OFF = STAGES * SLOT_BYTES;
   static constexpr unsigned GEO_OFF = BAR_OFF + ((STAGES * 8 + 15) / 16) * 16;
-  static constexpr unsigned WARP_BYTES = ((GEO_OFF + GEO_BYTES + 127) / 128) * 128;
+  // adjoint only: per-lane harmonic-gradient partial sums of RED_EDGES edges, one padded row of 32 lanes per
+  // (edge, harmonic); lane r later adds up row r
+  static constexpr int RED_EDGES = 32 / S::NH, RED_PITCH = 36;
+  static constexpr unsigned RED_OFF = GEO_OFF + GEO_BYTES;
+  static constexpr unsigned RED_BYTES = ADJ ? RED_EDGES * S::NH * RED_PITCH * 4 : 0;
+  static constexpr unsigned WARP_BYTES = ((RED_OFF + RED_BYTES + 127) / 128) * 128;
   static constexpr unsigned BLOCK_BYTES = WARP_BYTES * kTmaWarps;
 };
 
@@ -119,54 +127,56 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocks) tp_graph_forwar
 #pragma unroll
   for (int k = 0; k < S::NO; ++k) acc[k] = V::dup(0.f);
   const int64_t begin = ldg(a.rowptr + n), end = ldg(a.rowptr + n + 1);
-  auto edge_at = [&](int64_t it) -> int64_t { return a.order ? ldg(a.order + it) : it; };
-  auto issue = [&](int slot, int64_t e, int64_t s, int64_t pos) {
+  // edge ids and row numbers fit 32 bits (checked by the launcher): 32 x 32 -> 64-bit multiplies form the addresses
+  auto edge_at = [&](int64_t it) -> int { return int(a.order ? ldg(a.order + it) : it); };
+  auto row_at = [&](int e) -> int { return int(ldg(a.nbr + e)); };
+  auto issue = [&](int slot, int e, int s, int64_t pos) {
     if (lane == 0) {
       const unsigned bar = bars + slot * 8;
       unsigned char* dst = mine + slot * L::SLOT_BYTES;
       mbar_expect_tx(bar, L::SLOT_BYTES);
       const int64_t gr = gate_row_of(a, e, pos);
       bulk_g2s(smem_addr(dst), a.g + gr * (S::NP * C), L::GATE_BYTES, bar);
-      if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.x + s * (S::NX * C), L::ROW_BYTES, bar);
+      if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.x + int64_t(s) * (S::NX * C), L::ROW_BYTES, bar);
     }
   };
   // prologue: fill the ring
 #pragma unroll
   for (int k = 0; k < STAGES; ++k)
     if (begin + k < end) {
-      const int64_t e = edge_at(begin + k);
-      issue(k, e, ldg(a.nbr + e), begin + k);
+      const int e = edge_at(begin + k);
+      issue(k, e, row_at(e), begin + k);
     }
   // (edge id, sender) of the edge that will be issued at the END of this iteration, started early
-  int64_t e_pf = 0, s_pf = 0;
+  int e_pf = 0, s_pf = 0;
   if (begin + STAGES < end) {
     e_pf = edge_at(begin + STAGES);
-    s_pf = ldg(a.nbr + e_pf);
+    s_pf = row_at(e_pf);
   }
-  int64_t e_cur = begin < end ? edge_at(begin) : 0;
-  int64_t r_cur = begin < end ? ldg(a.nbr + e_cur) : 0;
-  float shv = (begin < end && lane < S::NH) ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
+  int e_cur = begin < end ? edge_at(begin) : 0;
+  int r_cur = begin < end ? row_at(e_cur) : 0;
+  float shv = (begin < end && lane < S::NH) ? ldg(a.sh + int64_t(e_cur) * S::NH + lane) : 0.f;
   int slot = 0, buf = 0;
   unsigned parity = 0;
   for (int64_t it = begin; it < end; ++it, buf ^= 1) {
-    const int64_t e = e_cur;
+    const int e = e_cur;
     const float sh_now = shv;
     V ge[S::NP], x[S::NX];
     if (!kStageRows) {
-      const float* xp = a.x + r_cur * (S::NX * C) + lane * CPL;
+      const float* xp = a.x + int64_t(r_cur) * (S::NX * C) + lane * CPL;
 #pragma unroll
       for (int i = 0; i < S::NX; ++i) x[i] = V::load(xp + i * C);
     }
     // start the index/harmonic loads of later edges before blocking on this edge's data
-    int64_t e_pf2 = 0, s_pf2 = 0;
+    int e_pf2 = 0, s_pf2 = 0;
     if (it + 1 < end) {
       e_cur = edge_at(it + 1);
-      r_cur = ldg(a.nbr + e_cur);
-      shv = lane < S::NH ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
+      r_cur = row_at(e_cur);
+      shv = lane < S::NH ? ldg(a.sh + int64_t(e_cur) * S::NH + lane) : 0.f;
     }
     if (it + STAGES + 1 < end) {
       e_pf2 = edge_at(it + STAGES + 1);
-      s_pf2 = ldg(a.nbr + e_pf2);
+      s_pf2 = row_at(e_pf2);
     }
     V* sb = geo + buf * L::NBP;
     build_geometry<F::NB, CPL, L::R>(bt, sh_now, lane, sb);
@@ -214,8 +224,9 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocks) tp_graph_forwar
 }
 
 // ------------------------------------------------------------------------------------------------
-template <class S, class F, int CPL, int STAGES, bool GRAPH, bool NEEDX, bool NEEDH, bool NEEDG>
-__global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_tma_kernel(TpArgs a) {
+// PLAIN: no edge mask and no path weights (decided on the host), so the per-path scaling code is not compiled in.
+template <class S, class F, int CPL, int STAGES, bool GRAPH, bool NEEDX, bool NEEDH, bool NEEDG, bool PLAIN>
+__global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinWarpsAdj / kTmaWarps) tp_adjoint_tma_kernel(TpArgs a) {
   using V = Vec<CPL>;
   using L = TmaLayout<S, F, CPL, STAGES, true>;
   constexpr int C = L::C;
@@ -249,44 +260,47 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_t
     begin = ldg(a.rowptr + owner);
     end = ldg(a.rowptr + owner + 1);
   }
-  auto edge_at = [&](int64_t it) -> int64_t { return (GRAPH && a.order) ? ldg(a.order + it) : it; };
-  auto row_of = [&](int64_t e) -> int64_t { return GRAPH ? ldg(a.nbr + e) : e; };
-  auto issue = [&](int slot, int64_t e, int64_t d, int64_t pos) {
+  auto edge_at = [&](int64_t it) -> int { return int((GRAPH && a.order) ? ldg(a.order + it) : it); };
+  auto row_of = [&](int e) -> int { return GRAPH ? int(ldg(a.nbr + e)) : e; };
+  auto issue = [&](int slot, int e, int d, int64_t pos) {
     if (lane == 0) {
       const unsigned bar = bars + slot * 8;
       unsigned char* dst = mine + slot * L::SLOT_BYTES;
       mbar_expect_tx(bar, L::SLOT_BYTES);
       const int64_t gr = gate_row_of(a, e, pos);
       bulk_g2s(smem_addr(dst), a.g + gr * (S::NP * C), L::GATE_BYTES, bar);
-      if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.v + d * (S::NO * C), L::ROW_BYTES, bar);
+      if (kStageRows) bulk_g2s(smem_addr(dst + L::GATE_BYTES), a.v + int64_t(d) * (S::NO * C), L::ROW_BYTES, bar);
     }
   };
 #pragma unroll
   for (int k = 0; k < STAGES; ++k)
     if (begin + k < end) {
-      const int64_t e = edge_at(begin + k);
+      const int e = edge_at(begin + k);
       issue(k, e, row_of(e), begin + k);
     }
-  int64_t e_pf = 0, d_pf = 0;
+  int e_pf = 0, d_pf = 0;
   if (begin + STAGES < end) {
     e_pf = edge_at(begin + STAGES);
     d_pf = row_of(e_pf);
   }
-  int64_t e_cur = begin < end ? edge_at(begin) : 0;
-  int64_t r_cur = begin < end ? row_of(e_cur) : 0;
-  float shv = (begin < end && lane < S::NH) ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
+  int e_cur = begin < end ? edge_at(begin) : 0;
+  int r_cur = begin < end ? row_of(e_cur) : 0;
+  float shv = (begin < end && lane < S::NH) ? ldg(a.sh + int64_t(e_cur) * S::NH + lane) : 0.f;
   int slot = 0, buf = 0;
   unsigned parity = 0;
+  float* red = reinterpret_cast<float*>(mine + L::RED_OFF);
+  int batch_edge[L::RED_EDGES];
+  int batch = 0;
   for (int64_t it = begin; it < end; ++it, buf ^= 1) {
-    const int64_t e = e_cur;
+    const int e = e_cur;
     const float sh_now = shv;
     static_assert(!kStageRows, "the path-major adjoint reads the cotangent row from global memory");
-    const float* vp = a.v + r_cur * (S::NO * C) + lane * CPL;     // this edge's cotangent row, read slot by slot
-    int64_t e_pf2 = 0, d_pf2 = 0;
+    const float* vp = a.v + int64_t(r_cur) * (S::NO * C) + lane * CPL;     // this edge's cotangent row, read slot by slot
+    int e_pf2 = 0, d_pf2 = 0;
     if (it + 1 < end) {
       e_cur = edge_at(it + 1);
       r_cur = row_of(e_cur);
-      shv = lane < S::NH ? ldg(a.sh + e_cur * S::NH + lane) : 0.f;
+      shv = lane < S::NH ? ldg(a.sh + int64_t(e_cur) * S::NH + lane) : 0.f;
     }
     if (it + STAGES + 1 < end) {
       e_pf2 = edge_at(it + STAGES + 1);
@@ -304,33 +318,62 @@ __global__ void __launch_bounds__(kTmaWarps * 32, kTmaMinBlocksAdj) tp_adjoint_t
       return;
     }
     const unsigned char* base = mine + slot * L::SLOT_BYTES + lane * (CPL * 4);
-    const bool scaled = a.mask || a.w;
+    const bool scaled = !PLAIN && (a.mask || a.w);
     const V mu = V::dup((scaled && a.mask) ? ldg(a.mask + e) : 1.f);
     auto scale_of = [&](int p) -> V { return a.w ? vmul(mu, V::load(a.w + p * C + lane * CPL)) : mu; };
     auto gate = [&](int p) -> V {
       const V g = lds_vec<CPL>(base + p * (C * 4));
+      if (PLAIN) return g;
       return scaled ? vmul(g, scale_of(p)) : g;
     };
-    const int64_t dgr = NEEDG ? dg_row_of(a, e, it) : 0;
-    float* dgp = a.dg + (dgr < 0 ? 0 : dgr) * (S::NP * C) + lane * CPL;
+    int dgr = e;            // row of this edge's gate gradient (negative: outside the caller's window, not stored)
+    if (NEEDG && a.dg_base) {
+      const int64_t r = it - ldg(a.dg_base);
+      dgr = (r >= 0 && r < a.dg_cap) ? int(r) : -1;
+    }
+    float* dgp = a.dg + int64_t(dgr < 0 ? 0 : dgr) * (S::NP * C) + lane * CPL;
     auto store_dg = [&](int p, V val) {
-      if (dgr >= 0) (scaled ? vmul(val, scale_of(p)) : val).store(dgp + p * C);
+      if (PLAIN) {
+        if (dgr >= 0) val.store(dgp + p * C);
+      } else if (dgr >= 0) {
+        (scaled ? vmul(val, scale_of(p)) : val).store(dgp + p * C);
+      }
     };
     __syncwarp();   // geometry visible to every lane
     V dshv[S::NH];
 #pragma unroll
     for (int j = 0; j < S::NH; ++j) dshv[j] = V::dup(0.f);
-    F::template adjoint_fused<NEEDX, NEEDH, NEEDG>(x, vp, gate, sb, dx, dshv, store_dg);
+    auto cot = [&](int k) -> V { return V::load(vp + k * C); };      // slot k of the cotangent row
+    F::template adjoint_fused<NEEDX, NEEDH, NEEDG>(x, cot, gate, sb, dx, dshv, store_dg);
     __syncwarp();   // every lane is done with the slot and the geometry buffer
     if (NEEDH) {
-      // 12-shuffle recursive halving instead of nine 5-step butterflies
-      float part[S::NH];
+      // The sum over the 32 lanes goes through shared memory: every lane parks its NH partial sums in column `lane`
+      // of the batch buffer; once RED_EDGES edges are in (or the row ends) lane r adds up row r = (edge, harmonic)
+      // with eight 16-byte loads, in a fixed order.
 #pragma unroll
-      for (int j = 0; j < S::NH; ++j) part[j] = dshv[j].hsum();
-      int which;
-      bool holder;
-      const float tot = warp_reduce_scatter<S::NH>(part, lane, which, holder);
-      if (holder) a.dsh[e * S::NH + which] = tot;
+      for (int j = 0; j < S::NH; ++j) red[(batch * S::NH + j) * L::RED_PITCH + lane] = dshv[j].hsum();
+#pragma unroll
+      for (int k = 0; k < L::RED_EDGES; ++k)
+        if (batch == k) batch_edge[k] = e;      // unrolled so that the array stays in registers
+      if (++batch == L::RED_EDGES || it + 1 == end) {
+        __syncwarp();
+        if (lane < batch * S::NH) {
+          const float4* row = reinterpret_cast<const float4*>(red + lane * L::RED_PITCH);
+          float tot = 0.f;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 t = row[q];
+            tot += (t.x + t.y) + (t.z + t.w);
+          }
+          const int b = lane / S::NH;
+          int eb = batch_edge[0];
+#pragma unroll
+          for (int k = 1; k < L::RED_EDGES; ++k) eb = b == k ? batch_edge[k] : eb;
+          a.dsh[int64_t(eb) * S::NH + (lane - b * S::NH)] = tot;
+        }
+        batch = 0;
+        __syncwarp();
+      }
     }
     if (it + STAGES < end) issue(slot, e_pf, d_pf, it + STAGES);
     e_pf = e_pf2;
@@ -371,16 +414,23 @@ template <class S, class F, int CPL> int launch_graph_forward_tma(const TpArgs& 
   return finish_launch("tp_graph_forward_tma");
 }
 
-template <class S, class F, int CPL, bool GRAPH, bool NX_, bool NH_, bool NG_>
-int launch_adjoint_tma_one(const TpArgs& a, cudaStream_t st) {
+template <class S, class F, int CPL, bool GRAPH, bool NX_, bool NH_, bool NG_, bool PLAIN>
+int launch_adjoint_tma_plain(const TpArgs& a, cudaStream_t st) {
   using L = TmaLayout<S, F, CPL, kAdjStages, true>;
-  auto kernel = tp_adjoint_tma_kernel<S, F, CPL, kAdjStages, GRAPH, NX_, NH_, NG_>;
+  auto kernel = tp_adjoint_tma_kernel<S, F, CPL, kAdjStages, GRAPH, NX_, NH_, NG_, PLAIN>;
   static const int attr = set_smem(kernel, L::BLOCK_BYTES);
   if (attr != ICTC_OK) return attr;
   const int64_t owners = GRAPH ? a.N : a.E;
   const int64_t blocks = (owners + kTmaWarps - 1) / kTmaWarps;
   kernel<<<(unsigned)blocks, kTmaWarps * 32, L::BLOCK_BYTES, st>>>(a);
   return finish_launch("tp_adjoint_tma");
+}
+
+template <class S, class F, int CPL, bool GRAPH, bool NX_, bool NH_, bool NG_>
+int launch_adjoint_tma_one(const TpArgs& a, cudaStream_t st) {
+  // the unscaled sender-row sweep is the molecular-dynamics case and gets its own instantiation
+  if (GRAPH && !a.mask && !a.w) return launch_adjoint_tma_plain<S, F, CPL, GRAPH, NX_, NH_, NG_, GRAPH>(a, st);
+  return launch_adjoint_tma_plain<S, F, CPL, GRAPH, NX_, NH_, NG_, false>(a, st);
 }
 
 template <class S, class F, int CPL, bool GRAPH> int launch_adjoint_tma_g(const TpArgs& a, cudaStream_t st) {
@@ -398,7 +448,7 @@ template <class S, class F, int CPL, bool GRAPH> int launch_adjoint_tma_g(const 
 }
 
 template <class S, int ID> int graph_forward_dispatch_tma(const TpArgs& a, cudaStream_t st) {
-  if (a.N > 0 && a.E > 0 && (a.C == 32 || a.C == 64) && (a.N + kTmaWarps - 1) / kTmaWarps <= 2147483647LL &&
+  if (a.N > 0 && a.E > 0 && a.E <= 2147483647LL && (a.C == 32 || a.C == 64) && a.N <= 2147483647LL &&
       aligned16(a.x) && aligned16(a.g) && aligned8(a.out) && (!a.w || aligned8(a.w))) {
     if (a.C == 64) return launch_graph_forward_tma<S, TpFast<ID, 2>, 2>(a, st);
     return launch_graph_forward_tma<S, TpFast<ID, 1>, 1>(a, st);
@@ -408,7 +458,8 @@ template <class S, int ID> int graph_forward_dispatch_tma(const TpArgs& a, cudaS
 
 template <class S, int ID> int adjoint_dispatch_tma(const TpArgs& a, bool graph, cudaStream_t st) {
   const int64_t owners = graph ? a.N : a.E;
-  if (owners > 0 && a.E > 0 && (a.C == 32 || a.C == 64) && (owners + kTmaWarps - 1) / kTmaWarps <= 2147483647LL &&
+  if (owners > 0 && a.E > 0 && a.E <= 2147483647LL && (a.C == 32 || a.C == 64) && owners <= 2147483647LL &&
+      a.N <= 2147483647LL &&
       aligned16(a.g) && aligned16(a.v) && aligned8(a.x) && (!a.w || aligned8(a.w)) && (!a.dx || aligned8(a.dx)) &&
       (!a.dg || aligned8(a.dg))) {
     if (a.C == 64)
