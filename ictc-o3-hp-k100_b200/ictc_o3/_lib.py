@@ -42,6 +42,8 @@ SIGNATURES = {
     "ictc_mlp_chain_forward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ictc_mlp_chain_backward": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P]),
     "ictc_channel_linear_tc": (_I, [_L, _I, _I, _P, _I, _L, _P, _P, _I, _L, _P]),
+    "ictc_weight_grad_workspace": (_L, [_L, _I]),
+    "ictc_weight_grad_tc": (_I, [_L, _I, _P, _L, _P, _L, _P, _L, _P, _P]),
     "ictc_csr_scratch_bytes": (_L, [_L, _L]),
     "ictc_csr_build": (_I, [_P, _L, _L, _P, _P, _P, _P, _P]),
     "ictc_csr_build_static": (_I, [_P, _L, _L, _P, _P, _P, _P]),

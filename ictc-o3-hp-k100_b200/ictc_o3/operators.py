@@ -441,10 +441,48 @@ def _tc_matmul(rows, weight):
     return out
 
 
+def _tc_weight_grad(grad, rows):
+    """grad^T @ rows = [Cout, Cin], contracted over the rows on the tcgen05 weight-gradient kernel
+    (``ictc_weight_grad_tc``: split over the SMs, partial sums added in a fixed order).  The 64-wide side is the
+    kernel's second operand; the wide side is covered in blocks of at most 768 columns."""
+    cout, cin = grad.shape[1], rows.shape[1]
+    if cin != 64:                         # the wide side has to be the first operand: dW^T = rows^T @ grad
+        return _tc_weight_grad(rows, grad).t()
+    grad, rows = grad.contiguous(), rows.contiguous()
+    r = grad.shape[0]
+    out = torch.empty(cout, 64, dtype=torch.float32, device=grad.device)
+    lib = _lib.load()
+    with _lib.on_device(grad.device):
+        for start in range(0, cout, 768):
+            width = min(768, cout - start)
+            need = lib.ictc_weight_grad_workspace(r, width)
+            work = torch.empty(max(need, 16) // 4, dtype=torch.float32, device=grad.device)
+            _lib.check(lib.ictc_weight_grad_tc(r, width, grad.data_ptr() + 4 * start, cout, rows.data_ptr(), 64,
+                                               out.data_ptr() + 4 * 64 * start, 64, work.data_ptr(),
+                                               _lib.stream(grad.device)), "ictc_weight_grad_tc")
+    return out
+
+
+class _WeightGrad(torch.autograd.Function):
+    """The weight gradient as a differentiable node (its own derivatives are plain products, on the library GEMM:
+    they are only met by third-order differentiation)."""
+
+    @staticmethod
+    def forward(ctx, grad, rows):
+        ctx.save_for_backward(grad, rows)
+        return _tc_weight_grad(grad, rows)
+
+    @staticmethod
+    def backward(ctx, g):
+        grad, rows = ctx.saved_tensors
+        return (rows.mm(g.t()) if ctx.needs_input_grad[0] else None,
+                grad.mm(g) if ctx.needs_input_grad[1] else None)
+
+
 class _RowsTimesWeight(torch.autograd.Function):
     """y = rows @ weight^T on the tensor-core kernel.  The input gradient is the same kernel with the weight
     transposed (applied through this function, so it stays differentiable); the weight gradient is the
-    row-contracted outer product, a library GEMM."""
+    row-contracted outer product on the tcgen05 weight-gradient kernel."""
 
     @staticmethod
     def forward(ctx, rows, weight):
@@ -456,7 +494,7 @@ class _RowsTimesWeight(torch.autograd.Function):
         rows, weight = ctx.saved_tensors
         grad = grad.contiguous()
         d_rows = _RowsTimesWeight.apply(grad, weight.t()) if ctx.needs_input_grad[0] else None
-        d_weight = grad.t().mm(rows) if ctx.needs_input_grad[1] else None
+        d_weight = _WeightGrad.apply(grad, rows.contiguous()) if ctx.needs_input_grad[1] else None
         return d_rows, d_weight
 
 

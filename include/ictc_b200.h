@@ -302,6 +302,17 @@ int ictc_gate_gemm_backward_rows(int64_t capacity, int num_out, const float* dga
 int ictc_channel_linear_tc(int64_t num_rows, int k_chunks, int n_chunks, const float* in, int in_mm, int64_t in_ld,
                            const float* w_packed, float* out, int out_mm, int64_t out_ld, void* stream);
 
+/* Weight gradient of a row-wise linear map, dW[o, i] = sum_r grad[r, o] * rows[r, i], contracted over the rows on
+ * the tensor cores with fp32-level accuracy (three-term TF32) and a fixed summation order (reference: the dW branch
+ * of the training gate, ictc_o3/ops/training_gate_message.py:120-186, and the weight gradients of channel_linear,
+ * ictc_o3/operators.py:609-628, under autograd).  num_out is a multiple of 64 up to 768, `rows` contributes 64
+ * columns; grad_ld / rows_ld / dweight_ld are row strides in floats, so a wider `rows` or `dweight` is covered by
+ * one call per 64-column block.  `workspace` holds ictc_weight_grad_workspace(num_rows, num_out) bytes (16-byte
+ * aligned; negative result: unsupported size). */
+int64_t ictc_weight_grad_workspace(int64_t num_rows, int num_out);
+int ictc_weight_grad_tc(int64_t num_rows, int num_out, const float* grad, int64_t grad_ld, const float* rows,
+                        int64_t rows_ld, float* dweight, int64_t dweight_ld, float* workspace, void* stream);
+
 /* Hidden layers of the gate MLP as a chain through tensor memory (same reference as the last layer above):
  * the two 64 x 64 layers are three-term TF32 tcgen05.mma products with the activations kept in TMEM, the
  * num_basis-wide layer is fp32 FMA.  w1_packed / w2_packed come from ictc_gate_pack_weights(64, W, 0, ...),

@@ -295,3 +295,53 @@ def test_row_limit_on_the_device_bounds_the_work():
     assert float((da3[:live].double().cpu() - ref).abs().max() / ref.abs().max()) < 1e-5
     assert bool(torch.isnan(da3[live:]).all())
     assert _status(lib) == 0
+
+
+@pytest.mark.parametrize("rows,nout,pad", [(1, 64, 0), (7, 192, 0), (1000, 704, 0), (70001, 704, 0), (9, 768, 0),
+                                           (148 * 8 * 5 + 3, 64, 32), (0, 192, 0)])
+def test_weight_gradient_on_the_tensor_cores(rows, nout, pad):
+    """dW = grad^T @ rows contracted over the rows (tcgen05, both operands transposed into shared memory): against
+    float64, with strided operands, bitwise repeatable."""
+    from ictc_o3 import _lib
+    lib = _lib.load()
+    torch.manual_seed(rows + nout)
+    grad_full = torch.randn(max(rows, 1), nout + pad).cuda()
+    rows_full = torch.randn(max(rows, 1), 64 + pad).cuda()
+    need = lib.ictc_weight_grad_workspace(rows, nout)
+    assert need > 0
+    work = torch.empty(need // 4, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    outs = []
+    for _ in range(2):
+        dw = torch.full((nout, 64 + pad), float("nan"), device="cuda")
+        _lib.check(lib.ictc_weight_grad_tc(rows, nout, grad_full.data_ptr(), nout + pad, rows_full.data_ptr(), 64 + pad,
+                                           dw.data_ptr(), 64 + pad, work.data_ptr(), st), "weight_grad")
+        outs.append(dw[:, :64].clone())
+        assert bool(torch.isnan(dw[:, 64:]).all())
+    assert _status(lib) == 0
+    assert torch.equal(outs[0], outs[1])
+    ref = grad_full[:rows, :nout].double().cpu().t() @ rows_full[:rows, :64].double().cpu()
+    scale = float(ref.abs().max()) if rows else 1.0
+    assert float((outs[0].double().cpu() - ref).abs().max()) <= 1e-5 * max(scale, 1e-30)      # fp32 accumulation
+    assert lib.ictc_weight_grad_workspace(10, 100) < 0 and lib.ictc_weight_grad_workspace(10, 832) < 0
+
+
+def test_gate_mlp_weight_gradients_through_autograd():
+    """The autograd route of the gate MLP: layers with 64-multiple sides run forward, input gradient and weight gradient
+    on the tcgen05 kernels; all of them against float64, force-loss style (a gradient of a gradient)."""
+    from ictc_o3.operators import _RowsTimesWeight
+    torch.manual_seed(11)
+    rows = torch.randn(3001, 64, device="cuda", requires_grad=True)
+    w1 = (torch.randn(64, 64, device="cuda") / 8).requires_grad_(True)
+    w2 = (torch.randn(1472, 64, device="cuda") / 8).requires_grad_(True)      # wider than one 768-column block
+
+    def run(r, a, b, op):
+        h = torch.nn.functional.silu(op(r, a))
+        g = op(h, b)
+        first, = torch.autograd.grad((g * g).sum(), r, create_graph=True)
+        return torch.autograd.grad((first * first).sum() + g.sum(), [r, a, b])
+
+    got = run(rows, w1, w2, _RowsTimesWeight.apply)
+    ref = run(*(t.detach().double().cpu().requires_grad_(True) for t in (rows, w1, w2)), lambda r, w: r @ w.t())
+    for a, b in zip(got, ref):
+        assert float((a.double().cpu() - b).abs().max() / b.abs().max()) < 5e-5     # second order, fp32 sums 1,472 wide
