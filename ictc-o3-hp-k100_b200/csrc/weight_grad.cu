@@ -94,10 +94,10 @@ __global__ void __launch_bounds__(kThreads, 1) weight_grad_kernel(Args a) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < kRawStages; ++i) {
       mbar_init(saddr(&bar->raw_full[i]), 1);
-      mbar_init(saddr(&bar->raw_empty[i]), kWorkers);
+      mbar_init(saddr(&bar->raw_empty[i]), kWorkWarps);
     }
     for (int i = 0; i < kOpStages; ++i) {
-      mbar_init(saddr(&bar->op_full[i]), kWorkers);
+      mbar_init(saddr(&bar->op_full[i]), kWorkWarps);
       mbar_init(saddr(&bar->op_empty[i]), 1);
     }
     mbar_init(saddr(&bar->done), 1);
@@ -157,17 +157,27 @@ __global__ void __launch_bounds__(kThreads, 1) weight_grad_kernel(Args a) {
       const unsigned fb = saddr(&bar->raw_full[s]);
       if (lane == 0) mbar_expect_tx(fb, unsigned(valid) * unsigned(pitch));
       __syncwarp();
-      for (int r = lane; r < valid; r += 32) {
-        const unsigned dst = saddr(raw + s * raw_b + r * pitch);
-        bulk_g2s(dst, a.grad + (r0 + r) * a.grad_ld, unsigned(a.NO) * 4u, fb);
-        bulk_g2s(dst + unsigned(a.NO) * 4u, a.rows + (r0 + r) * a.rows_ld, kK * 4u, fb);
+      // raw stage = [stage_rows x NO] block of grad, then [stage_rows x 64] block of rows; an operand stored without
+      // row padding arrives as ONE copy (small per-row copies are bound by the copy engine's request rate)
+      const unsigned gdst = saddr(raw + s * raw_b), xdst = gdst + unsigned(stage_rows) * unsigned(a.NO) * 4u;
+      if (a.grad_ld == a.NO) {
+        if (lane == 0) bulk_g2s(gdst, a.grad + r0 * a.grad_ld, unsigned(valid) * unsigned(a.NO) * 4u, fb);
+      } else {
+        for (int r = lane; r < valid; r += 32)
+          bulk_g2s(gdst + unsigned(r) * unsigned(a.NO) * 4u, a.grad + (r0 + r) * a.grad_ld, unsigned(a.NO) * 4u, fb);
+      }
+      if (a.rows_ld == kK) {
+        if (lane == 1) bulk_g2s(xdst, a.rows + r0 * a.rows_ld, unsigned(valid) * kK * 4u, fb);
+      } else {
+        for (int r = lane; r < valid; r += 32)
+          bulk_g2s(xdst + unsigned(r) * kK * 4u, a.rows + (r0 + r) * a.rows_ld, kK * 4u, fb);
       }
     }
   } else {
     // ---- transform: thread = up to kItemsMax 16-byte chunks (K step, feature, four consecutive rows) per stage
     const int pt = threadIdx.x - 64;
     const int per_k = tiles * 2 * kRows + 2 * kK, a_items = tiles * 2 * kRows, items = ks_n * per_k;
-    int src_off[kItemsMax], dst_off[kItemsMax], part[kItemsMax], row0[kItemsMax];
+    int src_off[kItemsMax], src_step[kItemsMax], dst_off[kItemsMax], part[kItemsMax], row0[kItemsMax];
     bool used[kItemsMax];
 #pragma unroll
     for (int i = 0; i < kItemsMax; ++i) {
@@ -178,7 +188,8 @@ __global__ void __launch_bounds__(kThreads, 1) weight_grad_kernel(Args a) {
       const int q = is_a ? rem / (tiles * kRows) : (rem - a_items) / kK;
       const int f = is_a ? rem - q * (tiles * kRows) : (rem - a_items) - q * kK;
       row0[i] = ks * 8 + 4 * q;
-      src_off[i] = row0[i] * pitch + (is_a ? f : a.NO + f) * 4;
+      src_step[i] = (is_a ? a.NO : kK) * 4;
+      src_off[i] = (is_a ? 0 : stage_rows * a.NO * 4) + row0[i] * src_step[i] + f * 4;
       dst_off[i] = ks * ks_b + (is_a ? (f / kRows) * 2 * kAPart + q * (kRows * 16) + (f % kRows) * 16
                                      : tiles * 2 * kAPart + q * (kK * 16) + f * 16);
       part[i] = is_a ? kAPart : kBPart;
@@ -200,7 +211,7 @@ __global__ void __launch_bounds__(kThreads, 1) weight_grad_kernel(Args a) {
         float v[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          v[j] = (src_off[i] >= 0 && row0[i] + j < valid) ? *reinterpret_cast<const float*>(in + src_off[i] + j * pitch) : 0.f;
+          v[j] = (src_off[i] >= 0 && row0[i] + j < valid) ? *reinterpret_cast<const float*>(in + src_off[i] + j * src_step[i]) : 0.f;
         float4 big, small;
         big.x = to_tf32(v[0]); small.x = to_tf32(v[0] - big.x);
         big.y = to_tf32(v[1]); small.y = to_tf32(v[1] - big.y);
@@ -210,8 +221,11 @@ __global__ void __launch_bounds__(kThreads, 1) weight_grad_kernel(Args a) {
         *reinterpret_cast<float4*>(out + dst_off[i] + part[i]) = small;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA's reads
-      mbar_arrive(saddr(&bar->op_full[os]));
-      mbar_arrive(saddr(&bar->raw_empty[rs]));
+      __syncwarp();
+      if (lane == 0) {                 // one arrival per warp: 512 single arrivals per stage cost more than the stage
+        mbar_arrive(saddr(&bar->op_full[os]));
+        mbar_arrive(saddr(&bar->raw_empty[rs]));
+      }
     }
     // ---- epilogue: warps 2-5 cover the four lane quarters of TMEM (quarter = warp % 4)
     if (warp <= 5) {
