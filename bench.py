@@ -532,6 +532,12 @@ def main_md(args, rank, world, local):
     dev = torch.device("cuda", local)
     if world > 1:
         import torch.distributed as dist
+        if world > 2 and args.capture_collectives != "no":
+            # recorded collectives on more than two ranks need the collective library without in-switch reduction and
+            # without buffer registration at capture time (the replay never completed with the defaults); plain ring /
+            # peer-copy kernels are all the small exchanges of this step need
+            os.environ["NCCL_NVLS_ENABLE"] = "0"
+            os.environ["NCCL_GRAPH_REGISTER"] = "0"
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -554,7 +560,8 @@ def main_md(args, rank, world, local):
     z = np.array([1, 6, 8])[species]
     md = MolecularDynamics(model, pos, z, box, dt=MD_DT, temperature=MD_T, seed=1, distributed=world > 1,
                            skin=args.skin, chunk_rows=chunk_rows or None, sort_atoms=not args.no_sort,
-                           stream_gates={"auto": None, "yes": True, "no": False}[args.stream_gates])
+                           stream_gates={"auto": None, "yes": True, "no": False}[args.stream_gates],
+                           capture_collectives={"auto": None, "yes": True, "no": False}[args.capture_collectives])
     del pos, species
     warm = max(3, args.warmup)
     md.compute_forces()
@@ -879,6 +886,9 @@ def main():
     ap.add_argument("--cpu-md-side", type=int, default=24, help="CPU arm: sites per edge of the periodic sample")
     ap.add_argument("--no-sort", action="store_true", help="keep the atoms in lattice order (no space-filling-curve sort)")
     ap.add_argument("--no-graph", action="store_true", help="do not record the MD step as a CUDA graph")
+    ap.add_argument("--capture-collectives", default="auto", choices=["auto", "yes", "no"],
+                    help="decomposed run: record the step with its collectives as one CUDA graph (auto: yes; beyond two ranks "
+                         "the benchmark then switches NVLS and graph buffer registration off before NCCL starts)")
     ap.add_argument("--atoms", type=int, default=NUM_ATOMS)
     ap.add_argument("--nodes", type=int, default=SC_NODES)
     ap.add_argument("--cpu-sample-atoms", type=int, default=2048)

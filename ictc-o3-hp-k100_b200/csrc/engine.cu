@@ -164,20 +164,30 @@ struct LayoutArgs {
   int count[kLayoutBlocks], m[kLayoutBlocks], off[kLayoutBlocks + 1];
 };
 
-__global__ void layout_copy_kernel(LayoutArgs a, const float* __restrict__ in, float* __restrict__ out, int to_ir_mul) {
-  const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= a.rows * a.width) return;
-  const int64_t r = idx / a.width;
-  const int col = int(idx % a.width);
-  int b = 0;
-  while (b + 1 < a.nblocks && col >= a.off[b + 1]) ++b;
-  const int m = a.m[b], C = a.C;
-  const int rel = col - a.off[b];
-  const int slot = rel / (C * m), q = rel % (C * m);
-  // output index q -> (outer, inner) of the OUTPUT block; the input block is its transpose
-  const int outer = to_ir_mul ? q / C : q / m, inner = to_ir_mul ? q % C : q % m;
-  const int src = to_ir_mul ? inner * m + outer : inner * C + outer;
-  out[idx] = in[r * a.width + a.off[b] + slot * C * m + src];
+// One block per group of rows: a row is read as it lies in memory (coalesced) into shared memory, and written in the
+// other order from there (the transposed reads hit shared memory with odd strides 2l+1, or stride C across the
+// 2l+1 <= 5 components: no bank conflicts worth mentioning), so both global accesses are contiguous.
+__global__ void __launch_bounds__(256) layout_copy_kernel(LayoutArgs a, const float* __restrict__ in,
+                                                          float* __restrict__ out, int to_ir_mul) {
+  extern __shared__ float layout_row[];
+  for (int64_t r = blockIdx.x; r < a.rows; r += gridDim.x) {
+    const float* src_row = in + r * a.width;
+    for (int col = threadIdx.x; col < a.width; col += blockDim.x) layout_row[col] = src_row[col];
+    __syncthreads();
+    float* dst_row = out + r * a.width;
+    for (int col = threadIdx.x; col < a.width; col += blockDim.x) {
+      int b = 0;
+      while (b + 1 < a.nblocks && col >= a.off[b + 1]) ++b;
+      const int m = a.m[b], C = a.C;
+      const int rel = col - a.off[b];
+      const int slot = rel / (C * m), q = rel - slot * (C * m);
+      // output index q -> (outer, inner) of the OUTPUT block; the input block is its transpose
+      const int outer = to_ir_mul ? q / C : q / m, inner = to_ir_mul ? q - outer * C : q - outer * m;
+      const int src = to_ir_mul ? inner * m + outer : inner * C + outer;
+      dst_row[col] = layout_row[a.off[b] + slot * C * m + src];
+    }
+    __syncthreads();
+  }
 }
 
 }  // namespace ictc
@@ -266,8 +276,14 @@ int ictc_layout_copy(int64_t rows, int channels, int num_blocks, const int* host
   const int64_t total = rows * int64_t(off);
   if (total == 0) return ICTC_OK;
   if (!in || !out) { set_error("layout copy: NULL buffer"); return ICTC_ERR_BAD_ARG; }
-  if ((total + 255) / 256 > 2147483647LL) { set_error("layout copy: too large"); return ICTC_ERR_TOO_LARGE; }
-  layout_copy_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, in, out, to_ir_mul);
+  const size_t smem = size_t(off) * sizeof(float);
+  if (smem > 200 * 1024) { set_error("layout copy: rows of %d floats do not fit shared memory", off); return ICTC_ERR_TOO_LARGE; }
+  if (smem > 48 * 1024) {
+    const cudaError_t attr = cudaFuncSetAttribute(layout_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (attr != cudaSuccess) { set_error("layout copy smem: %s", cudaGetErrorString(attr)); return ICTC_ERR_LAUNCH; }
+  }
+  const int64_t blocks = rows < 148 * 8 * 4 ? rows : 148 * 8 * 4;       // a few waves of row-looping blocks
+  layout_copy_kernel<<<(unsigned)blocks, 256, smem, (cudaStream_t)stream>>>(a, in, out, to_ir_mul);
   return finish_launch("layout_copy");
 }
 

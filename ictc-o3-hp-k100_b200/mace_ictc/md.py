@@ -199,11 +199,18 @@ class MolecularDynamics:
     gates themselves are streamed or only their gradient (``ForceEngine.stream_gates``).  ``use_engine``: None picks the
     tape-free force engine for the 64-channel two-interaction model and autograd through the same kernels
     otherwise.  ``watch_peers``: check before every block of steps that all ranks are still there.
+    ``capture_collectives``: whether ``enable_graph`` of a decomposed run records the step, collectives included, as
+    one CUDA graph.  On four ranks the replay of such a graph never completed with the collective library's defaults
+    (every rank waiting in the host read after the replays; the same step run eagerly before it was fine; no GPU
+    fault) and completes with in-switch reduction and capture-time buffer registration switched off
+    (NCCL_NVLS_ENABLE=0, NCCL_GRAPH_REGISTER=0, set before the process group is created).  None = record with two
+    ranks, and with more ranks only when the environment shows both settings; otherwise the step is launched
+    eagerly — same kernels, same fixed buffers, no host read-back inside a block of steps.
     """
 
     def __init__(self, model, positions, atomic_numbers, box, *, dt=1.0, temperature=300.0, seed=0,
                  velocities=None, distributed=False, use_engine=None, share_gates=True, skin=2.0, chunk_rows=None,
-                 stream_gates=None, watch_peers=False, sort_atoms=True):
+                 stream_gates=None, watch_peers=False, sort_atoms=True, capture_collectives=None):
         self.model = model
         dev = next(model.parameters()).device
         self.device = dev
@@ -283,7 +290,11 @@ class MolecularDynamics:
         self._stale_block = 8
         self.refresh_seconds = 0.0   # host time spent in refreshes (they synchronise)
         self.events = []             # (what, steps, host seconds) of the decomposed run's blocks and refreshes
-        self.capture_collectives = True
+        if capture_collectives is None:
+            import os
+            capture_collectives = self.world <= 2 or (os.environ.get("NCCL_NVLS_ENABLE") == "0"
+                                                      and os.environ.get("NCCL_GRAPH_REGISTER") == "0")
+        self.capture_collectives = bool(capture_collectives)
         self.zero_box = torch.zeros(3, dtype=torch.float32, device=dev)
         self._watch = D.PeerWatch() if (watch_peers and self.world > 1) else None
 
@@ -666,6 +677,8 @@ class MolecularDynamics:
         if self.world > 1:
             if self._dist is None:
                 self.compute_forces()
+            if not self.capture_collectives:        # the step stays an eager launch sequence on the fixed buffers
+                return self._dist["cap"]
             keep = (self.pos.clone(), self.vel.clone(), self.forces.clone(), self._dist["energy"].clone())
             side = torch.cuda.Stream(device=dev)
             side.wait_stream(torch.cuda.current_stream(dev))
