@@ -728,7 +728,7 @@ def main_md(args, rank, world, local):
 
 # DRAM bytes per edge of one layer-1 adjoint launch, measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum)
 # on the 32,768-atom case; traffic grows in proportion to the edge count at fixed density
-TRAFFIC_PER_EDGE = 6266.0
+TRAFFIC_PER_EDGE = 6235.0
 TRAFFIC_SOURCE = "ncu on 32768 atoms, scaled by edges"
 
 
