@@ -204,8 +204,9 @@ class MolecularDynamics:
     (every rank waiting in the host read after the replays; the same step run eagerly before it was fine; no GPU
     fault) and completes with in-switch reduction and capture-time buffer registration switched off
     (NCCL_NVLS_ENABLE=0, NCCL_GRAPH_REGISTER=0, set before the process group is created).  None = record with two
-    ranks, and with more ranks only when the environment shows both settings; otherwise the step is launched
-    eagerly — same kernels, same fixed buffers, no host read-back inside a block of steps.
+    ranks, with three or four ranks when the environment shows both settings (the rank counts the recording was run
+    on), otherwise launch the step eagerly — same kernels, same fixed buffers, no host read-back inside a block of
+    steps.  True records at any rank count.
     """
 
     def __init__(self, model, positions, atomic_numbers, box, *, dt=1.0, temperature=300.0, seed=0,
@@ -292,7 +293,7 @@ class MolecularDynamics:
         self.events = []             # (what, steps, host seconds) of the decomposed run's blocks and refreshes
         if capture_collectives is None:
             import os
-            capture_collectives = self.world <= 2 or (os.environ.get("NCCL_NVLS_ENABLE") == "0"
+            capture_collectives = self.world <= 2 or (self.world <= 4 and os.environ.get("NCCL_NVLS_ENABLE") == "0"
                                                       and os.environ.get("NCCL_GRAPH_REGISTER") == "0")
         self.capture_collectives = bool(capture_collectives)
         self.zero_box = torch.zeros(3, dtype=torch.float32, device=dev)
