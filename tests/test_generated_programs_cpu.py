@@ -114,3 +114,37 @@ def test_generated_programs_equal_the_coupling_list(spec):
     np.testing.assert_allclose(dx3, dx, rtol=1e-12, atol=1e-13)
     np.testing.assert_allclose(dg3, dg, rtol=1e-12, atol=1e-13)
     np.testing.assert_allclose(dsh3, dsh, rtol=1e-6, atol=1e-7)      # the constants are float32 literals of one group member
+
+
+@pytest.mark.parametrize("name,spec", [("tp_c5_l111_e13_w", "L111"), ("tp_c8_l022_e19", "L022"), ("tp_c8_l222_e37", "L222")])
+def test_generated_coupling_list_matches_reference_outputs(name, spec):
+    """The coupling list of the generated header, evaluated in numpy on the inputs of the reference-produced vectors
+    (tests/golden/make_golden.py: the reference's own EdgeTensorProduct), gives the reference's outputs: the constants
+    the kernels are compiled from are pinned on the reference without a GPU."""
+    mac = _macros()
+    gold = np.load(os.path.join(os.path.dirname(HEADER), "..", "..", "..", "tests", "golden", name + ".npz"))
+    lin, lout, c = int(gold["lin"]), int(gold["lout"]), int(gold["channels"])
+    paths = [tuple(int(v) for v in p) for p in gold["paths"]]
+    e = gold["sh"].shape[0]
+    x = np.concatenate([np.transpose(gold[f"x{l}"], (0, 2, 1)) for l in range(lin + 1)], axis=1)      # [E, i, C]
+    sh = gold["sh"]
+    gates = gold["gates"].reshape(e, len(paths), c) * gold["weight"][None]
+    terms = [(int(a[0]), int(a[1]), int(a[2]), int(a[3]), a[4]) for _n, a in _calls(mac[f"ICTC_TP_{spec}_BYK"])]
+    outp = {int(a[0]): int(a[1]) for _n, a in _calls(mac[f"ICTC_TP_{spec}_OUTP"])}
+    no = int(mac[f"ICTC_TP_{spec}_NO"])
+    out = np.zeros((e, no, c))
+    for i, j, k, p, coef in terms:
+        assert outp[k] == p
+        out[:, k] += coef * x[:, i] * sh[:, j, None] * gates[:, p]
+    # output slots: degree -> path slot (paths of that output degree, in path order) -> component
+    k = 0
+    for l in range(lout + 1):
+        slots = [p for p, (_a, _b, lo) in enumerate(paths) if lo == l]
+        ref = gold[f"out{l}"].reshape(e, len(slots), c, 2 * l + 1)
+        for s, p in enumerate(slots):
+            for m in range(2 * l + 1):
+                assert outp[k] == p
+                err = np.abs(out[:, k] - ref[:, s, :, m]).max()
+                assert err <= 3e-7 * max(np.abs(ref).max(), 1e-30), (l, s, m, err)
+                k += 1
+    assert k == no
