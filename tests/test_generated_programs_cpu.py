@@ -148,3 +148,26 @@ def test_generated_coupling_list_matches_reference_outputs(name, spec):
                 assert err <= 3e-7 * max(np.abs(ref).max(), 1e-30), (l, s, m, err)
                 k += 1
     assert k == no
+
+
+def test_generated_harmonic_polynomials_match_reference_harmonics():
+    """The polynomial table the harmonics kernels are compiled from (csrc/generated/harmonics_tables.cuh), evaluated in
+    numpy on the unit vectors of the reference-produced harmonics vectors: values and the gradient contracted with the
+    stored cotangent (the table is differentiated term by term, as the kernel does)."""
+    text = open(os.path.join(os.path.dirname(HEADER), "harmonics_tables.cuh")).read().replace("\\\n", " ")
+    body = re.search(r"#define ICTC_HARM_TERMS\(T\) (.*)", text).group(1)
+    terms = [(int(a[0]), int(a[1]), int(a[2]), int(a[3]), a[4]) for _n, a in _calls(body)]
+    gold = np.load(os.path.join(os.path.dirname(HEADER), "..", "..", "..", "tests", "golden", "harmonics_l2_e41.npz"))
+    n, cot = gold["n"], gold["cot"]
+    y, dn = np.zeros_like(gold["y"]), np.zeros_like(n)
+    for h, a, b, c, coef in terms:
+        px, py, pz = n[:, 0] ** a, n[:, 1] ** b, n[:, 2] ** c
+        y[:, h] += coef * px * py * pz
+        if a:
+            dn[:, 0] += cot[:, h] * coef * a * n[:, 0] ** (a - 1) * py * pz
+        if b:
+            dn[:, 1] += cot[:, h] * coef * b * px * n[:, 1] ** (b - 1) * pz
+        if c:
+            dn[:, 2] += cot[:, h] * coef * c * px * py * n[:, 2] ** (c - 1)
+    assert np.abs(y - gold["y"]).max() <= 3e-7 * np.abs(gold["y"]).max()
+    assert np.abs(dn - gold["dn"]).max() <= 3e-7 * np.abs(gold["dn"]).max()
